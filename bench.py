@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the hot path on B200: BASELINE config 2 (MLP fwd+bwd fp16 + AdamW).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--extras]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-configs]
 
 One "step" is one forward + backward + AdamW step of the 784 -> 8192 -> 8192 -> 10 MLP on a
 256-sample batch, issued as C-ABI launches (torchvulkan_b200.workloads.MLPStep).
@@ -13,8 +13,11 @@ launch whose step count lives in device memory). `e2e` is the same metric with t
 from pinned host memory and the loss read back inside the timed region. `roofline` describes the kernel that takes the largest share of the
 step, timed live with CUDA events; `cpu_baseline` is the ATen-CPU fp32 step (the reference's own CPU
 path for these ops) on the host cores. `--impl reference` times that CPU path alone.
-`--extras` adds the other BASELINE configs (fp32 mm 1024^3, bf16 bmm 64x4096^3 sharded over the
-ranks with an all-gather, fp32 add/exp/sum/argmax over 2^30 elements) as extra keys.
+The same line carries the other BASELINE configs: `sharded_bmm` (bf16 bmm 64x4096^3 with the batches sharded over the
+ranks and C completed on every rank, value-checked; at every N, N = 1 included) and, at N = 1, `configs`: fp32 mm
+1024^3, the config-2 / 3 / 4 training scripts on the "vulkan" device (eager and torchvulkan.Graph, config 4 in NCHW and
+channels-last) beside ATen CPU fp32, and fp32 add/exp/sum/argmax over 2^30 elements as GB/s. `--no-configs` leaves
+those out.
 """
 from __future__ import annotations
 
@@ -35,6 +38,12 @@ SIZES = (784, 8192, 8192, 10)
 BATCH = 256
 METRIC = "fp16 mm TFLOP/s over the MLP fwd+bwd+AdamW step"
 UNIT = "TFLOP/s"
+# fp16 loss scaling: the backward pass runs on loss * LOSS_SCALE and AdamW's eps is scaled by the same factor, which in
+# exact arithmetic is the unscaled AdamW(eps=1e-8) step (the update m/(sqrt(v)+eps) is homogeneous of degree 0 in the
+# gradient scale once eps scales with it). Without it the fp16 second moments of a mean loss over 256 samples underflow
+# to zero on any backend and the parameters turn into inf/NaN within a few steps.
+LOSS_SCALE = 16384.0
+ADAM_EPS = 1e-8 * LOSS_SCALE
 
 
 def peaks():
@@ -174,9 +183,11 @@ def summarize_trace(trace):
     return agg
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu captures of these two kernels
-# whose summaries are kept under profiles/
-NCU_TRAFFIC_BYTES = {"adam_step n67108864": 882.9e6, "adam_step_multi n73629706": 974.6e6, "gemm m256 n8192 k8192": 142.2e6}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from recorded ncu captures of these kernels (bytes, summary
+# file). They are NOT measured by this run: the line says where the figure comes from, and a kernel without a capture
+# reports null.
+NCU_TRAFFIC_BYTES = {"adam_step n67108864": (882.9e6, "profiles/adam_vec_kernel_half_67M_params.md"),
+                     "adam_step_multi n73629706": (974.6e6, "profiles/adam_multi_kernel_half_73M_params.md")}
 
 
 def kernel_algorithmic(tag: str, es: int = 2):
@@ -206,7 +217,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     pk = peaks()
     # one list launch for AdamW over all six parameter tensors, its step count in device memory: the whole step is
     # then a fixed sequence of launches that can be replayed as a CUDA graph
-    step = MLPStep(sizes=SIZES, batch=BATCH, dtype=torch.float16, device=dev, seed=0, list_optimizer=True)
+    step = MLPStep(sizes=SIZES, batch=BATCH, dtype=torch.float16, device=dev, seed=0, list_optimizer=True, loss_scale=LOSS_SCALE, eps=ADAM_EPS)
     g = torch.Generator().manual_seed(0)
     x_host = torch.randn(BATCH, SIZES[0], generator=g).half().pin_memory()
     y_host = torch.randint(0, SIZES[-1], (BATCH,), generator=g).pin_memory()
@@ -283,6 +294,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         e2e_step()
     ms_e2e = timed(e2e_step, args.steps) / args.steps
     clocks = sampler.stop() if rank == 0 else None
+    final_loss = float(loss_host)
     e2e = {"value": world * flops / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
            "h2d_bytes_per_step": x_host.numel() * 2 + y_host.numel() * 8, "d2h_bytes_per_step": 2,
            "api": "C-ABI launches (tvk_* entry points) captured once and replayed as a CUDA graph; inputs from pinned host memory, loss read back"}
@@ -299,15 +311,17 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         total = sum(v[1] for v in agg.values())
         kernels = sorted(((t, c, msum) for t, (c, msum) in agg.items()), key=lambda r: -r[2])
         top_tag, top_count, top_ms = kernels[0]
-        bound, alg, _ = kernel_algorithmic(top_tag)
+        bound, alg, alg_bytes = kernel_algorithmic(top_tag)
         dur = top_ms / top_count * 1e-3
         if bound == "tensor":
             achieved, peak, unit = alg / dur / 1e12, pk["bf16_tflops"], "TFLOP/s"
         else:
             achieved, peak, unit = (alg / dur / 1e9 if alg else None), pk["hbm_gbs"], "GB/s"
+        traffic, traffic_src = NCU_TRAFFIC_BYTES.get(top_tag, (None, None))
         roofline = {"kernel": top_tag, "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
-                    "frac": (achieved / peak if achieved else None), "traffic": NCU_TRAFFIC_BYTES.get(top_tag), "peak_source": pk["source"],
-                    "launch_us": dur * 1e6, "share_of_step": top_ms / total}
+                    "frac": (achieved / peak if achieved else None), "traffic": traffic,
+                    "traffic_source": (traffic_src + " (recorded ncu capture, not this run)") if traffic_src else None,
+                    "algorithmic_bytes": alg_bytes, "peak_source": pk["source"], "launch_us": dur * 1e6, "share_of_step": top_ms / total}
         breakdown = [{"kernel": t, "launches_per_step": c // reps, "us_per_launch": msum / c * 1e3, "share": msum / total} for t, c, msum in kernels[:8]]
 
         cpu = None
@@ -323,28 +337,28 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "config": {"workload": "MLP 784-8192-8192-10 GELU, batch 256, fwd+bwd+AdamW (BASELINE config 2)",
                        "parallelism": "replicas only" if world > 1 else "single GPU",
                        "l2": "no flush: 0.74 GB of weights, gradients and optimizer state per step exceed the 126 MB L2",
-                       "launch": "CUDA-graph replay of the step's launches"},
+                       "launch": "CUDA-graph replay of the step's launches",
+                       "loss_scale": LOSS_SCALE, "adam_eps": ADAM_EPS, "loss_after_timed_steps": final_loss},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu, "kernels": breakdown,
         }
-    if world > 1 and not args.extras:
-        # the one part of the path that shards: reported with every multi-GPU run
-        sharded = run_sharded_bmm(rank, world, dev, pk)
-        if rank == 0:
-            line["sharded_bmm"] = sharded
-    if args.extras:
-        extras = run_extras(args, rank, world, dev, pk)
-        if rank == 0:
-            line["extras"] = extras
+    del step
+    torch.cuda.empty_cache()
+    # the one part of the path that shards: reported with every run (N = 1 is the anchor of the strong-scaling curve)
+    sharded = run_sharded_bmm(rank, world, dev, pk)
+    if rank == 0:
+        line["sharded_bmm"] = sharded
+    if world == 1 and not args.no_configs:
+        line["configs"] = run_configs(args, dev, pk)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_extras(args, rank, world, dev, pk):
-    """The other BASELINE configs: C1 fp32 mm, C5 sharded bf16 bmm + all-gather, C5 bandwidth kernels."""
+def run_configs(args, dev, pk):
+    """The other single-GPU BASELINE configs: C1 fp32 mm 1024^3 (-> relu -> sum), C5 (ii) fp32 add/exp/sum/argmax over
+    2^30 elements, and the training scripts of configs 2, 3 and 4 on the "vulkan" device."""
     import torch
-    import torch.distributed as dist
     from torchvulkan_b200 import cuda_ops as ops
 
     out = {}
@@ -362,46 +376,68 @@ def run_extras(args, rank, world, dev, pk):
         return statistics.median(times)
 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than L2
-    if rank == 0:
-        torch.manual_seed(0)
-        a, b = torch.randn(1024, 1024).to(dev), torch.randn(1024, 1024).to(dev)
-        for _ in range(3):
-            ops.gemm(a, b)
-        ms = ev_time(lambda: ops.gemm(a, b), 10, flush)
-        out["c1_fp32_mm_1024"] = {"ms": ms, "tflops": 2 * 1024 ** 3 / ms / 1e9, "note": "3xTF32, includes the hi/lo split launches"}
+    torch.manual_seed(0)
+    ah, bh = torch.randn(1024, 1024), torch.randn(1024, 1024)
+    a, b = ah.to(dev), bh.to(dev)
+    for _ in range(3):
+        ops.gemm(a, b)
+    ms = ev_time(lambda: ops.gemm(a, b), 10, flush)
 
-    out["c5_bf16_bmm_64x4096"] = run_sharded_bmm(rank, world, dev, pk)
+    def c1_chain():
+        return ops.reduce("sum", ops.unary("relu", ops.gemm(a, b)))
 
-    if rank == 0:
-        n = 1 << 30
-        x = torch.randn(n, device=dev)
-        y = torch.randn(n, device=dev)
-        z = torch.empty_like(x)
-        bw = {}
-        for name, fn, nbytes in (("add", lambda: ops.binary("add", x, y, out=z), 12 * n), ("exp", lambda: ops.unary("exp", x, out=z), 8 * n),
-                                 ("sum", lambda: ops.reduce("sum", x), 4 * n), ("argmax", lambda: ops.argreduce(x), 4 * n)):
-            fn()
-            ms = ev_time(fn, 5)
-            bw[name] = {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / pk["hbm_gbs"]}
-        out["c5_fp32_2p30"] = bw
-        del x, y, z
-        out.update(run_model_steps(args))
+    s_dev = float(c1_chain())
+    ms_chain = ev_time(c1_chain, 10, flush)
+    ref = float((ah.double() @ bh.double()).relu().sum())
+    out["c1_fp32_mm_1024"] = {"ms": ms, "tflops": 2 * 1024 ** 3 / ms / 1e9, "ms_mm_relu_sum": ms_chain, "sum": s_dev, "sum_fp64_cpu": ref,
+                              "sum_rel_error": abs(s_dev - ref) / abs(ref), "note": "3xTF32, includes the hi/lo split launches; L2 flushed between repetitions"}
+    del a, b, flush
+
+    n = 1 << 30
+    x = torch.randn(n, device=dev)
+    y = torch.randn(n, device=dev)
+    z = torch.empty_like(x)
+    bw = {}
+    for name, fn, nbytes in (("add", lambda: ops.binary("add", x, y, out=z), 12 * n), ("exp", lambda: ops.unary("exp", x, out=z), 8 * n),
+                             ("sum", lambda: ops.reduce("sum", x), 4 * n), ("argmax", lambda: ops.argreduce(x), 4 * n)):
+        fn()
+        ms = ev_time(fn, 5)
+        bw[name] = {"ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / pk["hbm_gbs"], "algorithmic_bytes": nbytes}
+    bw["peak_gbs"], bw["peak_source"] = pk["hbm_gbs"], pk["source"]
+    bw["l2"] = "operands of 4 GiB each: far larger than L2, no flush"
+    out["c5_fp32_2p30"] = bw
+    del x, y, z
+    torch.cuda.empty_cache()
+    out.update(run_model_steps(args))
     return out
 
 
 def run_sharded_bmm(rank, world, dev, pk):
     """BASELINE config 5 (i): bf16 bmm 64 x 4096^3 with the batches sharded over the ranks; every rank ends with the
     full C. Times the local GEMM alone and the three ways of completing C (torchvulkan_b200/sharded.py), each as the
-    max over ranks of a CUDA-event interval around `reps` back-to-back steps."""
+    max over ranks of a CUDA-event interval around `reps` back-to-back steps, and then CHECKS what every mode left in
+    this rank's copy of C: for one batch owned by each other rank (and one of its own) the operands are regenerated
+    here from the batch's seed, the batch is multiplied locally, and the block that arrived over NVLink must match that
+    local product (1e-3 relative Frobenius error; whether it was bit-identical is reported); a 97-row sample of it is
+    also held to 1e-2 against an fp32 product by torch. A mode that fails the check fails the run."""
     import torch
     import torch.distributed as dist
     from torchvulkan_b200.sharded import ShardedBmm, shard_range
 
     lo, hi = shard_range(64, rank, world)
     nb = hi - lo
-    g = torch.Generator(device=dev).manual_seed(rank)
-    A = torch.randn(nb, 4096, 4096, device=dev, generator=g).bfloat16()
-    B = torch.randn(nb, 4096, 4096, device=dev, generator=g).bfloat16()
+
+    def batch_operands(b):
+        # operands of global batch b: the same bits on whichever rank generates them
+        g = torch.Generator(device=dev).manual_seed(1000 + b)
+        a_ = torch.randn(4096, 4096, device=dev, generator=g).bfloat16()
+        b_ = torch.randn(4096, 4096, device=dev, generator=g).bfloat16()
+        return a_, b_
+
+    A = torch.empty(nb, 4096, 4096, dtype=torch.bfloat16, device=dev)
+    B = torch.empty(nb, 4096, 4096, dtype=torch.bfloat16, device=dev)
+    for i in range(nb):
+        A[i], B[i] = batch_operands(lo + i)
     Cfull = torch.empty(64, 4096, 4096, dtype=torch.bfloat16, device=dev)
 
     def timed(fn, reps=5):
@@ -423,32 +459,81 @@ def run_sharded_bmm(rank, world, dev, pk):
             ms = float(t[0])
         return ms
 
-    flops = 64 * 2 * 4096 ** 3
     local = ShardedBmm(Cfull, mode="allgather", compute=None)
+    scratch = torch.empty(4096, 4096, dtype=torch.bfloat16, device=dev)
+    rows = torch.arange(97, device=dev) * 42 + 7          # 97 rows spread over the 4096
+
+    def verify(run_once):
+        """Poisons C, runs one more step and compares the blocks described above. Returns (ok, worst error, bit-equal)."""
+        Cfull.fill_(float("nan"))
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        run_once()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ok, worst, bit_equal = True, 0.0, True
+        for q in range(world):
+            qlo, qhi = shard_range(64, q, world)
+            if qhi <= qlo:
+                continue
+            b = qlo + (rank + 3 * q) % (qhi - qlo)        # a different batch of rank q on every rank
+            a_, b_ = batch_operands(b)
+            local._gemm(a_, b_, scratch)
+            bit_equal = bit_equal and bool(torch.equal(scratch, Cfull[b]))
+            # the whole block against the local product (a line that never arrived is still NaN and fails this)
+            whole = float((Cfull[b].float() - scratch.float()).norm() / scratch.float().norm())
+            ref = a_[rows].float() @ b_.float()
+            err = float((Cfull[b][rows].float() - ref).norm() / ref.norm())
+            ok = ok and whole <= 1e-3 and err <= 1e-2
+            worst = max([worst] + [e if e == e else float("inf") for e in (err, whole)])
+        flag = torch.tensor([0.0 if ok else 1.0, worst, 0.0 if bit_equal else 1.0], device=dev)
+        if world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        return bool(flag[0] == 0), float(flag[1]), bool(flag[2] == 0)
+
+    flops = 64 * 2 * 4096 ** 3
     ms_gemm = timed(lambda: local._gemm(A, B, local.mine))
     res = {"n_gpus": world, "batches_per_gpu": nb, "ms_gemm_only": ms_gemm, "tflops_per_gpu_gemm_only": nb * 2 * 4096 ** 3 / ms_gemm / 1e9,
            "frac_of_peak_gemm_only": nb * 2 * 4096 ** 3 / ms_gemm / 1e9 / pk["bf16_tflops_sustained"], "peak": pk["bf16_tflops_sustained"],
-           "peak_source": pk["source"] + " (sustained)"}
+           "peak_source": pk["source"] + " (sustained)",
+           "check": "per mode: C poisoned with NaN, one more step, then one batch of every rank recomputed locally from its seed: the block in this "
+                    "rank's C within 1e-3 relative Frobenius error of it (bit_equal says whether it was identical), and a 97-row sample within 1e-2 "
+                    "of an fp32 product"}
+    failed = []
     if world == 1:
-        res.update({"ms_per_step": ms_gemm, "tflops_total": flops / ms_gemm / 1e9})
+        ok, worst, biteq = verify(lambda: local._gemm(A, B, local.mine))
+        res.update({"ms_per_step": ms_gemm, "tflops_total": flops / ms_gemm / 1e9, "verified": ok, "worst_rel_error": worst, "bit_equal": biteq})
+        if not ok:
+            failed.append("single")
     else:
         recv = (world - 1) / world * Cfull.numel() * 2
         modes = {}
         for mode in ("allgather", "pipelined", "push"):
             op = ShardedBmm(Cfull, mode=mode, chunks=4)
             ms = timed(lambda: op.run(A, B))
+            ok, worst, biteq = verify(lambda: op.run(A, B))
             op.close()
-            modes[mode] = {"ms_per_step": ms, "tflops_total": flops / ms / 1e9}
+            modes[mode] = {"ms_per_step": ms, "tflops_total": flops / ms / 1e9, "verified": ok, "worst_rel_error": worst, "bit_equal": biteq,
+                           "ingest_gbs": recv / ms / 1e6}
+            if not ok:
+                failed.append(mode)
         best = min(modes, key=lambda m: modes[m]["ms_per_step"])
         # the slower of the tensor-core time of the local GEMM and the NVLink time of the bytes each GPU must receive
         link_ms = recv / 770e9 * 1e3
         target = max(nb * 2 * 4096 ** 3 / (pk["bf16_tflops_sustained"] * 1e12) * 1e3, link_ms)
         res.update({"modes": modes, "best_mode": best, "ms_per_step": modes[best]["ms_per_step"], "tflops_total": modes[best]["tflops_total"],
-                    "bytes_received_per_gpu": recv, "nvlink_ms_at_770GBs": link_ms, "roofline_target_ms": target,
+                    "verified": not failed, "bytes_received_per_gpu": recv, "nvlink_ms_at_770GBs": link_ms, "roofline_target_ms": target,
                     "frac_of_roofline": target / modes[best]["ms_per_step"],
                     "collective": {"allgather": "ncclAllGather after the GEMM", "pipelined": "NCCL send/recv of chunk i under the GEMM of chunk i+1",
                                    "push": "GEMM epilogue stores each tile into every peer's C over NVLink, then a 4-byte all-reduce"}})
-    del A, B, Cfull
+    del A, B, Cfull, scratch
+    torch.cuda.empty_cache()
+    if failed:
+        if rank == 0:
+            print(json.dumps({"sharded_bmm": res, "error": f"value check failed for {failed}"}), flush=True)
+        raise SystemExit(f"sharded bmm: the value check failed for {failed}")
     return res
 
 
@@ -485,9 +570,9 @@ def profile_model_steps(args):
 
 
 def run_model_steps(args):
-    """BASELINE configs 3 and 4 as a user runs them: a torch script on the "vulkan" device (fwd + bwd + optimizer step),
+    """BASELINE configs 2, 3 and 4 as a user runs them: a torch script on the "vulkan" device (fwd + bwd + optimizer step),
     timed like the reference's benchmark (warm-up 3, median of 10, zero_grad(set_to_none=True), device synchronize on
-    both sides, wall clock), beside the same script in fp32 on ATen CPU."""
+    both sides, wall clock), beside the same script in fp32 on ATen CPU (1 warm-up + 2 timed steps)."""
     import torch
     import torch.nn.functional as F
 
@@ -499,7 +584,7 @@ def run_model_steps(args):
     vk = torch.device("vulkan:0")
     out = {}
 
-    def time_script(model, make_loss, opt, sync, reps, warm):
+    def time_script(model, make_loss, opt, sync, reps, warm, read_loss=False):
         times = []
         for i in range(warm + reps):
             sync()
@@ -508,6 +593,8 @@ def run_model_steps(args):
             loss = make_loss(model)
             loss.backward()
             opt.step()
+            if read_loss:
+                loss.item()               # the device -> host read of the step's result, inside the timed region
             sync()
             if i >= warm:
                 times.append(time.perf_counter() - t0)
@@ -516,7 +603,16 @@ def run_model_steps(args):
     torch.manual_seed(0)
     ids, tgt = torch.randint(0, 128, (32, 256)), torch.randint(0, 128, (32 * 256,))
     xr, yr = torch.randn(256, 3, 32, 32), torch.randint(0, 10, (256,))
+    xm, ym = torch.randn(BATCH, SIZES[0]), torch.randint(0, SIZES[-1], (BATCH,))
+    mlp_loss = lambda m, d, half, t=(xm, ym): F.cross_entropy(m((t[0].half() if half else t[0]).to(d)), t[1].to(d)) * (LOSS_SCALE if half else 1.0)  # noqa: E731
     cfgs = {
+        # config 2 as the reference's example script runs it (examples/mlp.py:36-47): inputs moved to the device every step,
+        # AdamW(lr=1e-3, weight_decay=1e-2) with torch.optim's default (foreach) implementation, the loss read back
+        "c2_mlp_step_default_adamw": (lambda: models.mlp(SIZES), mlp_loss,
+                                      lambda ps, half: torch.optim.AdamW(ps, lr=1e-3, weight_decay=1e-2, eps=ADAM_EPS if half else 1e-8), float(gemm_flops())),
+        # the same with AdamW(fused=True): one list launch, step count on the device, so the step can also be replayed
+        "c2_mlp_step": (lambda: models.mlp(SIZES), mlp_loss,
+                        lambda ps, half: torch.optim.AdamW(ps, lr=1e-3, weight_decay=1e-2, eps=ADAM_EPS if half else 1e-8, fused=half), float(gemm_flops())),
         "c3_decoder_step": (lambda: models.Decoder(vocab=128, seq=256, layers=6, width=512, heads=8, kv_heads=2, hidden=1376),
                             lambda m, d, half, t=(ids, tgt): F.cross_entropy(m(t[0].to(d)).view(-1, 128), t[1].to(d)) * (4096.0 if half else 1.0),
                             lambda ps, half: torch.optim.AdamW(ps, lr=1e-3 / (4096.0 if half else 1.0), fused=half), 865e9),
@@ -540,11 +636,16 @@ def run_model_steps(args):
         if "channels_last" in name:
             model = model.to(memory_format=torch.channels_last)
         opt = make_opt(model.parameters(), True)
-        ms, loss = time_script(model, lambda m: loss_fn(m, vk, True), opt, torchvulkan.synchronize, 10, 3)
-        rec = {"ms_per_step": ms, "tflops_algorithmic": flops / ms / 1e9, "loss": loss, "dtype": "f16", "protocol": "warm-up 3, median of 10, wall clock"}
+        ms, loss = time_script(model, lambda m: loss_fn(m, vk, True), opt, torchvulkan.synchronize, 10, 3, read_loss=True)
+        scale = LOSS_SCALE if name.startswith("c2_") else (4096.0 if name.startswith("c3_") else 1024.0)
+        rec = {"ms_per_step": ms, "tflops_algorithmic": flops / ms / 1e9, "loss": loss / scale, "loss_scale": scale, "dtype": "f16",
+               "api": "torch script on the vulkan device: host inputs .to(device) and loss.item() every step",
+               "protocol": "warm-up 3, median of 10, wall clock with a device synchronize on both sides"}
         # The same step captured once with torchvulkan.Graph and replayed (inputs resident on the device): what the step
         # costs the GPU when the host's per-operator dispatch is out of the way.
         try:
+            if name.endswith("default_adamw"):
+                raise RuntimeError("not replayable: torch.optim's foreach AdamW keeps its step count on the host")
             host_inputs = loss_fn.__defaults__[0]
             dev_inputs = tuple((t.half() if t.is_floating_point() else t).to(vk) for t in host_inputs)
             if "channels_last" in name:
@@ -569,13 +670,13 @@ def run_model_steps(args):
                 g.replay()
             torchvulkan.synchronize()
             gms = (time.perf_counter() - t0) / 20 * 1e3
-            rec["graph_replay"] = {"ms_per_step": gms, "tflops_algorithmic": flops / gms / 1e9, "loss": float(gl.item()),
+            rec["graph_replay"] = {"ms_per_step": gms, "tflops_algorithmic": flops / gms / 1e9, "loss": float(gl.item()) / scale,
                                    "protocol": "torchvulkan.Graph: warm-up 3, mean of 20 replays, wall clock with a device synchronize on both sides"}
             g.reset()
         except Exception as e:  # noqa: BLE001
             rec["graph_replay"] = {"unavailable": str(e).splitlines()[0][:200]}
-        if "channels_last" in name:
-            out[name] = rec
+        if "channels_last" in name or name.startswith("c2_"):
+            out[name] = rec            # (config 2's CPU leg is the line's cpu_baseline)
             del model
             continue
         if not args.no_cpu_baseline:
@@ -616,7 +717,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--extras", action="store_true", help="also measure BASELINE configs 1 and 5")
+    ap.add_argument("--no-configs", action="store_true", help="leave out the `configs` key (BASELINE configs 1, 3, 4, 5(ii) and the vulkan-device scripts)")
+    ap.add_argument("--extras", action="store_true", help="accepted for compatibility: the other configs are part of the default line now")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-run", action="store_true", help="only warm-up + K device-resident steps (for ncu)")
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c4cl"],

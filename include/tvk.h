@@ -197,6 +197,8 @@ typedef enum tvk_activation {
  * bias may be NULL; its strides may be 0 for broadcast (matmul.cpp:49-53).
  * dtype is the type of A, B, C and bias: TVK_F16/TVK_BF16 accumulate in fp32
  * (matmul.cpp:92-95); TVK_F32 runs as a 3xTF32 split on the tensor cores. */
+enum { TVK_AUX_NONE = 0, TVK_AUX_GELU_BACKWARD = 1, TVK_AUX_RELU_BACKWARD = 2 };
+
 typedef struct tvk_gemm_desc {
     int32_t dtype;
     int32_t activation;
@@ -217,6 +219,21 @@ typedef struct tvk_gemm_desc {
     int32_t n_peer_c;
     int32_t reserved_;
     void* peer_c[7];
+    /* Epilogue fusion across the operator boundaries the reference's API exposes one by one (tensor-core path, fp16 /
+     * bf16, no peer copies; other launches answer TVK_ERR_UNSUPPORTED and the caller issues the separate operators).
+     * All NULL / 0 = plain behaviour.
+     *   c2      second output with C's strides: C then receives alpha*A@B + beta*bias WITHOUT the activation (what
+     *           backward needs) and c2 the activated value (what the next layer reads): addmm + gelu/relu
+     *           (src/api/ops/matmul.cpp:670-683 keeps only one of the two) in one pass over the accumulator.
+     *   aux     per-element operand of C's shape and dtype (row pitch aux_rs, batch pitch aux_bs, contiguous columns).
+     *           aux_op TVK_AUX_GELU_BACKWARD: C = v * gelu'(aux) (erf form, src/shaders/core/dtype.slang:739-744), i.e.
+     *           mm followed by gelu_backward with aux the saved pre-activation; TVK_AUX_RELU_BACKWARD: C = aux > 0 ? v : 0
+     *           (threshold_backward). Applied after alpha and bias, before the activation. */
+    void* c2;
+    const void* aux;
+    int64_t aux_rs, aux_bs;
+    int32_t aux_op;
+    int32_t reserved2_;
 } tvk_gemm_desc;
 
 /* Sharing a device buffer between the one-process-per-GPU ranks of a node (no counterpart in the reference).
@@ -238,6 +255,13 @@ TVK_API int tvk_gemm_workspace_size(const tvk_gemm_desc* d, uint64_t* bytes);
 TVK_API int tvk_gemm(const tvk_gemm_desc* d, void* workspace, uint64_t workspace_bytes, void* stream);
 /* Which path tvk_gemm would take: 1 = tcgen05 tensor-core kernel, 2 = CUDA-core kernel. */
 TVK_API int tvk_gemm_path(const tvk_gemm_desc* d, int* path);
+/* Tuning hook of the tensor-core path, process-wide (the counterpart of pinning an entry of the reference's autotune
+ * cache, src/vulkan/autotuner.cpp:123-178; used by sweeps and tests, not needed for normal use). 0 (stagger: -1) keeps
+ * the library's choice. bn: tile width 32/64/128/256; mt: 128-row tiles per CTA block (1, 2); splits: K slices;
+ * stagger: 0 = every block starts at k = 0, 1 = every column tile starts at its own k-block, n > 1 = tile tn starts at
+ * k-block (tn * n) mod count; group_m: tile rows per raster group; debug: timing probes (1: the epilogue stores
+ * nothing, 2: nothing is loaded or multiplied - results are then undefined). */
+TVK_API int tvk_debug_gemm_tuning(int bn, int mt, int splits, int stagger, int group_m, int debug);
 
 /* ------------------------------------------------------------------------- *
  * Elementwise maps.
@@ -433,7 +457,8 @@ TVK_API int tvk_embedding_backward(int dtype, void* grad_table, const void* grad
  * src/api/ops/attention.cpp:395-480, 641-749; src/shaders/ops/attention_coop.slang). fp16 / bf16.
  * q, out, dq, dout: contiguous [B, Hq, L, D]; k, v, dk, dv: contiguous [B, Hk, S, D]; Hq % Hk == 0 and
  * query head h reads key/value head h / (Hq/Hk). lse: fp32 [B, Hq, L]. causal != 0 masks key j of
- * query l when j > l + (S - L). A row with no visible key gives out = 0, lse = +inf, zero gradients.
+ * query l when j > l (top-left aligned when L != S, as src/api/ops/attention.cpp:107-112 and ATen's is_causal do).
+ * A row with no visible key (lse = +inf) gives out = 0 and zero gradients.
  * D and S must be multiples of 8. */
 TVK_API int tvk_attention_workspace_size(int dtype, int64_t B, int64_t Hq, int64_t Hk, int64_t L, int64_t S,
                                          int64_t D, int backward, uint64_t* bytes);

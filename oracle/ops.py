@@ -296,8 +296,9 @@ def conv2d_backward_weight(gy, x, w_shape, stride=1, padding=0):
 # ----------------------------------------------------------------------------- attention
 def attention_forward(q, k, v, causal=True, scale=None):
     """softmax(q k^T * scale + mask) v with grouped-query heads (kvh = h // (Hq/Hk)), float64.
-    Semantics of src/api/ops/attention.cpp:395-480 and attention_coop.slang:117-222: bottom-right
-    aligned causal mask, a row without a visible key gives out = 0 and lse = +inf.
+    Semantics of src/api/ops/attention.cpp:395-480 and attention_coop.slang:117-222: the causal mask hides
+    key > row (top-left aligned for L != S: src/api/ops/attention.cpp:107-112, attention_coop.slang:53-56, which
+    is also ATen's is_causal rule); a row without a visible key (only possible for S = 0) gives out = 0, lse = +inf.
     q: [B, Hq, L, D], k/v: [B, Hk, S, D]. Returns (out, lse, p)."""
     q, k, v = (np.asarray(t, np.float64) for t in (q, k, v))
     B, Hq, L, D = q.shape
@@ -307,7 +308,7 @@ def attention_forward(q, k, v, causal=True, scale=None):
     kk, vv = np.repeat(k, g, axis=1), np.repeat(v, g, axis=1)
     s = np.einsum("bhld,bhsd->bhls", q, kk) * scale
     if causal:
-        vis = np.arange(S)[None, :] <= (np.arange(L)[:, None] + (S - L))
+        vis = np.arange(S)[None, :] <= np.arange(L)[:, None]
         s = np.where(vis[None, None], s, -np.inf)
     m = s.max(axis=-1, keepdims=True)
     dead = ~np.isfinite(m)

@@ -35,11 +35,15 @@ def main():
         for chunks in ((1, 3) if mode == "pipelined" else (1,)):
             out = torch.full((args.batch, m, n), float("nan"), dtype=dtype, device=dev)
             op = ShardedBmm(out, mode=mode, chunks=chunks, compute=compute)
-            for _ in range(2):
-                op.run(a_mine, b_mine)
+            # two steps with different operands and a reader of the first result in between: the second step must
+            # not disturb what the reader sees, and must itself be complete on every rank
+            op.run(a_mine, b_mine)
+            seen = out.float().sum(dim=(1, 2))                       # consumer of step 1, same stream
+            op.run(a_mine, -b_mine)
             if gpu:
                 torch.cuda.synchronize()
-            assert torch.equal(out.float().cpu(), want), (mode, chunks, rank)
+            assert torch.equal(seen.cpu(), want.sum(dim=(1, 2))), (mode, chunks, rank, "first result")
+            assert torch.equal(out.float().cpu(), -want), (mode, chunks, rank)
             op.close()
     if gpu:
         from torchvulkan_b200 import cuda_ops

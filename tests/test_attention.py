@@ -24,10 +24,8 @@ def f64(t):
 
 
 @pytest.mark.parametrize("causal", [True, False])
-@pytest.mark.parametrize("Hq,Hk,L,S", [(4, 2, 16, 16), (8, 2, 12, 20), (2, 2, 7, 7)])
+@pytest.mark.parametrize("Hq,Hk,L,S", [(4, 2, 16, 16), (8, 2, 12, 20), (2, 2, 20, 12), (2, 2, 7, 7)])
 def test_oracle_matches_aten_sdpa(causal, Hq, Hk, L, S):
-    if causal and L != S:
-        pytest.skip("ATen's is_causal mask is top-left aligned; the two conventions agree only for L == S")
     q, k, v, do = _inputs(2, Hq, Hk, L, S, 8, torch.float64, 0)
     q.requires_grad_(); k.requires_grad_(); v.requires_grad_()
     ref = F.scaled_dot_product_attention(q, k, v, is_causal=causal, enable_gqa=True)
@@ -40,10 +38,15 @@ def test_oracle_matches_aten_sdpa(causal, Hq, Hk, L, S):
     np.testing.assert_allclose(dv, gv.numpy(), rtol=1e-9, atol=1e-11)
 
 
-def test_oracle_rows_without_visible_keys():
-    q, k, v, _ = _inputs(1, 2, 1, 6, 4, 8, torch.float64, 1)      # L > S: the first two query rows see nothing
-    out, lse, p = oracle.attention_forward(q.numpy(), k.numpy(), v.numpy(), True)
-    assert np.all(out[:, :, :2] == 0) and np.all(np.isinf(lse[:, :, :2])) and np.all(np.isfinite(lse[:, :, 2:]))
+def test_oracle_causal_mask_is_top_left_aligned():
+    # the reference hides key > row (src/api/ops/attention.cpp:107-112): with L != S query row 0 still sees exactly key 0
+    for L, S in ((6, 4), (4, 6)):
+        q, k, v, _ = _inputs(1, 2, 1, L, S, 8, torch.float64, 1)
+        out, lse, p = oracle.attention_forward(q.numpy(), k.numpy(), v.numpy(), True)
+        assert np.all(np.isfinite(lse))
+        assert np.all(p[:, :, 0, 1:] == 0) and np.allclose(p[:, :, 0, 0], 1.0)
+        vis = np.tril(np.ones((L, S), bool))
+        assert np.all(p[0, 0][~vis] == 0) and np.all(p[0, 0][vis] > 0)
 
 
 @pytest.mark.gpu
@@ -52,6 +55,7 @@ def test_oracle_rows_without_visible_keys():
                                                   (2, 2, 1, 72, 40, 64, True), (1, 8, 2, 264, 264, 128, True),
                                                   # head size 64, <= 256 keys, 128-row groups: the fused forward kernel
                                                   (1, 2, 1, 256, 128, 64, True), (2, 4, 2, 64, 200, 64, False), (1, 4, 1, 32, 8, 64, True),
+                                                  (2, 4, 2, 12, 24, 64, True), (2, 4, 2, 24, 16, 64, True), (1, 2, 2, 12, 24, 32, True), (1, 2, 2, 40, 24, 32, True),
                                                   # head size 64, keys a multiple of 128: the fused backward kernel (1 to 4 key blocks, tiles that
                                                   # straddle heads, L < S and L > S under a causal mask)
                                                   (1, 4, 2, 64, 384, 64, False), (2, 4, 2, 64, 384, 64, True), (1, 2, 2, 512, 512, 64, True),

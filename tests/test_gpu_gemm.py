@@ -182,6 +182,53 @@ def test_epilogue_bias_alpha_beta_activation(cuda, dtype, path):
             run_case(cuda, dtype, 160, 264, 192, False, True, path=path, bias=bias, alpha=0.5, beta=2.0, act=act, seed=30)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,n,k,ta,tb", [(256, 8192, 512, False, True), (160, 264, 192, False, True), (300, 200, 136, False, False),
+                                         (256, 1000, 320, True, False), (64, 72, 64, False, True)])
+def test_fused_epilogue_two_outputs_and_activation_gradient(cuda, dtype, m, n, k, ta, tb):
+    """The fused forms against the oracle's composition of the separate operators: (i) addmm with the pre-activation in
+    C and gelu / relu of it in c2; (ii) mm followed by gelu_backward / threshold_backward with the saved pre-activation
+    as the aux operand (src/shaders/core/dtype.slang:739-744). Same bars as the plain product."""
+    a, b = operand(m, k, dtype, 61, ta), operand(k, n, dtype, 62, tb)
+    bias = cpu_randn(n, dtype, 63)
+    adev = torch.empty_strided(a.shape, a.stride(), dtype=dtype, device=cuda).copy_(a)
+    bdev = torch.empty_strided(b.shape, b.stride(), dtype=dtype, device=cuda).copy_(b)
+    for act in ("gelu", "relu"):
+        z = torch.full((m, n), float("nan"), dtype=dtype, device=cuda)
+        h = torch.full((m, n), float("nan"), dtype=dtype, device=cuda)
+        ops().gemm(adev, bdev, bias=bias.to(cuda), alpha=0.25, beta=1.0, act=act, out=z, out2=h)
+        ops().check_device_status()
+        check(z, oracle.gemm(f64(a), f64(b), f64(bias), 0.25, 1.0, None), dtype)
+        check(h, oracle.gemm(f64(a), f64(b), f64(bias), 0.25, 1.0, act), dtype)
+        # c2 comes from the fp32 accumulator, not from the rounded value in C: it equals the one-output
+        # addmm-activation result of the same kernel bit for bit
+        h1 = ops().gemm(adev, bdev, bias=bias.to(cuda), alpha=0.25, beta=1.0, act=act, force_path=1)
+        assert torch.equal(h, h1)
+    x = cpu_randn((m, n), dtype, 64)                     # the saved pre-activation
+    for aux_op, back in (("gelu_backward", oracle.gelu_backward), ("relu_backward", lambda g, t: np.where(t > 0, g, 0.0))):
+        out = torch.full((m, n), float("nan"), dtype=dtype, device=cuda)
+        ops().gemm(adev, bdev, alpha=0.25, out=out, aux=x.to(cuda), aux_op=aux_op)
+        ops().check_device_status()
+        check(out, back(oracle.gemm(f64(a), f64(b), None, 0.25), f64(x)), dtype)
+    # a strided aux operand (a column slice of a wider buffer) and both fusions at once
+    wide = cpu_randn((m, n + 24), dtype, 65)
+    xs = wide.to(cuda)[:, 8:8 + n]
+    z = torch.full((m, n), float("nan"), dtype=dtype, device=cuda)
+    h = torch.full((m, n), float("nan"), dtype=dtype, device=cuda)
+    ops().gemm(adev, bdev, alpha=0.25, act="relu", out=z, out2=h, aux=xs, aux_op="gelu_backward")
+    ref = oracle.gelu_backward(oracle.gemm(f64(a), f64(b), None, 0.25), f64(wide[:, 8:8 + n]))
+    check(z, ref, dtype)
+    check(h, np.maximum(ref, 0.0), dtype)
+
+
+def test_fused_epilogue_is_refused_off_the_tensor_core_path(cuda):
+    from torchvulkan_b200.capi import TvkError
+    a, b = cpu_randn((64, 64), torch.float32, 1).to(cuda), cpu_randn((64, 64), torch.float32, 2).to(cuda)
+    out, out2 = torch.empty(64, 64, device=cuda), torch.empty(64, 64, device=cuda)
+    with pytest.raises(TvkError, match="NOT IMPLEMENTED"):
+        ops().gemm(a, b, out=out, out2=out2, act="relu")
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("path", [1, 2])
 def test_batched(cuda, dtype, path):

@@ -167,6 +167,22 @@ def test_nn_ops_forward_backward(vk):
     close(torch.bmm(torch.ones(3, 4, 5, device=vk), torch.ones(3, 5, 6, device=vk)), torch.full((3, 4, 6), 5.0), 0)
 
 
+@pytest.mark.parametrize("L,S", [(12, 24), (24, 16), (256, 128), (64, 384)])
+def test_sdpa_causal_with_unequal_lengths_matches_aten(vk, L, S):
+    """is_causal hides key > row whatever L and S are (src/api/ops/attention.cpp:107-112), which is ATen's rule too:
+    out and all three gradients against ATen CPU in fp32 on the same fp16-rounded inputs."""
+    torch.manual_seed(11)
+    q, k, v = torch.randn(2, 4, L, 64).half(), torch.randn(2, 2, S, 64).half(), torch.randn(2, 2, S, 64).half()
+    g = torch.randn(2, 4, L, 64).half()
+    dq, dk, dv = (t.to(vk).requires_grad_() for t in (q, k, v))
+    cq, ck, cv = (t.float().requires_grad_() for t in (q, k, v))
+    out = F.scaled_dot_product_attention(dq, dk, dv, is_causal=True, enable_gqa=True)
+    ref = F.scaled_dot_product_attention(cq, ck, cv, is_causal=True, enable_gqa=True)
+    out.backward(g.to(vk)); ref.backward(g.float())
+    close(out, ref, 1e-2)
+    close(dq.grad, cq.grad, 1e-2); close(dk.grad, ck.grad, 1e-2); close(dv.grad, cv.grad, 1e-2)
+
+
 def make_mlp(sizes):
     layers = []
     for i in range(len(sizes) - 1):

@@ -52,7 +52,12 @@ class GemmDesc(C.Structure):
                 ("c", C.c_void_p), ("c_rs", C.c_int64), ("c_bs", C.c_int64),
                 ("bias", C.c_void_p), ("bias_rs", C.c_int64), ("bias_cs", C.c_int64), ("bias_bs", C.c_int64),
                 ("alpha", C.c_float), ("beta", C.c_float), ("force_path", C.c_int32), ("c_f32", C.c_int32),
-                ("n_peer_c", C.c_int32), ("reserved_", C.c_int32), ("peer_c", C.c_void_p * 7)]
+                ("n_peer_c", C.c_int32), ("reserved_", C.c_int32), ("peer_c", C.c_void_p * 7),
+                ("c2", C.c_void_p), ("aux", C.c_void_p), ("aux_rs", C.c_int64), ("aux_bs", C.c_int64),
+                ("aux_op", C.c_int32), ("reserved2_", C.c_int32)]
+
+
+AUX_NONE, AUX_GELU_BACKWARD, AUX_RELU_BACKWARD = 0, 1, 2
 
 
 class MultiItem(C.Structure):
@@ -128,6 +133,7 @@ SIGNATURES = {
     "tvk_gemm_workspace_size": (_i, [_P(GemmDesc), _P(_u64)]),
     "tvk_gemm": (_i, [_P(GemmDesc), _p, _u64, _p]),
     "tvk_gemm_path": (_i, [_P(GemmDesc), _P(_i)]),
+    "tvk_debug_gemm_tuning": (_i, [_i, _i, _i, _i, _i, _i]),
     "tvk_unary": (_i, [_i, _i, _p, _p, _i64, _p]),
     "tvk_binary": (_i, [_i, _i, _p, _p, _p, _d, _d, _i64, _p]),
     "tvk_compare": (_i, [_i, _i, _p, _p, _p, _d, _i64, _p]),

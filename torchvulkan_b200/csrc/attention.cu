@@ -31,8 +31,9 @@ __global__ void __launch_bounds__(128) attn_softmax_kernel(T* __restrict__ P, fl
     __shared__ float smem[33];
     const int64_t row = blockIdx.x;
     const int64_t l = row % L;
-    // causal mask aligned to the bottom-right corner: key j is visible when j <= l + (S - L)
-    const int64_t limit = causal ? (l + (S - L) + 1) : S;
+    // causal mask aligned to the top-left corner (key j is visible when j <= l), as the reference masks key > row
+    // (src/api/ops/attention.cpp:107-112, src/shaders/ops/attention_coop.slang:53-56)
+    const int64_t limit = causal ? (l + 1) : S;
     const int64_t nvis = limit < 0 ? 0 : (limit > S ? S : limit);
     const float* s = scores + row * S;
     T* p = P + row * S;
@@ -96,7 +97,7 @@ __global__ void __launch_bounds__(128) attn_dsoftmax_kernel(T* __restrict__ P, T
                                                            float scale, int causal) {
     const int64_t row = blockIdx.x;
     const int64_t l = row % L;
-    const int64_t limit = causal ? (l + (S - L) + 1) : S;
+    const int64_t limit = causal ? (l + 1) : S;
     const int64_t nvis = limit < 0 ? 0 : (limit > S ? S : limit);
     const float ls = lse[row], dl = delta[row];
     const bool dead = !(ls < INFINITY);   // +inf (or NaN): the row attended to nothing
@@ -136,7 +137,7 @@ __global__ void __launch_bounds__(256) attn_softmax_warp_kernel(T* __restrict__ 
     const int64_t row = (int64_t)blockIdx.x * 8 + warp;
     if (row >= rows) return;
     const int64_t l = row % L;
-    const int64_t limit = causal ? (l + (S - L) + 1) : S;
+    const int64_t limit = causal ? (l + 1) : S;
     const int nvis = (int)(limit < 0 ? 0 : (limit > S ? S : limit));
     const float4* s4 = (const float4*)(scores + row * S);
     uint2* p2 = (uint2*)(P + row * S);
@@ -187,7 +188,7 @@ __global__ void __launch_bounds__(256) attn_dsoftmax_vec_kernel(T* __restrict__ 
         const int64_t row = i / nv;
         const int j0 = (int)(i - row * nv) * 4;
         const int64_t l = row % L;
-        const int64_t limit = causal ? (l + (S - L) + 1) : S;
+        const int64_t limit = causal ? (l + 1) : S;
         const int nvis = (int)(limit < 0 ? 0 : (limit > S ? S : limit));
         const float ls = lse[row], dl = delta[row];
         const bool dead = !(ls < INFINITY);

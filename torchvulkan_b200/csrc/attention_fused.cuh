@@ -6,7 +6,7 @@
 // (src/api/ops/attention.cpp:395-480, src/shaders/ops/attention_coop.slang:117-222), whose conventions are kept:
 // probabilities are rounded to the input dtype before they multiply V and the denominator sums the rounded values;
 // the log-sum-exp is fp32; a query row without a visible key gives out = 0 and lse = +inf; causal masks are aligned
-// to the bottom-right corner (key j is visible to query l when j <= l + S - L); all query heads of a KV group are
+// to the top-left corner (key j is visible to query l when j <= l, attention_coop.slang:53-56); all query heads of a KV group are
 // rows of one matrix (row = g*L + l).
 //
 // One CTA per 128 query rows of one (batch, kv head) group, 192 threads:
@@ -83,7 +83,7 @@ attn_fwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     int tile_keys = p.S;
     if (p.causal) {
         const int l_hi = (p.L % 128 == 0) ? (int)((tile * 128) % p.L) + 127 : p.L - 1;     // largest query index in the tile
-        const int lim = l_hi + (p.S - p.L) + 1;
+        const int lim = l_hi + 1;
         tile_keys = lim < 0 ? 0 : (lim > p.S ? p.S : lim);
     }
     const int nk = tile_keys <= 0 ? 64 : (tile_keys + 63) / 64 * 64;
@@ -128,7 +128,7 @@ attn_fwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         const int r = lane_window + lane;                                  // row of the tile
         const int64_t row = row0 + r;
         const int l = (int)(row % p.L);
-        const int limit = p.causal ? (l + (p.S - p.L) + 1) : p.S;
+        const int limit = p.causal ? (l + 1) : p.S;
         const int nvis = limit < 0 ? 0 : (limit > p.S ? p.S : limit);
         const uint32_t trow = tmem_base + ((uint32_t)lane_window << 16);
         bool ok = mbar_wait(bar_s, 0, abort_flag, p.status, 54);

@@ -4,7 +4,7 @@
 // Replaces, for these shapes, the five GEMMs and the dsoftmax kernel of attention.cu (which stay the path for every other
 // shape). Counterpart in the reference: sdpa_backward_vulkan (src/api/ops/attention.cpp:641-749), same conventions as the
 // forward: p = exp(s*scale - lse) (0 where masked or lse = +inf), P rounded to the input dtype before it multiplies dO,
-// dS = p * (dP - delta) * scale with delta = sum(dO * O), causal masks aligned to the bottom-right corner, all query heads
+// dS = p * (dP - delta) * scale with delta = sum(dO * O), causal masks aligned to the top-left corner (key j visible to query l when j <= l), all query heads
 // of a KV group are rows of one matrix (row = g*L + l).
 //
 // One CTA per (group, block of 128 keys), 576 threads; K_j and V_j stay in shared memory and the CTA walks the 128-row
@@ -54,7 +54,7 @@ struct BwdParams {
 __host__ __device__ inline bool tile_sees_block(int tile, int kb, int L, int S, int causal) {
     if (!causal) return true;
     const int l_hi = (L % 128 == 0) ? (tile * 128) % L + 127 : L - 1;
-    return kb * 128 <= l_hi + (S - L);
+    return kb * 128 <= l_hi;
 }
 
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -175,7 +175,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             if (!tile_sees_block(tile, kb, p.L, p.S, p.causal)) continue;
             const int64_t row = grow0 + (int64_t)tile * 128 + r;
             const int l = (int)((tile * 128 + r) % p.L);
-            const int limit = p.causal ? (l + (p.S - p.L) + 1) : p.S;      // keys [0, limit) are visible to this row
+            const int limit = p.causal ? (l + 1) : p.S;      // keys [0, limit) are visible to this row
             const int nvis = limit - key0 < 0 ? 0 : (limit - key0 > 128 ? 128 : limit - key0);   // visible keys of this block
             const float ls = p.lse[row], dl = p.delta[row];
             const bool dead = !(ls < INFINITY);                            // +inf (or NaN): the row attended to nothing

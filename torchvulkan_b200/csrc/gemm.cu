@@ -360,6 +360,13 @@ struct Params {
     int stage_ok;        // C (and every peer copy) is 16-byte aligned with 16-byte multiples as row and batch pitch
     int n_peers;         // further copies of C (same strides) in other devices' memory, written by the epilogue
     int tma_store;       // C is written by TMA stores of 32-row x 128-byte boxes staged in shared memory (tmap_c is valid)
+    int k_stagger;       // > 0: the block of column tile tn walks its k-blocks starting at (tn * k_stagger) % num_kb
+    int group_m;         // tile rows per raster group (tm runs fastest inside a group)
+    int debug;           // tuning probes: 1 = the epilogue stores nothing, 2 = nothing is loaded or multiplied, 4 = staged tiles are not stored
+    void* c2;            // second output with C's strides: C receives the value before the activation, c2 the activated one
+    const void* aux;     // per-element operand of C's shape and dtype for aux_op (row pitch aux_rs, batch pitch aux_bs)
+    int64_t aux_rs, aux_bs;
+    int aux_op;          // TVK_AUX_*: what the epilogue does with aux
     void* peer_c[7];
 };
 
@@ -395,12 +402,23 @@ template <int BN, int MT> struct GemmCfg {
     static constexpr int kSmemBytes = kStages * kStage + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
+// aux_op of the epilogue: v is the scaled (and biased) accumulator, x the element of the aux operand.
+__device__ __forceinline__ float aux_apply(float v, float x, int op) {
+    if (op == TVK_AUX_GELU_BACKWARD) {          // the same expression as the elementwise gelu_backward kernel
+        const float cdf = 0.5f * (1.0f + erff(x * 0.7071067811865476f));
+        const float pdf = expf(-0.5f * x * x) * 0.3989422804014327f;
+        return v * (cdf + x * pdf);
+    }
+    if (op == TVK_AUX_RELU_BACKWARD) return (x <= 0.f) ? 0.f : v;
+    return v;
+}
+
 // ES = operand element size in bytes (2: f16/bf16, 4: tf32). MT = 128-row tiles per CTA block (1 or 2).
 template <int BN, int ES, int MT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__ CUtensorMap tmap_a1,
             const __grid_constant__ CUtensorMap tmap_b0, const __grid_constant__ CUtensorMap tmap_b1,
-            const __grid_constant__ CUtensorMap tmap_c, const Params p) {
+            const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_c2, const Params p) {
     using Cfg = GemmCfg<BN, MT>;
     constexpr int BK = 128 / ES;         // elements of K per stage
     constexpr int CH = 128 / ES;         // elements of M/N per 128-byte row of an MN-major tile
@@ -440,6 +458,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b1) : "memory");
         }
         if (p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_c) : "memory");
+        if (p.tma_store && p.c2) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_c2) : "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)Cfg::kTmemCols) : "memory");
@@ -464,10 +483,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
     auto decode = [&](int64_t t, int& b, int& tm, int& tn) {
         b = (int)(t / tiles_per_batch);
         const int r = (int)(t - (int64_t)b * tiles_per_batch);
-        const int group = 8 * p.tiles_n;
+        const int group = p.group_m * p.tiles_n;
         const int g = r / group, rr = r - g * group;
-        const int first_m = g * 8;
-        const int gm = (p.tiles_m - first_m) < 8 ? (p.tiles_m - first_m) : 8;
+        const int first_m = g * p.group_m;
+        const int gm = (p.tiles_m - first_m) < p.group_m ? (p.tiles_m - first_m) : p.group_m;
         tm = first_m + rr % gm;
         tn = rr / gm;
     };
@@ -478,17 +497,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int64_t t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+            for (int64_t t = blockIdx.x; t < p.total_tiles && ok && !(p.debug & 2); t += gridDim.x) {
                 int b, tm, tn;
                 decode(t, b, tm, tn);
                 const int ab = p.a_batched ? b : 0, bb = p.b_batched ? b : 0;
+                // Blocks that run at the same time would otherwise all read the same 128-byte column strip of their
+                // operand rows (and the very same lines of the shared operand) at the same moment; starting each column
+                // tile at its own k-block spreads those reads over all of the operands' columns. The sum over k is the
+                // same set of terms in a rotated order.
+                const int koff = p.k_stagger > 0 ? (int)(((int64_t)tn * p.k_stagger + b) % p.num_kb) : 0;
                 for (int kb0 = 0; kb0 < p.num_kb && ok; kb0 += ckb) {
                     const int kb1 = (kb0 + ckb) < p.num_kb ? (kb0 + ckb) : p.num_kb;
                     for (int pi = 0; pi < p.passes && ok; ++pi) {
                         const int pass = pass_of(pi);
                         const void* ta = (pass == 1) ? (const void*)&tmap_a1 : (const void*)&tmap_a0;
                         const void* tb = (pass == 2) ? (const void*)&tmap_b1 : (const void*)&tmap_b0;
-                        for (int kb = kb0; kb < kb1; ++kb) {
+                        for (int kbi = kb0; kbi < kb1; ++kbi) {
+                            const int kb = (kbi + koff >= p.num_kb) ? (kbi + koff - p.num_kb) : (kbi + koff);
                             ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.status, 1);
                             if (!ok) break;
                             const uint32_t sa = smem_u32(smem + stage * Cfg::kStage);
@@ -545,7 +570,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
                     tc_fence_after();
                     const uint32_t tmem_c = tmem_base + (uint32_t)(acc * MT * BN);
                     uint32_t accumulate = 0;
-                    for (int pi = 0; pi < p.passes && ok; ++pi) {
+                    for (int pi = 0; pi < p.passes && ok && !(p.debug & 2); ++pi) {
                         for (int kb = kb0; kb < kb1; ++kb) {
                             ok = mbar_wait(full0 + 8 * stage, phase, abort_flag, p.status, 4);
                             if (!ok) break;
@@ -604,8 +629,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
             const int bes = p.out_dtype == TVK_F32 ? 4 : 2;
             if (p.bias) brow = (const uint8_t*)p.bias + ((int64_t)b * p.bias_bs + row * p.bias_rs) * bes;
 
-            // scale, bias and activation of 32 consecutive columns of this thread's row
-            auto finish = [&](int c0, float* v) {
+            const uint8_t* arow = nullptr;
+            if (p.aux_op) arow = (const uint8_t*)p.aux + ((int64_t)b * p.aux_bs + row * p.aux_rs) * 2;
+            // scale, bias, the aux operation and (with_act) the activation of 32 consecutive columns of this thread's row
+            auto finish = [&](int c0, float* v, bool with_act) {
                 if (!row_ok) return;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = p.alpha * v[j];
@@ -624,20 +651,48 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
                         }
                     }
                 }
-                if (p.act != TVK_ACT_NONE) {
+                if (arow) {
+                    // the incoming gradient times the derivative of the activation at the saved pre-activation (aux)
+                    uint32_t a2[16];
+                    const uint16_t* ap = (const uint16_t*)arow + cbase;
+                    if (ncols == 32 && ((uintptr_t)ap & 15) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint4 q = __ldg((const uint4*)ap + j);
+                            a2[4 * j] = q.x; a2[4 * j + 1] = q.y; a2[4 * j + 2] = q.z; a2[4 * j + 3] = q.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const uint32_t lo = (2 * j < ncols) ? ap[2 * j] : 0u, hi = (2 * j + 1 < ncols) ? ap[2 * j + 1] : 0u;
+                            a2[j] = lo | (hi << 16);
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        float x0, x1;
+                        if (p.out_dtype == TVK_F16) { const float2 f = __half22float2(*(const __half2*)&a2[j]); x0 = f.x; x1 = f.y; }
+                        else { const float2 f = __bfloat1622float2(*(const __nv_bfloat162*)&a2[j]); x0 = f.x; x1 = f.y; }
+                        v[2 * j] = aux_apply(v[2 * j], x0, p.aux_op);
+                        v[2 * j + 1] = aux_apply(v[2 * j + 1], x1, p.aux_op);
+                    }
+                }
+                if (with_act && p.act != TVK_ACT_NONE) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = simt::apply_act(v[j], p.act);
                 }
             };
             // conversion and store of those columns straight from this thread's registers (any n, any alignment)
-            auto store_direct = [&](int c0, const float* v) {
+            auto store_direct = [&](int c0, const float* v, int which) {
                 if (!row_ok) return;
+                uint8_t* crow_w = which ? (uint8_t*)p.c2 + coff : crow;
+                const int n_peers_w = which ? 0 : p.n_peers;
                 const int64_t cbase = col0 + c0;
                 const int ncols = (p.n - cbase) < 32 ? (int)(p.n - cbase) : 32;
                 if (p.out_dtype == TVK_F32) {
                     // q == -1 is this device's C; q >= 0 pushes the same values into a peer's copy over NVLink
-                    for (int q = -1; q < p.n_peers; ++q) {
-                        float* dst = (float*)(q < 0 ? crow : (uint8_t*)p.peer_c[q] + coff) + cbase;
+                    for (int q = -1; q < n_peers_w; ++q) {
+                        float* dst = (float*)(q < 0 ? crow_w : (uint8_t*)p.peer_c[q] + coff) + cbase;
                         if (ncols == 32 && ((uintptr_t)dst & 15) == 0) {
 #pragma unroll
                             for (int j = 0; j < 32; j += 4) *(float4*)(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
@@ -658,8 +713,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
                             packed[j] = *(uint32_t*)&h;
                         }
                     }
-                    for (int q = -1; q < p.n_peers; ++q) {
-                        uint16_t* dst = (uint16_t*)(q < 0 ? crow : (uint8_t*)p.peer_c[q] + coff) + cbase;
+                    for (int q = -1; q < n_peers_w; ++q) {
+                        uint16_t* dst = (uint16_t*)(q < 0 ? crow_w : (uint8_t*)p.peer_c[q] + coff) + cbase;
                         if (ncols == 32 && ((uintptr_t)dst & 15) == 0) {
 #pragma unroll
                             for (int j = 0; j < 16; j += 4) *(uint4*)(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
@@ -701,17 +756,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
                 if (!ok) break;
 #pragma unroll
                 for (int c0 = 0; c0 < BN; c0 += 32) {
-                    if (col0 + c0 < p.n) { finish(c0, &sum[c0]); store_direct(c0, &sum[c0]); }
+                    if (col0 + c0 < p.n) { finish(c0, &sum[c0], true); store_direct(c0, &sum[c0], 0); }
                 }
             } else {
                 const int gcols = p.out_dtype == TVK_F32 ? 32 : 64;      // columns of C in 128 bytes
                 const bool staged = (p.tma_store || p.stage_ok) && BN % gcols == 0;
                 // 32 finished columns of this thread's row, starting at column c0 of the tile, on their way to C
-                auto emit = [&](int c0, float* v) {
+                auto emit = [&](int c0, float* v, int which) {
                     const int g0 = c0 / gcols * gcols;
                     // Groups of 128 bytes per row go through this warp's staging rows and leave as one TMA store (which clips
                     // rows >= m and columns >= n) or, towards peers, as whole 128-byte lines (whole groups only).
-                    if (!staged || (!p.tma_store && col0 + g0 + gcols > p.n)) { store_direct(c0, v); return; }
+                    if (!staged || (!p.tma_store && col0 + g0 + gcols > p.n)) { store_direct(c0, v, which); return; }
                     if (c0 == g0 && p.tma_store) {
                         // the previous store of this warp must have finished reading the buffer
                         if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
@@ -737,10 +792,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
                     }
                     if (!(c0 + 32 == g0 + gcols || (p.tma_store && col0 + c0 + 32 >= p.n))) return;
                     if (p.tma_store) {
+                        if (p.debug & 4) return;                     // probe: staged, never stored
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                         __syncwarp();
                         if (lane == 0 && tile_row0 + lane_window < p.m) {
-                            tma_store_3d(&tmap_c, smem_u32(buf), (int)(col0 + g0), (int)(tile_row0 + lane_window), b);
+                            tma_store_3d(which ? &tmap_c2 : &tmap_c, smem_u32(buf), (int)(col0 + g0), (int)(tile_row0 + lane_window), b);
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
                         return;
@@ -757,8 +813,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
                     const int64_t off0 = ((int64_t)b * p.c_bs + row0 * p.c_rs + col0 + g0) * es_out + (lane & 7) * 16;
                     const int64_t row_bytes = p.c_rs * es_out;
                     // q == -1 is this device's C; q >= 0 pushes the same lines into a peer's copy over NVLink
-                    for (int q = -1; q < p.n_peers; ++q) {
-                        uint8_t* base = (q < 0 ? (uint8_t*)p.c : (uint8_t*)p.peer_c[q]) + off0;
+                    for (int q = -1; q < (which ? 0 : p.n_peers); ++q) {
+                        uint8_t* base = (q < 0 ? (uint8_t*)(which ? p.c2 : p.c) : (uint8_t*)p.peer_c[q]) + off0;
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const int rr = 4 * i + (lane >> 3);
@@ -771,6 +827,37 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
                 // rest). Load, wait, finish, store one chunk at a time: keeping the next chunk's tensor-memory load in flight
                 // under the stores measured slower (weight-gradient shape 55 -> 65 us).
                 const uint32_t tacc = tmem_base + ((uint32_t)lane_window << 16) + (uint32_t)((acc * MT + mt) * BN);
+                // With a second output the accumulator is read twice: first for C (no activation), then for c2 (activated).
+                const int n_out = p.c2 ? 2 : 1;
+#pragma unroll 1
+                for (int which = 0; which < n_out; ++which) {
+                if (p.debug & 8) {
+                    // a whole 128-byte column group per step: both tensor-memory loads in flight before the one wait
+#pragma unroll 1
+                    for (int g0c = 0; g0c < BN; g0c += 64) {
+                        if (col0 + g0c >= p.n) break;
+                        if (((g0c / gcols) & 1) != half && gcols == 64) continue;
+                        if (gcols == 32 && ((((g0c) / 32) & 1) != half) && ((((g0c + 32) / 32) & 1) != half)) continue;
+                        uint32_t r0[32], r1[32];
+                        const bool second = (g0c + 32 < BN) && (col0 + g0c + 32 < p.n);
+                        tmem_ld32(tacc + (uint32_t)g0c, r0);
+                        if (second) tmem_ld32(tacc + (uint32_t)(g0c + 32), r1);
+                        tmem_ld_wait();
+                        float v[32];
+                        if (gcols == 64 || ((g0c / 32) & 1) == half) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r0[j]);
+                            finish(g0c, v, which == n_out - 1);
+                            if (!(p.debug & 1)) emit(g0c, v, which);
+                        }
+                        if (second && (gcols == 64 || (((g0c + 32) / 32) & 1) == half)) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r1[j]);
+                            finish(g0c + 32, v, which == n_out - 1);
+                            if (!(p.debug & 1)) emit(g0c + 32, v, which);
+                        }
+                    }
+                } else {
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 32) {
                     if (col0 + c0 >= p.n) break;                   // uniform across the warp
@@ -781,10 +868,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                    finish(c0, v);
-                    emit(c0, v);
+                    finish(c0, v, which == n_out - 1);
+                    if (!(p.debug & 1)) emit(c0, v, which);
                 }
-            }
+                }
+                }
             }   // mt
             if constexpr (!kChunked) {
                 tc_fence_before();
@@ -1012,7 +1100,7 @@ static int launch(const CUtensorMap* maps, const Params& p, cudaStream_t s) {
         attr_set[dev] = true;
     }
     int64_t grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
-    gemm_kernel<BN, ES, MT><<<(unsigned)grid, kGemmThreads, Cfg::kSmemBytes + kGemmStagingBytes, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
+    gemm_kernel<BN, ES, MT><<<(unsigned)grid, kGemmThreads, Cfg::kSmemBytes + kGemmStagingBytes, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p);
     return launch_status("tcgen05 gemm");
 }
 
@@ -1021,6 +1109,16 @@ static int launch(const CUtensorMap* maps, const Params& p, cudaStream_t s) {
 // =====================================================================================
 // dispatch
 // =====================================================================================
+// Tuning overrides set through tvk_debug_gemm_tuning (0 / -1 = the library's own choice). They stand where the
+// reference pins an entry of its autotune cache (src/vulkan/autotuner.cpp:123-178): a sweep sets them, measures, and
+// the winners become the rules of pick_block / tc_splitk_plan below.
+struct GemmTuning {
+    int bn = 0, mt = 0, splits = 0, stagger = -1, group_m = 0, debug = 0;
+};
+static GemmTuning g_tune;
+
+static bool fused_epilogue(const tvk_gemm_desc* d) { return d->c2 != nullptr || d->aux_op != TVK_AUX_NONE; }
+
 static int validate(const tvk_gemm_desc* d) {
     if (!d) return set_error(TVK_ERR_INVALID, "tvk_gemm: null descriptor");
     TVK_REQUIRE(d->dtype == TVK_F32 || d->dtype == TVK_F16 || d->dtype == TVK_BF16,
@@ -1033,6 +1131,13 @@ static int validate(const tvk_gemm_desc* d) {
     TVK_REQUIRE(d->c_rs >= d->n, "tvk_gemm: output row pitch %lld smaller than n %lld", (long long)d->c_rs, (long long)d->n);
     TVK_REQUIRE(d->n_peer_c >= 0 && d->n_peer_c <= 7, "tvk_gemm: n_peer_c %d outside [0, 7]", d->n_peer_c);
     for (int q = 0; q < d->n_peer_c; ++q) TVK_REQUIRE(d->peer_c[q], "tvk_gemm: peer_c[%d] is null", q);
+    TVK_REQUIRE(d->aux_op >= TVK_AUX_NONE && d->aux_op <= TVK_AUX_RELU_BACKWARD, "tvk_gemm: unknown aux_op %d", d->aux_op);
+    TVK_REQUIRE(d->aux_op == TVK_AUX_NONE || d->aux, "tvk_gemm: aux_op %d without an aux operand", d->aux_op);
+    if (fused_epilogue(d)) {
+        if (d->dtype == TVK_F32 || d->c_f32 || d->n_peer_c > 0)
+            return set_error(TVK_ERR_UNSUPPORTED, "torchvulkan [NOT IMPLEMENTED]: fused epilogue (c2 / aux) with fp32 data or peer copies");
+        TVK_REQUIRE(d->aux_op == TVK_AUX_NONE || d->aux_rs >= d->n, "tvk_gemm: aux row pitch %lld smaller than n %lld", (long long)d->aux_rs, (long long)d->n);
+    }
     return TVK_OK;
 }
 
@@ -1091,6 +1196,11 @@ static Repack plan_repack(const tvk_gemm_desc* d) {
 static int choose_path(const tvk_gemm_desc* d) {
     if (d->c_f32 && d->dtype != TVK_F32) return tc_eligible(d) ? 1 : 0;   // mixed output exists on the tensor-core path only
     if (d->n_peer_c > 0) return tc_eligible(d) ? 1 : 0;                   // so do the pushed peer copies
+    if (fused_epilogue(d)) {                                              // and the fused epilogues
+        if (tc_eligible(d)) return 1;
+        const Repack r = plan_repack(d);
+        return (r.a || r.b) ? 1 : 0;
+    }
     if (d->force_path == 2) return 2;
     const bool ok = tc_eligible(d);
     if (d->force_path == 1) return ok ? 1 : 0;
@@ -1180,6 +1290,7 @@ static int run_simt(const tvk_gemm_desc* d, void* ws, uint64_t ws_bytes, cudaStr
 // outputs one tile tall, else the tuning override TORCHVULKAN_GEMM_MT, else 0 = undecided.
 static int pick_mt(const tvk_gemm_desc* d) {
     if (d->dtype == TVK_F32 || d->m <= tc::BM) return 1;
+    if (g_tune.mt == 1 || g_tune.mt == 2) return g_tune.mt;
     const char* e = getenv("TORCHVULKAN_GEMM_MT");   // read per call so that a test can switch it
     const int v = e ? atoi(e) : 0;
     return (v == 1 || v == 2) ? v : 0;   // 0: let the cost model decide
@@ -1238,7 +1349,7 @@ static int run_tc(const tvk_gemm_desc* d, void* ws, uint64_t ws_bytes, cudaStrea
         bn = tc::pick_bn(d->batch, d->m, d->n, 32, 64, 1);
     } else {
         const char* e = getenv("TORCHVULKAN_GEMM_BN");
-        const int v = e ? atoi(e) : 0;
+        const int v = g_tune.bn ? g_tune.bn : (e ? atoi(e) : 0);
         const int forced_bn = (v == 32 || v == 64 || v == 128 || v == 256) ? v : 0;
         const int min_bn = b_mn ? 128 / es : 32;
         const int lo = forced_bn >= min_bn ? forced_bn : min_bn, hi = forced_bn >= min_bn ? forced_bn : 256;
@@ -1254,6 +1365,8 @@ static int run_tc(const tvk_gemm_desc* d, void* ws, uint64_t ws_bytes, cudaStrea
     p.status = device_status_word();
     p.n_peers = d->n_peer_c;
     for (int q = 0; q < d->n_peer_c; ++q) p.peer_c[q] = d->peer_c[q];
+    p.c2 = d->c2;
+    p.aux = d->aux_op ? d->aux : nullptr; p.aux_rs = d->aux_rs; p.aux_bs = d->aux_bs; p.aux_op = d->aux_op;
     {
         const int64_t es_out = p.out_dtype == TVK_F32 ? 4 : 2;
         bool aligned = ((uintptr_t)d->c & 15) == 0 && (d->c_rs * es_out) % 16 == 0 && (d->c_bs * es_out) % 16 == 0;
@@ -1263,6 +1376,15 @@ static int run_tc(const tvk_gemm_desc* d, void* ws, uint64_t ws_bytes, cudaStrea
         static const bool always = getenv("TORCHVULKAN_GEMM_STAGE_ALWAYS") != nullptr;
         p.stage_ok = (aligned && (d->n_peer_c > 0 || always)) ? 1 : 0;
     }
+    p.group_m = g_tune.group_m > 0 ? g_tune.group_m : 8;
+    p.debug = g_tune.debug;
+    p.k_stagger = 0;
+    if (!f32 && p.num_kb > 1) {
+        const int auto_stagger = 0;
+        const int st = g_tune.stagger >= 0 ? g_tune.stagger : auto_stagger;
+        // st == 1 asks for the spread that gives every column tile its own start: num_kb / tiles_n, at least 1
+        p.k_stagger = st == 1 ? (p.num_kb / p.tiles_n > 1 ? p.num_kb / p.tiles_n : 1) : st;
+    }
     p.a_mn = a_mn; p.b_mn = b_mn;
     p.a_batched = d->batch > 1 && a_bs != 0;
     p.b_batched = d->batch > 1 && b_bs != 0;
@@ -1271,7 +1393,7 @@ static int run_tc(const tvk_gemm_desc* d, void* ws, uint64_t ws_bytes, cudaStrea
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) | ((uint32_t)(bn >> 3) << 17) |
               ((uint32_t)(tc::BM >> 4) << 24);
 
-    CUtensorMap maps[5] = {};
+    CUtensorMap maps[6] = {};
     const int ch = 128 / es;
     for (int i = 0; i < 2; ++i) {
         int rc;
@@ -1291,8 +1413,11 @@ static int run_tc(const tvk_gemm_desc* d, void* ws, uint64_t ws_bytes, cudaStrea
         const bool aligned = ((uintptr_t)d->c & 15) == 0 && (d->c_rs * es_out) % 16 == 0 && (d->batch <= 1 || (d->c_bs * es_out) % 16 == 0) &&
                              d->c_rs * es_out < ((int64_t)1 << 40);
         p.tma_store = (!off && !f32 && d->n_peer_c == 0 && aligned && bn % gcols == 0) ? 1 : 0;
+        if (p.tma_store && p.c2 && ((uintptr_t)p.c2 & 15) != 0) p.tma_store = 0;
         if (p.tma_store) {
             int rc = tc::encode_operand(&maps[4], p.out_dtype, d->c, d->n, d->m, d->c_rs, d->batch, d->batch > 1 ? d->c_bs : 0, gcols, 32);
+            if (rc) return rc;
+            if (p.c2) rc = tc::encode_operand(&maps[5], p.out_dtype, p.c2, d->n, d->m, d->c_rs, d->batch, d->batch > 1 ? d->c_bs : 0, gcols, 32);
             if (rc) return rc;
         }
     }
@@ -1317,11 +1442,12 @@ static int run_tc(const tvk_gemm_desc* d, void* ws, uint64_t ws_bytes, cudaStrea
 // partials are summed with the epilogue by simt::splitk_epilogue_kernel.
 static int tc_splitk_plan(const tvk_gemm_desc* d) {
     static const bool off = getenv("TORCHVULKAN_GEMM_NO_SPLITK") != nullptr;
-    if (off || d->dtype == TVK_F32 || d->c_f32 || d->n_peer_c > 0 || d->batch != 1 || d->k < 2048 || d->k % 64 != 0) return 1;
+    if (off || d->dtype == TVK_F32 || d->c_f32 || d->n_peer_c > 0 || fused_epilogue(d) || d->batch != 1 || d->k < 2048 || d->k % 64 != 0) return 1;
     static const int forced = [] {
         const char* e = getenv("TORCHVULKAN_GEMM_SPLITS");
         return e ? atoi(e) : 0;
     }();
+    if (g_tune.splits >= 1 && g_tune.splits <= 64 && (d->k / 64) % g_tune.splits == 0) return g_tune.splits;
     if (forced >= 1 && forced <= 64 && (d->k / 64) % forced == 0) return forced;
     const int64_t tiles = ((d->m + tc::BM - 1) / tc::BM) * ((d->n + 127) / 128);
     if (tiles >= 100) return 1;
@@ -1395,6 +1521,11 @@ static int run_repack(const tvk_gemm_desc* d, const Repack& r, void* base, cudaS
 using namespace tvk;
 
 extern "C" {
+
+int tvk_debug_gemm_tuning(int bn, int mt, int splits, int stagger, int group_m, int debug) {
+    g_tune.bn = bn; g_tune.mt = mt; g_tune.splits = splits; g_tune.stagger = stagger; g_tune.group_m = group_m; g_tune.debug = debug;
+    return TVK_OK;
+}
 
 int tvk_gemm_path(const tvk_gemm_desc* d, int* path) {
     int rc = validate(d);

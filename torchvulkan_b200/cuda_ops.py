@@ -52,8 +52,13 @@ def check_device_status(device: int = 0) -> None:
 
 
 # ------------------------------------------------------------------------------- contraction
-def gemm_desc(a, b, out, bias=None, alpha=1.0, beta=1.0, act=None, force_path=0) -> capi.GemmDesc:
-    """a: [B?, m, k], b: [B?, k, n] (any strides), out: [B?, m, n] with contiguous rows."""
+AUX = {None: capi.AUX_NONE, "gelu_backward": capi.AUX_GELU_BACKWARD, "relu_backward": capi.AUX_RELU_BACKWARD}
+
+
+def gemm_desc(a, b, out, bias=None, alpha=1.0, beta=1.0, act=None, force_path=0, out2=None, aux=None, aux_op=None) -> capi.GemmDesc:
+    """a: [B?, m, k], b: [B?, k, n] (any strides), out: [B?, m, n] with contiguous rows.
+    out2 (same shape and strides as out): out then receives the value before the activation and out2 the activated one.
+    aux + aux_op ("gelu_backward" / "relu_backward"): out = (alpha * a @ b + beta * bias) * act'(aux), aux of out's shape."""
     a3 = a if a.dim() == 3 else a.unsqueeze(0)
     b3 = b if b.dim() == 3 else b.unsqueeze(0)
     o3 = out if out.dim() == 3 else out.unsqueeze(0)
@@ -71,16 +76,23 @@ def gemm_desc(a, b, out, bias=None, alpha=1.0, beta=1.0, act=None, force_path=0)
         bb = bias.expand(batch, m, n) if bias.dim() == 3 else bias.expand(m, n).unsqueeze(0).expand(batch, m, n)
         d.bias, d.bias_rs, d.bias_cs, d.bias_bs = bias.data_ptr(), bb.stride(1), bb.stride(2), bb.stride(0)
     d.alpha, d.beta, d.force_path = alpha, beta, force_path
+    if out2 is not None:
+        assert out2.shape == out.shape and out2.stride() == out.stride() and out2.dtype == out.dtype
+        d.c2 = out2.data_ptr()
+    if aux_op is not None:
+        x3 = aux if aux.dim() == 3 else aux.unsqueeze(0)
+        assert tuple(x3.shape) == (batch, m, n) and (n <= 1 or x3.stride(2) == 1) and aux.dtype == out.dtype
+        d.aux, d.aux_rs, d.aux_bs, d.aux_op = x3.data_ptr(), (x3.stride(1) if m > 1 else n), (x3.stride(0) if batch > 1 else 0), AUX[aux_op]
     return d
 
 
-def gemm(a, b, bias=None, alpha=1.0, beta=1.0, act=None, out=None, force_path=0):
+def gemm(a, b, bias=None, alpha=1.0, beta=1.0, act=None, out=None, force_path=0, out2=None, aux=None, aux_op=None):
     batch = max(a.shape[0] if a.dim() == 3 else 1, b.shape[0] if b.dim() == 3 else 1)
     m, n = a.shape[-2], b.shape[-1]
     if out is None:
         shape = (batch, m, n) if (a.dim() == 3 or b.dim() == 3) else (m, n)
         out = torch.empty(shape, dtype=a.dtype, device=a.device)
-    d = gemm_desc(a, b, out, bias, alpha, beta, act, force_path)
+    d = gemm_desc(a, b, out, bias, alpha, beta, act, force_path, out2, aux, aux_op)
     nbytes = C.c_uint64(0)
     capi.call("tvk_gemm_workspace_size", C.byref(d), C.byref(nbytes))
     ws = _ws(nbytes.value, a.device)

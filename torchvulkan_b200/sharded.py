@@ -74,7 +74,9 @@ class ShardedBmm:
     """out_full[b] = a[b] @ b[b] for all `batch` batches, with a_shard/b_shard holding this rank's batches.
 
     out_full is a [batch, m, n] tensor every rank allocates; after `run()` returns and the stream is synchronised
-    every rank's out_full holds the complete product.
+    every rank's out_full holds the complete product. Work that reads out_full must be issued on the same stream
+    before the next `run()`: in "push" mode that next call begins with a rendezvous of all ranks on that stream, so no
+    peer overwrites the buffer while a reader of the previous result is still running.
     """
 
     def __init__(self, out_full: torch.Tensor, mode: str = "push", group=None, chunks: int = 4, compute=None):
@@ -144,6 +146,10 @@ class ShardedBmm:
                 self._gemm(a_shard, b_shard, self.mine)
             return self.out
         if self.mode == "push":
+            # Peers store into this rank's out_full: no rank may start writing step k+1 while another rank's kernels
+            # still read step k's result. The same 4-byte all-reduce, ordered on each rank's stream after whatever
+            # consumed out_full there, holds every rank's GEMM back until all ranks have reached this point.
+            dist.all_reduce(self._flag, group=self.group)
             if nb:
                 esz = self.out.element_size()
                 off = self.lo * self.out.stride(0) * esz

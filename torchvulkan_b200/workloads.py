@@ -20,7 +20,7 @@ from . import cuda_ops as ops
 
 class MLPStep:
     def __init__(self, sizes=(784, 8192, 8192, 10), batch=256, dtype=torch.float16, device="cuda", seed=0,
-                 lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, params=None, list_optimizer=False):
+                 lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, params=None, list_optimizer=False, loss_scale=1.0, fused=False):
         self.sizes, self.batch, self.dtype, self.device = tuple(sizes), batch, dtype, torch.device(device)
         self.lr, self.betas, self.eps, self.wd = lr, betas, eps, weight_decay
         self.nl = len(sizes) - 1
@@ -47,6 +47,10 @@ class MLPStep:
         # list_optimizer: one tvk_adam_step_multi launch for all parameters, step count in device memory (as
         # torch.optim keeps it for fused optimizers) and advanced on the device: the step is then replayable
         self.list_optimizer = list_optimizer
+        # fused: the activation is written by the addmm epilogue next to the pre-activation (two outputs of one pass over
+        # the accumulator) and gelu_backward is applied by the epilogue of the input-gradient product (the saved
+        # pre-activation is its aux operand): four launches and four passes over 256 x 8192 tensors fewer per hidden layer pair
+        self.fused = fused
         self.step_dev = torch.zeros((), dtype=torch.float32, device=dev)
         self._adam_items = (capi.MultiItem * len(self.params))()
         for i, (p, g, m, v) in enumerate(zip(self.params, self.grads, self.m, self.v)):
@@ -65,7 +69,10 @@ class MLPStep:
         self.glogp = e(batch, sizes[-1])
         self.loss = e(())
         self.total_w = e(())
-        self.one = torch.ones((), dtype=dtype, device=dev)
+        # gradient of the (scaled) loss with respect to the mean loss: backward runs on loss * loss_scale. fp16 moments of
+        # unscaled gradients underflow; with eps scaled by the same factor the AdamW update is the unscaled one exactly.
+        self.loss_scale = float(loss_scale)
+        self.one = torch.full((), self.loss_scale, dtype=dtype, device=dev)
         self.launches_per_step = 0
         self._descs, self._desc_key = None, None
         self.trace = None   # list of (tag, start_event, end_event) when per-launch timing is on
@@ -77,14 +84,32 @@ class MLPStep:
         """All GEMMs of one step as (desc, tag); built per call because x may move."""
         d = []
         inp = x
+
+        def supported(desc):
+            # a fused form the library cannot run (an operand the tensor-core path cannot address) answers an error
+            # here; that product is then issued as the separate operators
+            p = C.c_int(0)
+            return capi.lib().tvk_gemm_path(C.byref(desc), C.byref(p)) == 0
+
+        self._fused_fwd, self._fused_bwd = [False] * self.nl, [False] * self.nl
         for i in range(self.nl):
-            d.append(ops.gemm_desc(inp, self.w[i].t(), self.z[i], bias=self.b[i]))       # addmm
+            plain = ops.gemm_desc(inp, self.w[i].t(), self.z[i], bias=self.b[i])        # addmm
+            if self.fused and i < self.nl - 1:
+                both = ops.gemm_desc(inp, self.w[i].t(), self.z[i], bias=self.b[i], act="gelu", out2=self.h[i])       # addmm + gelu
+                self._fused_fwd[i] = supported(both)
+                plain = both if self._fused_fwd[i] else plain
+            d.append(plain)
             inp = self.h[i] if i < self.nl - 1 else None
         for i in reversed(range(self.nl)):
             act_in = x if i == 0 else self.h[i - 1]
             d.append(ops.gemm_desc(self.gz[i].t(), act_in, self.gw[i]))                  # wgrad = gz^T @ in
             if i > 0:
-                d.append(ops.gemm_desc(self.gz[i], self.w[i], self.gh[i - 1]))           # dgrad = gz @ W
+                plain = ops.gemm_desc(self.gz[i], self.w[i], self.gh[i - 1])             # dgrad = gz @ W
+                if self.fused:
+                    both = ops.gemm_desc(self.gz[i], self.w[i], self.gz[i - 1], aux=self.z[i - 1], aux_op="gelu_backward")   # mm + gelu_backward
+                    self._fused_bwd[i] = supported(both)
+                    plain = both if self._fused_bwd[i] else plain
+                d.append(plain)
         return d
 
     def _workspace_bytes(self):
@@ -131,7 +156,7 @@ class MLPStep:
         k = 0
         for i in range(s.nl):
             s._gemm(descs[k]); k += 1
-            if i < s.nl - 1:
+            if i < s.nl - 1 and not s._fused_fwd[i]:
                 s._call("tvk_unary", capi.U_GELU, dtc, s.h[i].data_ptr(), s.z[i].data_ptr(), s.z[i].numel())
         n, c = s.batch, s.sizes[-1]
         s._call("tvk_softmax_forward", 1, dtc, dtc, s.logp.data_ptr(), s.z[-1].data_ptr(), n, c)
@@ -143,7 +168,9 @@ class MLPStep:
             s._call("tvk_reduce", capi.R_SUM, dtc, dtc, s.gb[i].data_ptr(), s.gz[i].data_ptr(), 1, n, s.sizes[i + 1],
                     s._ws.data_ptr(), s._ws.numel(), tag=f"sum.dim0 {n}x{s.sizes[i + 1]}")  # grad b_i
             if i > 0:
-                s._gemm(descs[k]); k += 1                                                # grad h_{i-1}
+                s._gemm(descs[k]); k += 1                                                # grad h_{i-1} (fused: grad z_{i-1})
+                if s._fused_bwd[i]:
+                    continue
                 s._call("tvk_binary", capi.B_GELU_BACKWARD, dtc, s.gz[i - 1].data_ptr(), s.gh[i - 1].data_ptr(), s.z[i - 1].data_ptr(),
                         0.0, 1.0, s.gz[i - 1].numel())
         return s.loss
