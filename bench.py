@@ -217,7 +217,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     pk = peaks()
     # one list launch for AdamW over all six parameter tensors, its step count in device memory: the whole step is
     # then a fixed sequence of launches that can be replayed as a CUDA graph
-    step = MLPStep(sizes=SIZES, batch=BATCH, dtype=torch.float16, device=dev, seed=0, list_optimizer=True, loss_scale=LOSS_SCALE, eps=ADAM_EPS)
+    step = MLPStep(sizes=SIZES, batch=BATCH, dtype=torch.float16, device=dev, seed=0, list_optimizer=True, loss_scale=LOSS_SCALE, eps=ADAM_EPS, fused=True)
     g = torch.Generator().manual_seed(0)
     x_host = torch.randn(BATCH, SIZES[0], generator=g).half().pin_memory()
     y_host = torch.randint(0, SIZES[-1], (BATCH,), generator=g).pin_memory()

@@ -256,12 +256,11 @@ TVK_API int tvk_gemm(const tvk_gemm_desc* d, void* workspace, uint64_t workspace
 /* Which path tvk_gemm would take: 1 = tcgen05 tensor-core kernel, 2 = CUDA-core kernel. */
 TVK_API int tvk_gemm_path(const tvk_gemm_desc* d, int* path);
 /* Tuning hook of the tensor-core path, process-wide (the counterpart of pinning an entry of the reference's autotune
- * cache, src/vulkan/autotuner.cpp:123-178; used by sweeps and tests, not needed for normal use). 0 (stagger: -1) keeps
- * the library's choice. bn: tile width 32/64/128/256; mt: 128-row tiles per CTA block (1, 2); splits: K slices;
- * stagger: 0 = every block starts at k = 0, 1 = every column tile starts at its own k-block, n > 1 = tile tn starts at
- * k-block (tn * n) mod count; group_m: tile rows per raster group; debug: timing probes (1: the epilogue stores
- * nothing, 2: nothing is loaded or multiplied - results are then undefined). */
-TVK_API int tvk_debug_gemm_tuning(int bn, int mt, int splits, int stagger, int group_m, int debug);
+ * cache, src/vulkan/autotuner.cpp:123-178; used by sweeps and tests, not needed for normal use). 0 keeps the library's
+ * choice. bn: tile width 32/64/128/256; mt: 128-row tiles per CTA block (1, 2); splits: K slices; group_m: tile rows
+ * per raster group; debug: bit flags of timing probes (1: the epilogue stores nothing, 2: nothing is loaded or
+ * multiplied, 4: staged tiles are not stored - results are then undefined). */
+TVK_API int tvk_debug_gemm_tuning(int bn, int mt, int splits, int group_m, int debug);
 
 /* ------------------------------------------------------------------------- *
  * Elementwise maps.

@@ -9,8 +9,11 @@ inputs; it also checks that an oversized shape is refused. The file sorts last o
 a run stopping at the first failure has already gone through every other test."""
 import ctypes as C
 
+import numpy as np
 import pytest
 import torch
+
+import oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -41,6 +44,15 @@ def test_reduce_noalloc_matches_reduce_on_two_consecutive_calls(cuda):
                               need.value, stream)
                     # same kernels, same launch geometry, same summation order: identical bits
                     assert torch.equal(out, ref), (dtype, op, outer, red, inner)
+                    # and against the CPU oracle (float64 on the same rounded inputs), so that the pair cannot be wrong
+                    # together: these shapes all go through the partials in the built-in array
+                    xin = x.float().cpu().double().numpy().reshape(outer, red, inner)
+                    want = oracle.reduce("sum" if op == capi.R_SUM else "amax", xin, 1).reshape(-1)
+                    got = out.cpu().double().numpy()
+                    if op == capi.R_AMAX:
+                        assert np.array_equal(got, want), (dtype, outer, red, inner)
+                    else:   # fp32 accumulation: 1e-5 of the size of the sum (floored at the spread of a zero-mean sum)
+                        assert np.all(np.abs(got - want) <= 1e-5 * np.maximum(np.abs(want), 3 * np.sqrt(red))), (dtype, outer, red, inner)
     # a short reduction needs no partials at all and still works
     x = torch.randn(8, 100, generator=g).to(cuda)
     out = torch.empty(8, device=cuda)

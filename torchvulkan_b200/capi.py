@@ -133,7 +133,7 @@ SIGNATURES = {
     "tvk_gemm_workspace_size": (_i, [_P(GemmDesc), _P(_u64)]),
     "tvk_gemm": (_i, [_P(GemmDesc), _p, _u64, _p]),
     "tvk_gemm_path": (_i, [_P(GemmDesc), _P(_i)]),
-    "tvk_debug_gemm_tuning": (_i, [_i, _i, _i, _i, _i, _i]),
+    "tvk_debug_gemm_tuning": (_i, [_i, _i, _i, _i, _i]),
     "tvk_unary": (_i, [_i, _i, _p, _p, _i64, _p]),
     "tvk_binary": (_i, [_i, _i, _p, _p, _p, _d, _d, _i64, _p]),
     "tvk_compare": (_i, [_i, _i, _p, _p, _p, _d, _i64, _p]),

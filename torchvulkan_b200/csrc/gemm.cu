@@ -22,7 +22,7 @@
 // split-K, for operands TMA cannot address (row pitch not a multiple of 16 bytes) and for
 // shapes with a very small M or N.
 #include "common.cuh"
-#include "tc_common.cuh"
+#include "gemm_tc.cuh"
 
 #include <cuda.h>
 
@@ -48,11 +48,8 @@ struct Params {
     int64_t k_chunk;     // k range per split (multiple of TK)
 };
 
-__device__ __forceinline__ float apply_act(float v, int act) {
-    if (act == TVK_ACT_RELU) return (v != v) ? v : fmaxf(v, 0.f);
-    if (act == TVK_ACT_GELU) return 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
-    return v;
-}
+
+__device__ __forceinline__ float apply_act(float v, int act) { return tc::act_apply(v, act); }
 
 template <typename T>
 __global__ void __launch_bounds__(256) gemm_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C, const T* __restrict__ bias,
@@ -198,7 +195,12 @@ __global__ void __launch_bounds__(256) skinny_n_kernel(const T* __restrict__ A, 
 #pragma unroll
         for (int j = 0; j < 16; ++j) acc[r][j] = 0.f;
     const int64_t packets = p.k / N;
-    for (int64_t q = threadIdx.x; q < packets; q += 256) {
+    const int iters = (int)((packets + 255) / 256);
+    // independent iterations, unrolled so that the loads of several of them are in flight together
+#pragma unroll 4
+    for (int it = 0; it < iters; ++it) {
+        const int64_t q = (int64_t)it * 256 + threadIdx.x;
+        if (q >= packets) break;
         float fa[R][N];
 #pragma unroll
         for (int r = 0; r < R; ++r) {
@@ -339,566 +341,6 @@ static int plan_splits(int64_t batch, int64_t m, int64_t n, int64_t k, int64_t* 
 namespace tc {
 
 
-struct Params {
-    int64_t m, n, batch;
-    int num_kb;          // k-blocks (128 bytes of K each) per pass
-    int passes;          // 1; 3 for the 3xTF32 split
-    int chunk_kb;        // fp32 only: k-blocks per tensor-memory accumulation chain
-    int a_mn, b_mn;      // operand is MN-major (its M/N index is the contiguous one)
-    int a_batched, b_batched;
-    int tiles_m, tiles_n;
-    int64_t total_tiles;
-    uint32_t idesc;
-    void* c;
-    int64_t c_rs, c_bs;
-    const void* bias;
-    int64_t bias_rs, bias_cs, bias_bs;
-    float alpha, beta;
-    int act;
-    int out_dtype;
-    int* status;
-    int stage_ok;        // C (and every peer copy) is 16-byte aligned with 16-byte multiples as row and batch pitch
-    int n_peers;         // further copies of C (same strides) in other devices' memory, written by the epilogue
-    int tma_store;       // C is written by TMA stores of 32-row x 128-byte boxes staged in shared memory (tmap_c is valid)
-    int k_stagger;       // > 0: the block of column tile tn walks its k-blocks starting at (tn * k_stagger) % num_kb
-    int group_m;         // tile rows per raster group (tm runs fastest inside a group)
-    int debug;           // tuning probes: 1 = the epilogue stores nothing, 2 = nothing is loaded or multiplied, 4 = staged tiles are not stored
-    void* c2;            // second output with C's strides: C receives the value before the activation, c2 the activated one
-    const void* aux;     // per-element operand of C's shape and dtype for aux_op (row pitch aux_rs, batch pitch aux_bs)
-    int64_t aux_rs, aux_bs;
-    int aux_op;          // TVK_AUX_*: what the epilogue does with aux
-    void* peer_c[7];
-};
-
-// Threads of the GEMM kernel: producer warp, MMA warp and EIGHT epilogue warps. A warp can only read the 32 tensor-memory
-// lanes (rows) of its quarter (warp index mod 4), so two warps share each quarter and take alternate column groups:
-// reading tensor memory is latency-bound per warp and the epilogue of a block is exposed when a block fills all of it.
-constexpr int kEpiWarps = 8;
-constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
-// Epilogue staging: every epilogue warp owns a 4 KB buffer of 32 rows x 128 bytes in the 128-byte-swizzle layout (chunk j
-// of row r sits at chunk j ^ (r & 7)), from where a group of columns leaves as one TMA store, or as whole 128-byte lines
-// towards this device's C and the peers' copies.
-constexpr int kOutBufBytes = 32 * 128;
-constexpr int kGemmStagingBytes = kEpiWarps * kOutBufBytes;       // 32 KB
-constexpr int kGemmStageBudget = 192 * 1024;
-
-__device__ __forceinline__ void tma_store_3d(const void* tmap, uint32_t src, int c0, int c1, int c2) {
-    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(tmap), "r"(src), "r"(c0), "r"(c1),
-                 "r"(c2)
-                 : "memory");
-}
-
-// Stage and tensor-memory sizing of a CTA that owns MT vertically adjacent 128 x BN tiles (a 128*MT x BN block of C).
-// With MT = 2 the two tiles share every B stage, so a block of C costs (128*MT + BN) rows of operands from L2 instead of
-// MT * (128 + BN): what bounds the weight-streaming and short-K shapes is that fill, not the tensor core.
-template <int BN, int MT> struct GemmCfg {
-    static constexpr int kStageA = MT * BM * 128;
-    static constexpr int kStageB = BN * 128;
-    static constexpr int kStage = kStageA + kStageB;
-    static constexpr int kStagesRaw = kGemmStageBudget / kStage;
-    static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-    static constexpr int kAccBufs = (2 * MT * BN <= 512) ? 2 : 1;       // accumulator sets: two let the epilogue overlap the next block
-    static constexpr int kTmemCols = kAccBufs * MT * BN < 32 ? 32 : kAccBufs * MT * BN;
-    static constexpr int kSmemBytes = kStages * kStage + 1024 /*alignment slack*/ + 256 /*barriers*/;
-};
-
-// aux_op of the epilogue: v is the scaled (and biased) accumulator, x the element of the aux operand.
-__device__ __forceinline__ float aux_apply(float v, float x, int op) {
-    if (op == TVK_AUX_GELU_BACKWARD) {          // the same expression as the elementwise gelu_backward kernel
-        const float cdf = 0.5f * (1.0f + erff(x * 0.7071067811865476f));
-        const float pdf = expf(-0.5f * x * x) * 0.3989422804014327f;
-        return v * (cdf + x * pdf);
-    }
-    if (op == TVK_AUX_RELU_BACKWARD) return (x <= 0.f) ? 0.f : v;
-    return v;
-}
-
-// ES = operand element size in bytes (2: f16/bf16, 4: tf32). MT = 128-row tiles per CTA block (1 or 2).
-template <int BN, int ES, int MT>
-__global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__ CUtensorMap tmap_a1,
-            const __grid_constant__ CUtensorMap tmap_b0, const __grid_constant__ CUtensorMap tmap_b1,
-            const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_c2, const Params p) {
-    using Cfg = GemmCfg<BN, MT>;
-    constexpr int BK = 128 / ES;         // elements of K per stage
-    constexpr int CH = 128 / ES;         // elements of M/N per 128-byte row of an MN-major tile
-    constexpr int kStages = Cfg::kStages;
-    constexpr bool kChunked = (ES == 4) && (BN <= 64);     // fp32: chains of K summed in registers (below)
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t* outbuf = smem + kStages * Cfg::kStage;                    // 1024-byte aligned: the stages are multiples of 1 KB
-    uint64_t* bars = (uint64_t*)(outbuf + kGemmStagingBytes);
-    // bars: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
-    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kStages + 4);
-    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kStages);
-    const uint32_t tfull0 = smem_u32(bars + 2 * kStages), tempty0 = smem_u32(bars + 2 * kStages + 2);
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, 1);
-        }
-        for (int a = 0; a < 2; ++a) {
-            mbar_init(tfull0 + 8 * a, 1);
-            mbar_init(tempty0 + 8 * a, kChunked ? 4 : kEpiWarps);
-        }
-        *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    if (warp == 0 && lane == 0) {
-        // the descriptors are fetched while the barriers and tensor memory are being set up
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a0) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b0) : "memory");
-        if (p.passes > 1) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a1) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b1) : "memory");
-        }
-        if (p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_c) : "memory");
-        if (p.tma_store && p.c2) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_c2) : "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)Cfg::kTmemCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-
-    // fp32 (3xTF32): K is cut into chunks of p.chunk_kb k-blocks, every chunk is one accumulation
-    // chain in tensor memory (small lo terms first, hi*hi last) and the epilogue warps sum the
-    // chunks in registers. Half types: one chain over all of K.
-    static_assert(!(kChunked && MT != 1), "the chunked fp32 epilogue handles one tile per block");
-    constexpr int kAccBufs = Cfg::kAccBufs;
-    // accumulator set and mbarrier parity of the it-th accumulation of this CTA
-    auto acc_of = [&](int64_t it) { return kAccBufs == 2 ? (int)(it & 1) : 0; };
-    auto acc_phase_of = [&](int64_t it) { return (uint32_t)((kAccBufs == 2 ? (it >> 1) : it) & 1); };
-    const int ckb = kChunked ? p.chunk_kb : p.num_kb;
-    auto pass_of = [&](int pi) { return kChunked ? (pi == 0 ? 1 : (pi == 1 ? 2 : 0)) : pi; };
-    const int tiles_per_batch = p.tiles_m * p.tiles_n;
-    auto decode = [&](int64_t t, int& b, int& tm, int& tn) {
-        b = (int)(t / tiles_per_batch);
-        const int r = (int)(t - (int64_t)b * tiles_per_batch);
-        const int group = p.group_m * p.tiles_n;
-        const int g = r / group, rr = r - g * group;
-        const int first_m = g * p.group_m;
-        const int gm = (p.tiles_m - first_m) < p.group_m ? (p.tiles_m - first_m) : p.group_m;
-        tm = first_m + rr % gm;
-        tn = rr / gm;
-    };
-
-    if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int64_t t = blockIdx.x; t < p.total_tiles && ok && !(p.debug & 2); t += gridDim.x) {
-                int b, tm, tn;
-                decode(t, b, tm, tn);
-                const int ab = p.a_batched ? b : 0, bb = p.b_batched ? b : 0;
-                // Blocks that run at the same time would otherwise all read the same 128-byte column strip of their
-                // operand rows (and the very same lines of the shared operand) at the same moment; starting each column
-                // tile at its own k-block spreads those reads over all of the operands' columns. The sum over k is the
-                // same set of terms in a rotated order.
-                const int koff = p.k_stagger > 0 ? (int)(((int64_t)tn * p.k_stagger + b) % p.num_kb) : 0;
-                for (int kb0 = 0; kb0 < p.num_kb && ok; kb0 += ckb) {
-                    const int kb1 = (kb0 + ckb) < p.num_kb ? (kb0 + ckb) : p.num_kb;
-                    for (int pi = 0; pi < p.passes && ok; ++pi) {
-                        const int pass = pass_of(pi);
-                        const void* ta = (pass == 1) ? (const void*)&tmap_a1 : (const void*)&tmap_a0;
-                        const void* tb = (pass == 2) ? (const void*)&tmap_b1 : (const void*)&tmap_b0;
-                        for (int kbi = kb0; kbi < kb1; ++kbi) {
-                            const int kb = (kbi + koff >= p.num_kb) ? (kbi + koff - p.num_kb) : (kbi + koff);
-                            ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.status, 1);
-                            if (!ok) break;
-                            const uint32_t sa = smem_u32(smem + stage * Cfg::kStage);
-                            const uint32_t sb = sa + Cfg::kStageA;
-                            const uint32_t bar = full0 + 8 * stage;
-                            mbar_expect_tx(bar, Cfg::kStage);
-                            if (!p.a_mn) {
-                                tma_load_3d(sa, ta, kb * BK, tm * (MT * BM), ab, bar);
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < MT * BM / CH; ++j) tma_load_3d(sa + j * (BK * 128), ta, tm * (MT * BM) + j * CH, kb * BK, ab, bar);
-                            }
-                            if (!p.b_mn) {
-                                tma_load_3d(sb, tb, kb * BK, tn * BN, bb, bar);
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < BN / CH; ++j) tma_load_3d(sb + j * (BK * 128), tb, tn * BN + j * CH, kb * BK, bb, bar);
-                            }
-                            if (++stage == kStages) { stage = 0; phase ^= 1; }
-                        }
-                    }
-                }
-            }
-            if (ok) {
-                // Drain: wait until the MMA warp has released every stage this thread filled, so no
-                // copy is still in flight towards shared memory when the CTA exits.
-                for (int s = 0; s < kStages && ok; ++s) {
-                    ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.status, 2);
-                    if (++stage == kStages) { stage = 0; phase ^= 1; }
-                }
-            }
-        }
-    } else if (warp == 1) {
-        // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            int64_t it = 0;
-            // Per k-step advance of the descriptor start address, and the LBO/SBO fields.
-            const uint32_t a_step = p.a_mn ? (uint32_t)((32 / ES) * 128) : 32u;
-            const uint32_t b_step = p.b_mn ? (uint32_t)((32 / ES) * 128) : 32u;
-            // MN-major: LBO is the distance between 128-byte-wide column blocks of the tile, SBO the
-            // distance between groups of eight k-rows. K-major: LBO is unused, SBO spans eight rows.
-            const uint32_t a_lbo = p.a_mn ? (uint32_t)(BK * 128) : 16u, a_sbo = 1024u;
-            const uint32_t b_lbo = p.b_mn ? (uint32_t)(BK * 128) : 16u, b_sbo = 1024u;
-            for (int64_t t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
-                for (int kb0 = 0; kb0 < p.num_kb && ok; kb0 += ckb, ++it) {
-                    const int kb1 = (kb0 + ckb) < p.num_kb ? (kb0 + ckb) : p.num_kb;
-                    const int acc = acc_of(it);
-                    const uint32_t acc_phase = acc_phase_of(it);
-                    ok = mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.status, 3);
-                    if (!ok) break;
-                    tc_fence_after();
-                    const uint32_t tmem_c = tmem_base + (uint32_t)(acc * MT * BN);
-                    uint32_t accumulate = 0;
-                    for (int pi = 0; pi < p.passes && ok && !(p.debug & 2); ++pi) {
-                        for (int kb = kb0; kb < kb1; ++kb) {
-                            ok = mbar_wait(full0 + 8 * stage, phase, abort_flag, p.status, 4);
-                            if (!ok) break;
-                            tc_fence_after();
-                            const uint32_t sa = smem_u32(smem + stage * Cfg::kStage);
-                            const uint32_t sb = sa + Cfg::kStageA;
-#pragma unroll
-                            for (int ks = 0; ks < 4; ++ks) {
-                                const uint64_t bdesc = make_smem_desc(sb + ks * b_step, b_lbo, b_sbo);
-#pragma unroll
-                                for (int mt = 0; mt < MT; ++mt) {
-                                    // tile mt of the block: its 128 rows (K-major) or its column blocks (MN-major) start BM*128 bytes on
-                                    const uint64_t adesc = make_smem_desc(sa + mt * (BM * 128) + ks * a_step, a_lbo, a_sbo);
-                                    umma<ES == 4>(tmem_c + (uint32_t)(mt * BN), adesc, bdesc, p.idesc, accumulate);
-                                }
-                                accumulate = 1;
-                            }
-                            umma_commit(empty0 + 8 * stage);
-                            if (++stage == kStages) { stage = 0; phase ^= 1; }
-                        }
-                    }
-                    if (ok) umma_commit(tfull0 + 8 * acc);
-                }
-            }
-        }
-    } else {
-        // ------------------------------ epilogue ------------------------------
-        const int lane_window = (warp & 3) * 32;   // TMEM lanes this warp may read
-        const int half = (warp - 2) >> 2;          // which of the two warps of this quarter: it takes column groups of its parity
-        uint8_t* buf = outbuf + (warp - 2) * kOutBufBytes;               // this warp's staging rows
-        bool ok = true;
-        int64_t it = 0;
-        for (int64_t t = blockIdx.x; t < p.total_tiles && ok && !(kChunked && half); t += gridDim.x) {
-            int b, tm, tn;
-            decode(t, b, tm, tn);
-            int acc = 0;
-            if constexpr (!kChunked) {
-                acc = acc_of(it);
-                const uint32_t acc_phase = acc_phase_of(it);
-                ++it;
-                ok = mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, 5);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tc_fence_after();
-            }
-#pragma unroll 1
-            for (int mt = 0; mt < MT; ++mt) {
-            const int64_t tile_row0 = ((int64_t)tm * MT + mt) * BM;
-            if (mt > 0 && tile_row0 >= p.m) break;      // the lower tile of the last block may lie wholly below C
-            const int64_t row = tile_row0 + lane_window + lane;
-            const int64_t col0 = (int64_t)tn * BN;
-            const bool row_ok = row < p.m;
-            const int64_t coff = ((int64_t)b * p.c_bs + row * p.c_rs) * (p.out_dtype == TVK_F32 ? 4 : 2);   // byte offset of this row in C
-            uint8_t* crow = (uint8_t*)p.c + coff;
-            const uint8_t* brow = nullptr;
-            const int bes = p.out_dtype == TVK_F32 ? 4 : 2;
-            if (p.bias) brow = (const uint8_t*)p.bias + ((int64_t)b * p.bias_bs + row * p.bias_rs) * bes;
-
-            const uint8_t* arow = nullptr;
-            if (p.aux_op) arow = (const uint8_t*)p.aux + ((int64_t)b * p.aux_bs + row * p.aux_rs) * 2;
-            // scale, bias, the aux operation and (with_act) the activation of 32 consecutive columns of this thread's row
-            auto finish = [&](int c0, float* v, bool with_act) {
-                if (!row_ok) return;
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = p.alpha * v[j];
-                const int64_t cbase = col0 + c0;
-                const int ncols = (p.n - cbase) < 32 ? (int)(p.n - cbase) : 32;
-                if (brow) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        if (j < ncols) {
-                            const int64_t off = (cbase + j) * p.bias_cs;
-                            float bv;
-                            if (p.out_dtype == TVK_F32) bv = ((const float*)brow)[off];
-                            else if (p.out_dtype == TVK_F16) bv = __half2float(((const __half*)brow)[off]);
-                            else bv = __bfloat162float(((const __nv_bfloat16*)brow)[off]);
-                            v[j] += p.beta * bv;
-                        }
-                    }
-                }
-                if (arow) {
-                    // the incoming gradient times the derivative of the activation at the saved pre-activation (aux)
-                    uint32_t a2[16];
-                    const uint16_t* ap = (const uint16_t*)arow + cbase;
-                    if (ncols == 32 && ((uintptr_t)ap & 15) == 0) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const uint4 q = __ldg((const uint4*)ap + j);
-                            a2[4 * j] = q.x; a2[4 * j + 1] = q.y; a2[4 * j + 2] = q.z; a2[4 * j + 3] = q.w;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const uint32_t lo = (2 * j < ncols) ? ap[2 * j] : 0u, hi = (2 * j + 1 < ncols) ? ap[2 * j + 1] : 0u;
-                            a2[j] = lo | (hi << 16);
-                        }
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        float x0, x1;
-                        if (p.out_dtype == TVK_F16) { const float2 f = __half22float2(*(const __half2*)&a2[j]); x0 = f.x; x1 = f.y; }
-                        else { const float2 f = __bfloat1622float2(*(const __nv_bfloat162*)&a2[j]); x0 = f.x; x1 = f.y; }
-                        v[2 * j] = aux_apply(v[2 * j], x0, p.aux_op);
-                        v[2 * j + 1] = aux_apply(v[2 * j + 1], x1, p.aux_op);
-                    }
-                }
-                if (with_act && p.act != TVK_ACT_NONE) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = simt::apply_act(v[j], p.act);
-                }
-            };
-            // conversion and store of those columns straight from this thread's registers (any n, any alignment)
-            auto store_direct = [&](int c0, const float* v, int which) {
-                if (!row_ok) return;
-                uint8_t* crow_w = which ? (uint8_t*)p.c2 + coff : crow;
-                const int n_peers_w = which ? 0 : p.n_peers;
-                const int64_t cbase = col0 + c0;
-                const int ncols = (p.n - cbase) < 32 ? (int)(p.n - cbase) : 32;
-                if (p.out_dtype == TVK_F32) {
-                    // q == -1 is this device's C; q >= 0 pushes the same values into a peer's copy over NVLink
-                    for (int q = -1; q < n_peers_w; ++q) {
-                        float* dst = (float*)(q < 0 ? crow_w : (uint8_t*)p.peer_c[q] + coff) + cbase;
-                        if (ncols == 32 && ((uintptr_t)dst & 15) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) *(float4*)(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) if (j < ncols) dst[j] = v[j];
-                        }
-                    }
-                } else {
-                    uint32_t packed[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (p.out_dtype == TVK_F16) {
-                            __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
-                            packed[j] = *(uint32_t*)&h;
-                        } else {
-                            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                            packed[j] = *(uint32_t*)&h;
-                        }
-                    }
-                    for (int q = -1; q < n_peers_w; ++q) {
-                        uint16_t* dst = (uint16_t*)(q < 0 ? crow_w : (uint8_t*)p.peer_c[q] + coff) + cbase;
-                        if (ncols == 32 && ((uintptr_t)dst & 15) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 16; j += 4) *(uint4*)(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (j < ncols) dst[j] = (uint16_t)((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffffu));
-                        }
-                    }
-                }
-            };
-
-            if constexpr (kChunked) {
-                // The tensor core adds into its accumulator with truncation, so a long chain of MMAs
-                // drifts by about one ulp per step. Each chunk of K is therefore accumulated from zero
-                // in tensor memory and the chunks are summed here in registers with round-to-nearest.
-                float sum[BN];
-#pragma unroll
-                for (int j = 0; j < BN; ++j) sum[j] = 0.f;
-                for (int kb0 = 0; kb0 < p.num_kb && ok; kb0 += ckb, ++it) {
-                    const int acc = (int)(it & 1);
-                    const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
-                    ok = mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, 5);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int c0 = 0; c0 < BN; c0 += 32) {
-                        uint32_t r[32];
-                        tmem_ld32(tmem_base + ((uint32_t)lane_window << 16) + (uint32_t)(acc * BN + c0), r);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) sum[c0 + j] += __uint_as_float(r[j]);
-                    }
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
-                }
-                if (!ok) break;
-#pragma unroll
-                for (int c0 = 0; c0 < BN; c0 += 32) {
-                    if (col0 + c0 < p.n) { finish(c0, &sum[c0], true); store_direct(c0, &sum[c0], 0); }
-                }
-            } else {
-                const int gcols = p.out_dtype == TVK_F32 ? 32 : 64;      // columns of C in 128 bytes
-                const bool staged = (p.tma_store || p.stage_ok) && BN % gcols == 0;
-                // 32 finished columns of this thread's row, starting at column c0 of the tile, on their way to C
-                auto emit = [&](int c0, float* v, int which) {
-                    const int g0 = c0 / gcols * gcols;
-                    // Groups of 128 bytes per row go through this warp's staging rows and leave as one TMA store (which clips
-                    // rows >= m and columns >= n) or, towards peers, as whole 128-byte lines (whole groups only).
-                    if (!staged || (!p.tma_store && col0 + g0 + gcols > p.n)) { store_direct(c0, v, which); return; }
-                    if (c0 == g0 && p.tma_store) {
-                        // the previous store of this warp must have finished reading the buffer
-                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                        __syncwarp();
-                    }
-                    uint8_t* mine = buf + lane * 128;
-                    const int sw = lane & 7;
-                    if (p.out_dtype == TVK_F32) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            *(float4*)(mine + ((j ^ sw) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                    } else {
-                        uint32_t packed[16];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            if (p.out_dtype == TVK_F16) { __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]); packed[j] = *(uint32_t*)&h; }
-                            else { __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]); packed[j] = *(uint32_t*)&h; }
-                        }
-                        const int j0 = (c0 - g0) >> 3;   // first 16-byte chunk of these 32 columns within the row
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            *(uint4*)(mine + (((j0 + j) ^ sw) << 4)) = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-                    }
-                    if (!(c0 + 32 == g0 + gcols || (p.tma_store && col0 + c0 + 32 >= p.n))) return;
-                    if (p.tma_store) {
-                        if (p.debug & 4) return;                     // probe: staged, never stored
-                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                        __syncwarp();
-                        if (lane == 0 && tile_row0 + lane_window < p.m) {
-                            tma_store_3d(which ? &tmap_c2 : &tmap_c, smem_u32(buf), (int)(col0 + g0), (int)(tile_row0 + lane_window), b);
-                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                        }
-                        return;
-                    }
-                    __syncwarp();
-                    uint4 line[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int rr = 4 * i + (lane >> 3);
-                        line[i] = *(const uint4*)(buf + rr * 128 + ((((lane & 7) ^ (rr & 7))) << 4));
-                    }
-                    const int es_out = p.out_dtype == TVK_F32 ? 4 : 2;
-                    const int64_t row0 = tile_row0 + lane_window;
-                    const int64_t off0 = ((int64_t)b * p.c_bs + row0 * p.c_rs + col0 + g0) * es_out + (lane & 7) * 16;
-                    const int64_t row_bytes = p.c_rs * es_out;
-                    // q == -1 is this device's C; q >= 0 pushes the same lines into a peer's copy over NVLink
-                    for (int q = -1; q < (which ? 0 : p.n_peers); ++q) {
-                        uint8_t* base = (q < 0 ? (uint8_t*)(which ? p.c2 : p.c) : (uint8_t*)p.peer_c[q]) + off0;
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int rr = 4 * i + (lane >> 3);
-                            if (row0 + rr < p.m) *(uint4*)(base + rr * row_bytes) = line[i];
-                        }
-                    }
-                    __syncwarp();
-                };
-                // This warp's chunks of 32 columns: the column groups of its parity (the other warp of the quarter takes the
-                // rest). Load, wait, finish, store one chunk at a time: keeping the next chunk's tensor-memory load in flight
-                // under the stores measured slower (weight-gradient shape 55 -> 65 us).
-                const uint32_t tacc = tmem_base + ((uint32_t)lane_window << 16) + (uint32_t)((acc * MT + mt) * BN);
-                // With a second output the accumulator is read twice: first for C (no activation), then for c2 (activated).
-                const int n_out = p.c2 ? 2 : 1;
-#pragma unroll 1
-                for (int which = 0; which < n_out; ++which) {
-                if (p.debug & 8) {
-                    // a whole 128-byte column group per step: both tensor-memory loads in flight before the one wait
-#pragma unroll 1
-                    for (int g0c = 0; g0c < BN; g0c += 64) {
-                        if (col0 + g0c >= p.n) break;
-                        if (((g0c / gcols) & 1) != half && gcols == 64) continue;
-                        if (gcols == 32 && ((((g0c) / 32) & 1) != half) && ((((g0c + 32) / 32) & 1) != half)) continue;
-                        uint32_t r0[32], r1[32];
-                        const bool second = (g0c + 32 < BN) && (col0 + g0c + 32 < p.n);
-                        tmem_ld32(tacc + (uint32_t)g0c, r0);
-                        if (second) tmem_ld32(tacc + (uint32_t)(g0c + 32), r1);
-                        tmem_ld_wait();
-                        float v[32];
-                        if (gcols == 64 || ((g0c / 32) & 1) == half) {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r0[j]);
-                            finish(g0c, v, which == n_out - 1);
-                            if (!(p.debug & 1)) emit(g0c, v, which);
-                        }
-                        if (second && (gcols == 64 || (((g0c + 32) / 32) & 1) == half)) {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r1[j]);
-                            finish(g0c + 32, v, which == n_out - 1);
-                            if (!(p.debug & 1)) emit(g0c + 32, v, which);
-                        }
-                    }
-                } else {
-#pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32) {
-                    if (col0 + c0 >= p.n) break;                   // uniform across the warp
-                    if (((c0 / gcols) & 1) != half) continue;
-                    uint32_t r[32];
-                    tmem_ld32(tacc + (uint32_t)c0, r);
-                    tmem_ld_wait();
-                    float v[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                    finish(c0, v, which == n_out - 1);
-                    if (!(p.debug & 1)) emit(c0, v, which);
-                }
-                }
-                }
-            }   // mt
-            if constexpr (!kChunked) {
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
-            }
-        }
-        // every TMA store of this warp has finished reading its staging rows before shared memory is handed back (the
-        // writes themselves complete with the grid)
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-    }
-
-    // ------------------------------ teardown ------------------------------
-    __syncwarp();
-    if (*abort_flag) {
-        // Let copies and MMAs that were already issued finish before shared and tensor memory
-        // are handed back.
-        for (int i = 0; i < 200; ++i) __nanosleep(1000);
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::kTmemCols) : "memory");
-    }
-}
 
 // 3xTF32 operand split: hi = round-to-nearest tf32 of x, lo = x - hi (exact in fp32). The copies
 // are always written K-major ([rows][k], pitch ld) whatever the source layout: element (r, k) of
@@ -1089,21 +531,6 @@ static void pick_block(int64_t batch, int64_t m, int64_t n, int64_t k, int min_b
     }
 }
 
-template <int BN, int ES, int MT>
-static int launch(const CUtensorMap* maps, const Params& p, cudaStream_t s) {
-    using Cfg = GemmCfg<BN, MT>;
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        TVK_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<BN, ES, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes + kGemmStagingBytes));
-        attr_set[dev] = true;
-    }
-    int64_t grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
-    gemm_kernel<BN, ES, MT><<<(unsigned)grid, kGemmThreads, Cfg::kSmemBytes + kGemmStagingBytes, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p);
-    return launch_status("tcgen05 gemm");
-}
-
 }  // namespace tc
 
 // =====================================================================================
@@ -1113,7 +540,7 @@ static int launch(const CUtensorMap* maps, const Params& p, cudaStream_t s) {
 // reference pins an entry of its autotune cache (src/vulkan/autotuner.cpp:123-178): a sweep sets them, measures, and
 // the winners become the rules of pick_block / tc_splitk_plan below.
 struct GemmTuning {
-    int bn = 0, mt = 0, splits = 0, stagger = -1, group_m = 0, debug = 0;
+    int bn = 0, mt = 0, splits = 0, group_m = 0, debug = 0;
 };
 static GemmTuning g_tune;
 
@@ -1196,7 +623,8 @@ static Repack plan_repack(const tvk_gemm_desc* d) {
 static int choose_path(const tvk_gemm_desc* d) {
     if (d->c_f32 && d->dtype != TVK_F32) return tc_eligible(d) ? 1 : 0;   // mixed output exists on the tensor-core path only
     if (d->n_peer_c > 0) return tc_eligible(d) ? 1 : 0;                   // so do the pushed peer copies
-    if (fused_epilogue(d)) {                                              // and the fused epilogues
+    if (fused_epilogue(d)) {                                              // the fused epilogues exist on the tensor-core path only
+        if (d->dtype == TVK_F32) return 0;
         if (tc_eligible(d)) return 1;
         const Repack r = plan_repack(d);
         return (r.a || r.b) ? 1 : 0;
@@ -1236,6 +664,7 @@ static int run_simt(const tvk_gemm_desc* d, void* ws, uint64_t ws_bytes, cudaStr
     p.c_rs = d->c_rs; p.c_bs = d->c_bs;
     p.bias_rs = d->bias_rs; p.bias_cs = d->bias_cs; p.bias_bs = d->bias_bs;
     p.alpha = d->alpha; p.beta = d->beta; p.act = d->activation;
+    if (fused_epilogue(d)) return set_error(TVK_ERR_UNSUPPORTED, "torchvulkan [NOT IMPLEMENTED]: fused epilogue (c2 / aux) on the CUDA-core path");
     if (skinny_n_ok(d)) {
         dim3 grid((unsigned)((d->m + simt::kSkinnyNRows - 1) / simt::kSkinnyNRows), (unsigned)d->batch);
         TVK_DISPATCH_FLOAT(d->dtype, T, (simt::skinny_n_kernel<T><<<grid, 256, 0, s>>>((const T*)d->a, (const T*)d->b, (T*)d->c, (const T*)d->bias, p)));
@@ -1378,13 +807,6 @@ static int run_tc(const tvk_gemm_desc* d, void* ws, uint64_t ws_bytes, cudaStrea
     }
     p.group_m = g_tune.group_m > 0 ? g_tune.group_m : 8;
     p.debug = g_tune.debug;
-    p.k_stagger = 0;
-    if (!f32 && p.num_kb > 1) {
-        const int auto_stagger = 0;
-        const int st = g_tune.stagger >= 0 ? g_tune.stagger : auto_stagger;
-        // st == 1 asks for the spread that gives every column tile its own start: num_kb / tiles_n, at least 1
-        p.k_stagger = st == 1 ? (p.num_kb / p.tiles_n > 1 ? p.num_kb / p.tiles_n : 1) : st;
-    }
     p.a_mn = a_mn; p.b_mn = b_mn;
     p.a_batched = d->batch > 1 && a_bs != 0;
     p.b_batched = d->batch > 1 && b_bs != 0;
@@ -1421,17 +843,11 @@ static int run_tc(const tvk_gemm_desc* d, void* ws, uint64_t ws_bytes, cudaStrea
             if (rc) return rc;
         }
     }
-#define TVK_TC_LAUNCH(BN_)                                                                     \
-    case BN_:                                                                                  \
-        if (es == 2) return mt == 2 ? tc::launch<BN_, 2, 2>(maps, p, s) : tc::launch<BN_, 2, 1>(maps, p, s); \
-        return tc::launch<(BN_ > 64 ? 64 : BN_), 4, 1>(maps, p, s);
-    switch (bn) {
-        TVK_TC_LAUNCH(256)
-        TVK_TC_LAUNCH(128)
-        TVK_TC_LAUNCH(64)
-        TVK_TC_LAUNCH(32)
-    }
-#undef TVK_TC_LAUNCH
+    const bool fused = p.c2 != nullptr || p.aux_op != TVK_AUX_NONE;
+    if (f32) return tc::launch_tf32(bn, 1, maps, p, s);
+    if (p.out_dtype == TVK_F32) return tc::launch_half_f32out(bn, mt, maps, p, s);
+    if (d->dtype == TVK_F16) return fused ? tc::launch_f16_fused(bn, mt, maps, p, s) : tc::launch_f16(bn, mt, maps, p, s);
+    if (d->dtype == TVK_BF16) return fused ? tc::launch_bf16_fused(bn, mt, maps, p, s) : tc::launch_bf16(bn, mt, maps, p, s);
     return set_error(TVK_ERR_INVALID, "tvk_gemm: internal tile selection error");
 }
 
@@ -1522,8 +938,8 @@ using namespace tvk;
 
 extern "C" {
 
-int tvk_debug_gemm_tuning(int bn, int mt, int splits, int stagger, int group_m, int debug) {
-    g_tune.bn = bn; g_tune.mt = mt; g_tune.splits = splits; g_tune.stagger = stagger; g_tune.group_m = group_m; g_tune.debug = debug;
+int tvk_debug_gemm_tuning(int bn, int mt, int splits, int group_m, int debug) {
+    g_tune.bn = bn; g_tune.mt = mt; g_tune.splits = splits; g_tune.group_m = group_m; g_tune.debug = debug;
     return TVK_OK;
 }
 

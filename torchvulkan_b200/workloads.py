@@ -20,7 +20,7 @@ from . import cuda_ops as ops
 
 class MLPStep:
     def __init__(self, sizes=(784, 8192, 8192, 10), batch=256, dtype=torch.float16, device="cuda", seed=0,
-                 lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, params=None, list_optimizer=False, loss_scale=1.0, fused=False):
+                 lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, params=None, list_optimizer=False, loss_scale=1.0, fused=False, fuse_forward=None):
         self.sizes, self.batch, self.dtype, self.device = tuple(sizes), batch, dtype, torch.device(device)
         self.lr, self.betas, self.eps, self.wd = lr, betas, eps, weight_decay
         self.nl = len(sizes) - 1
@@ -47,10 +47,13 @@ class MLPStep:
         # list_optimizer: one tvk_adam_step_multi launch for all parameters, step count in device memory (as
         # torch.optim keeps it for fused optimizers) and advanced on the device: the step is then replayable
         self.list_optimizer = list_optimizer
-        # fused: the activation is written by the addmm epilogue next to the pre-activation (two outputs of one pass over
-        # the accumulator) and gelu_backward is applied by the epilogue of the input-gradient product (the saved
-        # pre-activation is its aux operand): four launches and four passes over 256 x 8192 tensors fewer per hidden layer pair
+        # fused: gelu_backward is applied by the epilogue of the input-gradient product (the saved pre-activation is its
+        # aux operand; its factors are formed while the product streams the weights, so the launch costs what the plain
+        # product costs) wherever that product is long enough to hide them (k >= 1024). fuse_forward also lets the addmm
+        # epilogue write gelu(z) next to z (two outputs from one accumulator); measured on B200 that second pass over the
+        # accumulator costs more than the separate gelu launch it saves at batch 256, so it is off unless asked for.
         self.fused = fused
+        self.fuse_forward = bool(fuse_forward) if fuse_forward is not None else False
         self.step_dev = torch.zeros((), dtype=torch.float32, device=dev)
         self._adam_items = (capi.MultiItem * len(self.params))()
         for i, (p, g, m, v) in enumerate(zip(self.params, self.grads, self.m, self.v)):
@@ -94,7 +97,7 @@ class MLPStep:
         self._fused_fwd, self._fused_bwd = [False] * self.nl, [False] * self.nl
         for i in range(self.nl):
             plain = ops.gemm_desc(inp, self.w[i].t(), self.z[i], bias=self.b[i])        # addmm
-            if self.fused and i < self.nl - 1:
+            if self.fuse_forward and i < self.nl - 1:
                 both = ops.gemm_desc(inp, self.w[i].t(), self.z[i], bias=self.b[i], act="gelu", out2=self.h[i])       # addmm + gelu
                 self._fused_fwd[i] = supported(both)
                 plain = both if self._fused_fwd[i] else plain
@@ -105,7 +108,7 @@ class MLPStep:
             d.append(ops.gemm_desc(self.gz[i].t(), act_in, self.gw[i]))                  # wgrad = gz^T @ in
             if i > 0:
                 plain = ops.gemm_desc(self.gz[i], self.w[i], self.gh[i - 1])             # dgrad = gz @ W
-                if self.fused:
+                if self.fused and self.sizes[i + 1] >= 1024:
                     both = ops.gemm_desc(self.gz[i], self.w[i], self.gz[i - 1], aux=self.z[i - 1], aux_op="gelu_backward")   # mm + gelu_backward
                     self._fused_bwd[i] = supported(both)
                     plain = both if self._fused_bwd[i] else plain
