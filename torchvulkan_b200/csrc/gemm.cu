@@ -788,6 +788,7 @@ static int run_tc(const tvk_gemm_desc* d, void* ws, uint64_t ws_bytes, cudaStrea
     p.tiles_m = (int)((d->m + mt * tc::BM - 1) / (mt * tc::BM));
     p.tiles_n = (int)((d->n + bn - 1) / bn);
     p.total_tiles = (int64_t)d->batch * p.tiles_m * p.tiles_n;
+    if (p.total_tiles >= ((int64_t)1 << 31)) return set_error(TVK_ERR_UNSUPPORTED, "torchvulkan [NOT IMPLEMENTED]: matmul with %lld output tiles", (long long)p.total_tiles);
     p.c = d->c; p.c_rs = d->c_rs; p.c_bs = d->c_bs;
     p.bias = d->bias; p.bias_rs = d->bias_rs; p.bias_cs = d->bias_cs; p.bias_bs = d->bias_bs;
     p.alpha = d->alpha; p.beta = d->beta; p.act = d->activation; p.out_dtype = d->c_f32 ? TVK_F32 : d->dtype;

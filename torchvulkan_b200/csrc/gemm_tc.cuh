@@ -280,16 +280,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
     auto acc_phase_of = [&](int64_t it) { return (uint32_t)((kAccBufs == 2 ? (it >> 1) : it) & 1); };
     const int ckb = kChunked ? p.chunk_kb : p.num_kb;
     auto pass_of = [&](int pi) { return kChunked ? (pi == 0 ? 1 : (pi == 1 ? 2 : 0)) : pi; };
-    const int tiles_per_batch = p.tiles_m * p.tiles_n;
-    auto decode = [&](int64_t t, int& b, int& tm, int& tn) {
-        b = (int)(t / tiles_per_batch);
-        const int r = (int)(t - (int64_t)b * tiles_per_batch);
-        const int group = p.group_m * p.tiles_n;
-        const int g = r / group, rr = r - g * group;
-        const int first_m = g * p.group_m;
-        const int gm = (p.tiles_m - first_m) < p.group_m ? (p.tiles_m - first_m) : p.group_m;
-        tm = first_m + rr % gm;
-        tn = rr / gm;
+    // Tile index arithmetic in 32 bits (the host refuses launches with 2^31 tiles or more): a 64-bit division costs several
+    // hundred clocks, and this runs once per tile in every role.
+    const uint32_t tiles_per_batch = (uint32_t)(p.tiles_m * p.tiles_n);
+    const uint32_t total_tiles = (uint32_t)p.total_tiles;
+    auto decode = [&](uint32_t t, int& b, int& tm, int& tn) {
+        const uint32_t bb = t / tiles_per_batch;
+        const uint32_t r = t - bb * tiles_per_batch;
+        const uint32_t group = (uint32_t)(p.group_m * p.tiles_n);
+        const uint32_t g = r / group, rr = r - g * group;
+        const uint32_t first_m = g * (uint32_t)p.group_m;
+        const uint32_t left = (uint32_t)p.tiles_m - first_m;
+        const uint32_t gm = left < (uint32_t)p.group_m ? left : (uint32_t)p.group_m;
+        const uint32_t q = rr / gm;
+        b = (int)bb;
+        tm = (int)(first_m + (rr - q * gm));
+        tn = (int)q;
     };
 
     if (warp == 0) {
@@ -298,7 +304,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int64_t t = blockIdx.x; t < p.total_tiles && ok && !(p.debug & 2); t += gridDim.x) {
+            for (uint32_t t = blockIdx.x; t < total_tiles && ok && !(p.debug & 2); t += gridDim.x) {
                 int b, tm, tn;
                 decode(t, b, tm, tn);
                 const int ab = p.a_batched ? b : 0, bb = p.b_batched ? b : 0;
@@ -355,7 +361,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
             // distance between groups of eight k-rows. K-major: LBO is unused, SBO spans eight rows.
             const uint32_t a_lbo = p.a_mn ? (uint32_t)(BK * 128) : 16u, a_sbo = 1024u;
             const uint32_t b_lbo = p.b_mn ? (uint32_t)(BK * 128) : 16u, b_sbo = 1024u;
-            for (int64_t t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+            for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 for (int kb0 = 0; kb0 < p.num_kb && ok; kb0 += ckb, ++it) {
                     const int kb1 = (kb0 + ckb) < p.num_kb ? (kb0 + ckb) : p.num_kb;
                     const int acc = acc_of(it);
@@ -401,7 +407,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
         uint8_t* buf = outbuf + (warp - 2) * kOutBufBytes;               // this warp's staging rows
         bool ok = true;
         int64_t it = 0;
-        for (int64_t t = blockIdx.x; t < p.total_tiles && ok && !(kChunked && half); t += gridDim.x) {
+        for (uint32_t t = blockIdx.x; t < total_tiles && ok && !(kChunked && half); t += gridDim.x) {
             int b, tm, tn;
             decode(t, b, tm, tn);
             int acc = 0;
