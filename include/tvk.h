@@ -145,6 +145,10 @@ TVK_API int tvk_memcpy_d2d(int dev, void* dst, const void* src, uint64_t bytes);
 /* Cross-device copy; the reference bounces through the host (allocator.cpp:143-161), here it
  * is a peer copy over NVLink. */
 TVK_API int tvk_memcpy_peer(int dst_dev, void* dst, int src_dev, const void* src, uint64_t bytes);
+/* Device-to-device copy on a stream of the caller's (copy_device_to_device, src/vulkan/allocator.cpp:143-161, without
+ * the library's own stream): dst or src may be another device's memory mapped into this process (tvk_ipc_open, or a
+ * peer-enabled device), in which case the bytes travel over NVLink on a copy engine and occupy no SM. */
+TVK_API int tvk_memcpy_async(void* dst, const void* src, uint64_t bytes, void* stream);
 
 /* Device that owns a pointer handed out by tvk_malloc (or any CUDA device pointer). Replaces the
  * "data pointer is a VulkanBuffer*" lookup of getDeviceFromPtr (src/api/hook.cpp:58-61). */
@@ -164,7 +168,12 @@ TVK_API int tvk_event_elapsed_ms(void* start, void* end, float* ms);
  * into a CUDA graph and the whole step is replayed with one call. Between begin and end every launch of this library
  * on `dev` is recorded instead of run; calls that wait for the device (tvk_synchronize, tvk_memcpy_d2h, host-to-device
  * copies from pageable memory) fail while a capture is open. A replay reads and writes the buffers the captured step
- * used: keep them alive (tvk_malloc'ed blocks freed after the capture may be handed out again). */
+ * used. Blocks tvk_malloc hands out while the capture runs join a pool owned by the graph: when they are freed (during
+ * the capture or later) they are parked in that pool - reused inside the same capture only - and reach the shared
+ * cache or the driver only with tvk_graph_destroy, so no later allocation is given memory that a replay writes into.
+ * Inside a capture tvk_empty_cache is a no-op and an allocation the driver refuses fails with TVK_ERR_OOM at once (the
+ * usual free-the-cache-and-retry step would wait for the device). Blocks that were allocated BEFORE the capture (the
+ * model, the inputs) are the caller's to keep alive. tvk_graph_destroy waits for the device's stream first. */
 TVK_API int tvk_graph_begin_capture(int dev);
 TVK_API int tvk_graph_end_capture(int dev, void** graph);     /* instantiated, ready for tvk_graph_launch */
 TVK_API int tvk_graph_launch(int dev, void* graph);
@@ -395,6 +404,49 @@ TVK_API int tvk_nll_loss_forward(int dtype, void* out, void* total_weight, const
 TVK_API int tvk_nll_loss_backward(int dtype, void* grad_in, const void* grad_out, const int64_t* target,
                                   const void* weight, const void* total_weight, int64_t n, int64_t c,
                                   int reduction, int64_t ignore_index, void* stream);
+
+/* LayerNorm (layer_norm_shader / layer_norm_backward_shader, src/api/ops/norm.cpp:264-325; rowForward, rowBackwardInput,
+ * rowBackwardParams of src/shaders/ops/norm.slang:193-317). x viewed as [rows, cols] contiguous with cols the product of
+ * normalized_shape. y = (x - mean) * rstd * w + b; mean and rstd (biased variance, two-pass) saved as fp32 [rows].
+ * weight / bias may be NULL. */
+TVK_API int tvk_layernorm_forward(int dtype, void* y, float* mean, float* rstd, const void* x, const void* weight,
+                                  const void* bias, int64_t rows, int64_t cols, double eps, void* stream);
+/* Any of grad_x, grad_w, grad_b may be NULL. grad_w / grad_b (cols, `dtype`) need fp32 scratch of
+ * tvk_layernorm_backward_workspace_size bytes. cols <= 8192. */
+TVK_API int tvk_layernorm_backward_workspace_size(int64_t rows, int64_t cols, uint64_t* bytes);
+TVK_API int tvk_layernorm_backward(int dtype, void* grad_x, void* grad_w, void* grad_b, const void* grad_y, const void* x,
+                                   const void* weight, const float* mean, const float* rstd, int64_t rows, int64_t cols,
+                                   void* workspace, uint64_t workspace_bytes, void* stream);
+/* GroupNorm over contiguous [n, channels, hw] (native_group_norm, src/api/ops/norm.cpp:264-325 row mode with per-channel
+ * affine): mean / rstd fp32 [n, groups]. */
+TVK_API int tvk_groupnorm_forward(int dtype, void* y, float* mean, float* rstd, const void* x, const void* weight,
+                                  const void* bias, int64_t n, int64_t channels, int64_t hw, int64_t groups, double eps,
+                                  void* stream);
+TVK_API int tvk_groupnorm_backward(int dtype, void* grad_x, void* grad_w, void* grad_b, const void* grad_y, const void* x,
+                                   const void* weight, const float* mean, const float* rstd, int64_t n, int64_t channels,
+                                   int64_t hw, int64_t groups, void* stream);
+
+/* Cross-entropy of [n, c] logits with class-index targets in one pass each way: what the reference runs as log_softmax
+ * (src/api/decompositions.cpp:506-571) followed by nll_loss (src/api/ops/nllloss.cpp:79-174), without the [n, c] table
+ * of log-probabilities in between. Same conventions as tvk_nll_loss_*: reduction 0 none (loss has n elements), 1 mean
+ * (sum of w[t] * loss / sum of w[t]), 2 sum; targets equal to ignore_index or outside [0, c) contribute nothing.
+ * lse (fp32 [n], may be NULL) receives the row log-sum-exp, which the backward pass needs. total_weight (may be NULL)
+ * as nll_loss_forward's second result. Reductions other than none need tvk_cross_entropy_workspace_size bytes. */
+TVK_API int tvk_cross_entropy_workspace_size(int64_t n, uint64_t* bytes);
+TVK_API int tvk_cross_entropy_forward(int dtype, void* loss, void* total_weight, float* lse, const void* logits,
+                                      const int64_t* target, const void* weight, int64_t n, int64_t c, int reduction,
+                                      int64_t ignore_index, void* workspace, uint64_t workspace_bytes, void* stream);
+/* grad_logits[i, j] = (softmax(logits_i)[j] - [j == target_i]) * w[target_i] * grad_out (/ total_weight for the mean). */
+TVK_API int tvk_cross_entropy_backward(int dtype, void* grad_logits, const void* grad_out, const void* logits,
+                                       const float* lse, const int64_t* target, const void* weight,
+                                       const void* total_weight, int64_t n, int64_t c, int reduction,
+                                       int64_t ignore_index, void* stream);
+
+/* Inclusive scan along the middle axis of a contiguous [outer, n, inner] view (cumscan, src/api/ops/scan.cpp:35-102;
+ * src/shaders/ops/scan.slang): cumsum, cumprod, logcumsumexp. Floating types accumulate in fp32 and round every
+ * output; TVK_I64 scans in int64 (sum and product). */
+enum { TVK_SCAN_SUM = 0, TVK_SCAN_PROD = 1, TVK_SCAN_LOGADDEXP = 2 };
+TVK_API int tvk_scan(int op, int dtype, void* out, const void* in, int64_t outer, int64_t n, int64_t inner, void* stream);
 
 /* RMSNorm (src/api/ops/norm.cpp:169-260; src/shaders/ops/norm.slang:193-317).
  * y = x * rstd * w, rstd = rsqrt(mean(x^2) + eps) saved as fp32 [rows]. weight may be NULL. */

@@ -21,7 +21,9 @@ __all__ = [
     "softmax_backward", "log_softmax_backward", "nll_loss_forward", "nll_loss_backward", "rmsnorm_forward",
     "rmsnorm_backward", "batchnorm_forward", "batchnorm_backward", "embedding_forward", "embedding_backward",
     "adam_step", "sgd_step", "unary", "binary", "mlp_step", "attention_forward", "attention_backward",
-    "conv2d_forward", "conv2d_backward_input", "conv2d_backward_weight",
+    "conv2d_forward", "conv2d_backward_input", "conv2d_backward_weight", "layernorm_forward", "layernorm_backward",
+    "groupnorm_forward", "groupnorm_backward", "cross_entropy_forward", "cross_entropy_backward", "scan",
+    "gelu_tanh", "gelu_tanh_backward",
 ]
 
 
@@ -337,6 +339,100 @@ def attention_backward(dout, q, k, v, causal=True, scale=None):
     dk = np.einsum("bhls,bhld->bhsd", ds, q).reshape(B, Hk, g, S, D).sum(axis=2)
     dv = np.einsum("bhls,bhld->bhsd", p, dout).reshape(B, Hk, g, S, D).sum(axis=2)
     return dq, dk, dv
+
+
+# ----------------------------------------------------------------------------- layer / group norm
+def layernorm_forward(x, weight=None, bias=None, norm_dims=1, eps=1e-5):
+    """(x - mean) * rstd * w + b over the last `norm_dims` axes, biased variance, mean first then the centred squares
+    (rowForward, src/shaders/ops/norm.slang:193-226; host src/api/ops/norm.cpp:264-290). Returns (y, mean, rstd)."""
+    x = np.asarray(x, np.float64)
+    axes = tuple(range(x.ndim - norm_dims, x.ndim))
+    mean = x.mean(axis=axes, keepdims=True)
+    var = ((x - mean) ** 2).mean(axis=axes, keepdims=True)
+    rstd = 1.0 / np.sqrt(var + eps)
+    y = (x - mean) * rstd
+    if weight is not None:
+        y = y * np.asarray(weight, np.float64)
+    if bias is not None:
+        y = y + np.asarray(bias, np.float64)
+    return y, mean.reshape(x.shape[:x.ndim - norm_dims]), rstd.reshape(x.shape[:x.ndim - norm_dims])
+
+
+def layernorm_backward(grad_y, x, weight, mean, rstd, norm_dims=1):
+    """rowBackwardInput / rowBackwardParams (src/shaders/ops/norm.slang:228-317): grad_x = rstd * (g - mean(g) - xhat *
+    mean(g * xhat)) with g = grad_y * w; grad_w = sum grad_y * xhat and grad_b = sum grad_y over the rows."""
+    gy, x = np.asarray(grad_y, np.float64), np.asarray(x, np.float64)
+    axes = tuple(range(x.ndim - norm_dims, x.ndim))
+    lead = tuple(range(x.ndim - norm_dims))
+    shape = x.shape[:x.ndim - norm_dims] + (1,) * norm_dims
+    xhat = (x - np.asarray(mean, np.float64).reshape(shape)) * np.asarray(rstd, np.float64).reshape(shape)
+    g = gy * (np.asarray(weight, np.float64) if weight is not None else 1.0)
+    gx = np.asarray(rstd, np.float64).reshape(shape) * (g - g.mean(axis=axes, keepdims=True) - xhat * (g * xhat).mean(axis=axes, keepdims=True))
+    return gx, (gy * xhat).sum(axis=lead), gy.sum(axis=lead)
+
+
+def groupnorm_forward(x, groups, weight=None, bias=None, eps=1e-5):
+    """native_group_norm: statistics over (C / G, H, W) of every (sample, group), affine per channel
+    (src/api/ops/norm.cpp:264-325 in its row mode). Returns (y, mean [n, G], rstd [n, G])."""
+    x = np.asarray(x, np.float64)
+    n, c = x.shape[:2]
+    xg = x.reshape(n, groups, -1)
+    mean = xg.mean(axis=2)
+    var = ((xg - mean[..., None]) ** 2).mean(axis=2)
+    rstd = 1.0 / np.sqrt(var + eps)
+    y = ((xg - mean[..., None]) * rstd[..., None]).reshape(x.shape)
+    bshape = (1, c) + (1,) * (x.ndim - 2)
+    if weight is not None:
+        y = y * np.asarray(weight, np.float64).reshape(bshape)
+    if bias is not None:
+        y = y + np.asarray(bias, np.float64).reshape(bshape)
+    return y, mean, rstd
+
+
+def groupnorm_backward(grad_y, x, weight, mean, rstd, groups):
+    gy, x = np.asarray(grad_y, np.float64), np.asarray(x, np.float64)
+    n, c = x.shape[:2]
+    bshape = (1, c) + (1,) * (x.ndim - 2)
+    xhat = ((x.reshape(n, groups, -1) - np.asarray(mean, np.float64)[..., None]) * np.asarray(rstd, np.float64)[..., None]).reshape(x.shape)
+    g = gy * (np.asarray(weight, np.float64).reshape(bshape) if weight is not None else 1.0)
+    gg, xg = g.reshape(n, groups, -1), xhat.reshape(n, groups, -1)
+    gx = np.asarray(rstd, np.float64)[..., None] * (gg - gg.mean(axis=2, keepdims=True) - xg * (gg * xg).mean(axis=2, keepdims=True))
+    red = (0,) + tuple(range(2, x.ndim))
+    return gx.reshape(x.shape), (gy * xhat).sum(axis=red), gy.sum(axis=red)
+
+
+# ----------------------------------------------------------------------------- cross-entropy (fused form)
+def cross_entropy_forward(logits, target, weight=None, reduction="mean", ignore_index=-100):
+    """nll_loss(log_softmax(logits)) as one function (src/api/decompositions.cpp:506-571 followed by
+    src/api/ops/nllloss.cpp:79-174; ignored / out-of-range targets contribute nothing, nllloss.slang:20-39).
+    Returns (loss, total_weight, lse)."""
+    x = np.asarray(logits, np.float64)
+    m = x.max(axis=1, keepdims=True)
+    lse = (m + np.log(np.exp(x - m).sum(axis=1, keepdims=True)))[:, 0]
+    loss, total = nll_loss_forward(x - lse[:, None], target, weight, reduction, ignore_index)
+    return loss, total, lse
+
+
+def cross_entropy_backward(grad_out, logits, lse, target, weight=None, reduction="mean", ignore_index=-100, total_weight=None):
+    """(softmax - onehot) * w[t] * g (/ total_weight): log_softmax_backward of nll_loss_backward in one expression."""
+    x = np.asarray(logits, np.float64)
+    n, c = x.shape
+    sm = np.exp(x - np.asarray(lse, np.float64)[:, None])
+    g = nll_loss_backward(grad_out, target, c, weight, reduction, ignore_index, total_weight)      # -w*g/total at the target
+    return g - sm * g.sum(axis=1, keepdims=True)
+
+
+# ----------------------------------------------------------------------------- scans
+def scan(op, x, axis):
+    """Inclusive scan (src/shaders/ops/scan.slang: SumScanOp, ProdScanOp, LogAddExpScanOp)."""
+    x = np.asarray(x)
+    if op == "cumsum":
+        return np.cumsum(x, axis=axis)
+    if op == "cumprod":
+        return np.cumprod(x, axis=axis)
+    if op == "logcumsumexp":
+        return np.logaddexp.accumulate(np.asarray(x, np.float64), axis=axis)
+    raise ValueError(op)
 
 
 # ----------------------------------------------------------------------------- embedding

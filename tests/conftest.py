@@ -19,6 +19,11 @@ def golden():
 
 
 @pytest.fixture(scope="session")
+def golden_rowops():
+    return np.load(ROOT / "tests" / "golden" / "aten_cpu_rowops.npz")
+
+
+@pytest.fixture(scope="session")
 def cuda():
     import torch
 

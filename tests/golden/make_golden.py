@@ -153,5 +153,63 @@ def main() -> None:
     print(path, path.stat().st_size, "bytes,", len(out), "arrays")
 
 
+def main_rowops() -> None:
+    """tests/golden/aten_cpu_rowops.npz: LayerNorm, GroupNorm, cross-entropy and the scans (a file of its own so that adding
+    it left the first file's random stream, and with it every committed value there, untouched)."""
+    torch.manual_seed(4321)
+    torch.set_num_threads(1)
+    out: dict[str, np.ndarray] = {}
+
+    def put(name, t):
+        out[name] = t.detach().cpu().numpy().copy() if isinstance(t, torch.Tensor) else np.asarray(t)
+
+    # layer_norm forward + backward over one and two trailing axes (src/api/ops/norm.cpp:264-325)
+    for tag, shape, nd in (("a", (5, 7, 24), 1), ("b", (4, 6, 10), 2)):
+        x = torch.randn(*shape, dtype=torch.float64, requires_grad=True)
+        w = (torch.rand(shape[-nd:], dtype=torch.float64) + 0.5).requires_grad_()
+        b = torch.randn(shape[-nd:], dtype=torch.float64, requires_grad=True)
+        y = F.layer_norm(x, shape[-nd:], w, b, 1e-5)
+        g = torch.randn_like(y)
+        gx, gw, gb = torch.autograd.grad(y, (x, w, b), g)
+        for k, v in (("x", x), ("w", w), ("b", b), ("y", y), ("g", g), ("gx", gx), ("gw", gw), ("gb", gb)):
+            put(f"ln_{tag}_{k}", v)
+        put(f"ln_{tag}_nd", np.array(nd))
+    # group_norm forward + backward
+    x = torch.randn(3, 12, 5, 4, dtype=torch.float64, requires_grad=True)
+    w = (torch.rand(12, dtype=torch.float64) + 0.5).requires_grad_()
+    b = torch.randn(12, dtype=torch.float64, requires_grad=True)
+    y = F.group_norm(x, 4, w, b, 1e-5)
+    g = torch.randn_like(y)
+    gx, gw, gb = torch.autograd.grad(y, (x, w, b), g)
+    for k, v in (("x", x), ("w", w), ("b", b), ("y", y), ("g", g), ("gx", gx), ("gw", gw), ("gb", gb)):
+        put(f"gn_{k}", v)
+    # cross_entropy: mean / sum / none, class weights, ignored targets
+    logits = torch.randn(11, 9, dtype=torch.float64, requires_grad=True)
+    tgt = torch.tensor([0, 8, 3, -100, 2, 2, 5, -100, 1, 7, 4])
+    w = torch.rand(9, dtype=torch.float64) + 0.5
+    put("ce_x", logits); put("ce_t", tgt); put("ce_w", w)
+    for red in ("mean", "sum", "none"):
+        for use_w in (0, 1):
+            loss = F.cross_entropy(logits, tgt, weight=w if use_w else None, reduction=red)
+            go = torch.randn_like(loss)
+            gl, = torch.autograd.grad(loss, logits, go)
+            put(f"ce_{red}_w{use_w}_loss", loss); put(f"ce_{red}_w{use_w}_go", go); put(f"ce_{red}_w{use_w}_gx", gl)
+    # scans
+    s = torch.randn(4, 9, 5, dtype=torch.float64)
+    put("scan_x", s)
+    for d in (0, 1, 2):
+        put(f"cumsum_d{d}", torch.cumsum(s, d)); put(f"cumprod_d{d}", torch.cumprod(s, d)); put(f"logcumsumexp_d{d}", torch.logcumsumexp(s, d))
+    si = torch.randint(-3, 4, (3, 17))
+    put("scan_i", si); put("cumsum_i", torch.cumsum(si, 1)); put("cumprod_i", torch.cumprod(si, 1))
+    out["torch_version"] = np.array(torch.__version__)
+    path = Path(__file__).resolve().parent / "aten_cpu_rowops.npz"
+    np.savez_compressed(path, **out)
+    print(path, path.stat().st_size, "bytes,", len(out), "arrays")
+
+
 if __name__ == "__main__":
-    main()
+    import sys
+
+    if "--rowops-only" not in sys.argv:
+        main()
+    main_rowops()

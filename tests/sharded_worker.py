@@ -28,11 +28,11 @@ def main():
     lo, hi = shard_range(args.batch, rank, world)
     a_mine, b_mine = a[lo:hi].to(dev), b[lo:hi].to(dev)
     compute = None if gpu else (lambda x, y, out: torch.bmm(x, y, out=out))
-    modes = ("push", "pipelined", "allgather") if gpu else ("pipelined", "allgather")
+    modes = ("push", "copy", "pipelined", "allgather") if gpu else ("pipelined", "allgather")
     for mode in modes:
         if mode == "push" and args.batch % world:
             continue
-        for chunks in ((1, 3) if mode == "pipelined" else (1,)):
+        for chunks in ((1, 3) if mode in ("pipelined", "copy") else (1,)):
             out = torch.full((args.batch, m, n), float("nan"), dtype=dtype, device=dev)
             op = ShardedBmm(out, mode=mode, chunks=chunks, compute=compute)
             # two steps with different operands and a reader of the first result in between: the second step must

@@ -134,6 +134,39 @@ CHILD = textwrap.dedent(
     assert lib.tvk_mem_reset_peak(0) == 0 and stats().peak_allocated_bytes == stats().allocated_bytes
     assert lib.tvk_free(0, p) == 0 and lib.tvk_empty_cache(0) == 0 and stats().reserved_bytes == 0
     assert stats().total_allocated_bytes - stats().total_freed_bytes == 0
+    # A graph's private pool: blocks handed out during a capture are parked with the graph when freed, reused inside the
+    # capture only, invisible to other allocations and to empty_cache until the graph is destroyed.
+    g = C.c_void_p(); a = C.c_void_p(); b = C.c_void_p(); c = C.c_void_p()
+    assert lib.tvk_malloc(0, 2000, C.byref(a)) == 0 and lib.tvk_free(0, a) == 0          # one 2 KiB block in the shared cache
+    shared = a.value
+    assert lib.tvk_graph_begin_capture(0) == 0
+    assert lib.tvk_graph_begin_capture(0) == capi.ERR_INVALID                            # one capture per device
+    assert lib.tvk_malloc(0, 2000, C.byref(a)) == 0 and a.value == shared                 # a cached block may join the pool
+    assert lib.tvk_malloc(0, 3000, C.byref(b)) == 0
+    inside = b.value
+    assert lib.tvk_free(0, b) == 0                                                       # freed during the capture: parked
+    assert lib.tvk_malloc(0, 3000, C.byref(c)) == 0 and c.value == inside                 # ... and reused by the same capture
+    assert lib.tvk_free(0, c) == 0
+    frees = calls["free"]
+    assert lib.tvk_empty_cache(0) == 0 and calls["free"] == frees                        # no-op while capturing
+    fail_next[0] = 1
+    assert lib.tvk_malloc(0, 5000, C.byref(c)) == capi.ERR_OOM and b"during a graph capture" in lib.tvk_last_error()   # no ladder
+    assert lib.tvk_graph_end_capture(0, C.byref(g)) == 0 and g.value
+    reserved = stats().reserved_bytes
+    assert lib.tvk_malloc(0, 3000, C.byref(c)) == 0 and c.value != inside                 # between replays: not the parked block
+    assert lib.tvk_free(0, c) == 0
+    assert lib.tvk_free(0, a) == 0                                                       # a pool block freed after the capture: parked too
+    assert lib.tvk_malloc(0, 2000, C.byref(c)) == 0 and c.value != shared
+    assert lib.tvk_free(0, c) == 0
+    frees = calls["free"]
+    assert lib.tvk_empty_cache(0) == 0 and calls["free"] > frees                         # frees the shared cache only
+    assert stats().reserved_bytes == 2048 + 3072                                         # the two parked blocks stay reserved
+    assert lib.tvk_graph_launch(1, g) == capi.ERR_INVALID and lib.tvk_graph_launch(0, g) == 0
+    assert lib.tvk_graph_destroy(g) == 0
+    assert stats().cached_bytes == 2048 + 3072                                           # back in the shared cache
+    assert lib.tvk_malloc(0, 3000, C.byref(c)) == 0 and c.value == inside and lib.tvk_free(0, c) == 0
+    assert lib.tvk_empty_cache(0) == 0 and stats().reserved_bytes == 0
+    assert lib.tvk_graph_end_capture(0, C.byref(g)) == capi.ERR_INVALID                  # nothing to end
     # RNG bookkeeping: reserve hands out consecutive offsets (src/vulkan/generator.cpp:165-167)
     s = C.c_uint64(); o = C.c_uint64()
     assert lib.tvk_rng_set_seed(0, 42) == 0

@@ -63,8 +63,8 @@ def test_mlp_step_with_fused_epilogues(cuda, sizes, batch):
     fused = run(cuda, sizes, batch, fused=True, fuse_forward=True)
     run(cuda, sizes, batch, fused=True)
     plain = run(cuda, sizes, batch, fused=False)
-    saved = sum(fused._fused_fwd) + sum(fused._fused_bwd)
-    assert fused.launches_per_step == plain.launches_per_step - saved and saved >= (3 if batch == 256 else 2)
+    saved = sum(fused._fused_fwd) + sum(fused._fused_bwd) + 2      # and the cross-entropy: two launches instead of four
+    assert fused.launches_per_step == plain.launches_per_step - saved and saved >= (5 if batch == 256 else 4)
     for a, b in zip(fused.h, plain.h):
         # gelu of the fp32 accumulator against gelu of its fp16 rounding: one rounding apart
         assert rel_fro(f64(a), f64(b)) <= 1e-3

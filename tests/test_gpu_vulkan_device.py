@@ -183,6 +183,42 @@ def test_sdpa_causal_with_unequal_lengths_matches_aten(vk, L, S):
     close(dq.grad, cq.grad, 1e-2); close(dk.grad, ck.grad, 1e-2); close(dv.grad, cv.grad, 1e-2)
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.float16, 3e-3)])
+def test_layer_norm_group_norm_and_scans(vk, dtype, tol):
+    """native_layer_norm / native_group_norm forward and backward, cumsum / cumprod / logcumsumexp (the rows SURVEY lists
+    next to softmax and RMSNorm; src/api/ops/norm.cpp:264-325, src/api/ops/scan.cpp:104-126) against ATen CPU in fp32."""
+    torch.manual_seed(21)
+    x = torch.randn(6, 17, 96).to(dtype)
+    ln_c, ln_d = torch.nn.LayerNorm(96), torch.nn.LayerNorm(96).to(dtype).to(vk)
+    with torch.no_grad():
+        ln_c.weight.copy_(torch.rand(96) + 0.5); ln_c.bias.copy_(torch.randn(96))
+        ln_d.weight.copy_(ln_c.weight.to(dtype)); ln_d.bias.copy_(ln_c.bias.to(dtype))
+        ln_c.weight.copy_(ln_d.weight.cpu().float()); ln_c.bias.copy_(ln_d.bias.cpu().float())
+    xc, xd = x.float().requires_grad_(), x.to(vk).requires_grad_()
+    g = torch.randn(6, 17, 96).to(dtype)
+    ln_d(xd).backward(g.to(vk)); ln_c(xc).backward(g.float())
+    close(ln_d(xd), ln_c(xc), tol); close(xd.grad, xc.grad, tol); close(ln_d.weight.grad, ln_c.weight.grad, tol); close(ln_d.bias.grad, ln_c.bias.grad, tol)
+    close(F.layer_norm(xd, (17, 96)), F.layer_norm(xc, (17, 96)), tol)                     # two trailing axes, no affine
+    xi = torch.randn(4, 12, 6, 5).to(dtype)
+    gn_c, gn_d = torch.nn.GroupNorm(4, 12), torch.nn.GroupNorm(4, 12).to(dtype).to(vk)
+    with torch.no_grad():
+        gn_c.weight.copy_(torch.rand(12) + 0.5); gn_c.bias.copy_(torch.randn(12))
+        gn_d.weight.copy_(gn_c.weight.to(dtype)); gn_d.bias.copy_(gn_c.bias.to(dtype))
+        gn_c.weight.copy_(gn_d.weight.cpu().float()); gn_c.bias.copy_(gn_d.bias.cpu().float())
+    ic, idv = xi.float().requires_grad_(), xi.to(vk).requires_grad_()
+    gi = torch.randn(4, 12, 6, 5).to(dtype)
+    gn_d(idv).backward(gi.to(vk)); gn_c(ic).backward(gi.float())
+    close(gn_d(idv), gn_c(ic), tol); close(idv.grad, ic.grad, tol); close(gn_d.weight.grad, gn_c.weight.grad, tol); close(gn_d.bias.grad, gn_c.bias.grad, tol)
+    s = (torch.randn(5, 40, 3) * 0.5).to(dtype)
+    for d in (0, 1, 2, -1):
+        close(torch.cumsum(s.to(vk), d), torch.cumsum(s.float(), d), tol * 4)
+        close(torch.logcumsumexp(s.to(vk), d), torch.logcumsumexp(s.float(), d), tol * 4)
+    p = (1 + torch.randn(5, 40) * 0.05).to(dtype)
+    close(torch.cumprod(p.to(vk), 1), torch.cumprod(p.float(), 1), tol * 4)
+    i = torch.randint(-4, 5, (7, 33))
+    assert torch.equal(torch.cumsum(i.to(vk), 1).cpu(), torch.cumsum(i, 1)) and torch.equal(i.to(vk).cumsum(0).cpu(), i.cumsum(0))
+
+
 def make_mlp(sizes):
     layers = []
     for i in range(len(sizes) - 1):
@@ -492,8 +528,17 @@ def test_graph_replay_equals_eager_steps(vk, kind):
     g = torchvulkan.Graph()
     with g.capture():
         step(1)                                   # ... one recorded (not run) ...
-    for _ in range(4):
+    junk = []
+    for r in range(4):
         g.replay()                                # ... and four replays of it
+        # Work between the replays must not disturb the graph: its temporaries are parked in a pool of its own, so
+        # neither fresh allocations (of the sizes the step uses) nor empty_cache() can be given, or free, its memory.
+        junk.append([torch.full_like(p, float(r)) for p in models[1].parameters()])
+        junk.append(torch.randn(48, 136).half().to(vk).float().half())
+        if r == 1:
+            torchvulkan.empty_cache()
+        if r == 2:
+            junk.clear()
     torchvulkan.synchronize()
     for (n, p0), (_, p1) in zip(models[0].named_parameters(), models[1].named_parameters()):
         assert torch.equal(p0.cpu(), p1.cpu()), n

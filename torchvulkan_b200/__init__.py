@@ -150,6 +150,12 @@ class Graph:
     from host memory: keep its inputs on the device and overwrite them in place between replays (``x.copy_(batch)``
     before the replay). Optimizers must keep their step count on the device (``fused=True``). Tensors created during
     the capture that are still referenced afterwards (the loss, the gradients) are rewritten by every replay.
+
+    Memory: every block the allocator hands out during the capture belongs to the graph. Temporaries that are freed
+    are parked with the graph (and reused only inside the same capture), not returned to the shared cache, so work done
+    between replays (``x.copy_(batch)`` with a cast, another model, ``empty_cache()``) can never be given, or free,
+    memory a replay writes into. ``reset()`` (or deleting the Graph) releases the pool. Tensors that existed before
+    the capture (parameters, inputs) must be kept alive by the caller.
     """
 
     def __init__(self, device=None):

@@ -58,6 +58,7 @@ class GemmDesc(C.Structure):
 
 
 AUX_NONE, AUX_GELU_BACKWARD, AUX_RELU_BACKWARD = 0, 1, 2
+SCAN_SUM, SCAN_PROD, SCAN_LOGADDEXP = 0, 1, 2
 
 
 class MultiItem(C.Structure):
@@ -115,6 +116,7 @@ SIGNATURES = {
     "tvk_memcpy_d2h": (_i, [_i, _p, _p, _u64]),
     "tvk_memcpy_d2d": (_i, [_i, _p, _p, _u64]),
     "tvk_memcpy_peer": (_i, [_i, _p, _i, _p, _u64]),
+    "tvk_memcpy_async": (_i, [_p, _p, _u64, _p]),
     "tvk_pointer_device": (_i, [_p, _P(_i)]),
     "tvk_event_create": (_i, [_P(_p)]),
     "tvk_event_destroy": (_i, [_p]),
@@ -156,6 +158,15 @@ SIGNATURES = {
     "tvk_rmsnorm_forward": (_i, [_i, _p, _p, _p, _p, _i64, _i64, _d, _p]),
     "tvk_rmsnorm_backward_workspace_size": (_i, [_i64, _i64, _P(_u64)]),
     "tvk_rmsnorm_backward": (_i, [_i, _p, _p, _p, _p, _p, _p, _i64, _i64, _p, _u64, _p]),
+    "tvk_layernorm_forward": (_i, [_i, _p, _p, _p, _p, _p, _p, _i64, _i64, _d, _p]),
+    "tvk_layernorm_backward_workspace_size": (_i, [_i64, _i64, _P(_u64)]),
+    "tvk_layernorm_backward": (_i, [_i, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _p, _u64, _p]),
+    "tvk_groupnorm_forward": (_i, [_i, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _d, _p]),
+    "tvk_groupnorm_backward": (_i, [_i, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _p]),
+    "tvk_cross_entropy_workspace_size": (_i, [_i64, _P(_u64)]),
+    "tvk_cross_entropy_forward": (_i, [_i, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i64, _p, _u64, _p]),
+    "tvk_cross_entropy_backward": (_i, [_i, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i64, _p]),
+    "tvk_scan": (_i, [_i, _i, _p, _p, _i64, _i64, _i64, _p]),
     "tvk_embedding_forward": (_i, [_i, _p, _p, _p, _i64, _i64, _i64, _p]),
     "tvk_embedding_backward": (_i, [_i, _p, _p, _p, _i64, _i64, _i64, _i64, _p]),
     "tvk_batchnorm_workspace_size": (_i, [_i64, _i64, _i64, _P(_u64)]),

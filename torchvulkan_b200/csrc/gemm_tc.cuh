@@ -575,8 +575,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
                             const int64_t off0 = ((int64_t)b * p.c_bs + row0 * p.c_rs + col0 + g0) * kEsOut + (lane & 7) * 16;
                             const int64_t row_bytes = p.c_rs * kEsOut;
                             const int np = (FUSED && which) ? 0 : p.n_peers;
-                            // q == -1 is this device's C; q >= 0 pushes the same lines into a peer's copy over NVLink
-                            for (int q = -1; q < np; ++q) {
+                            // qi == -1 is this device's C; the others push the same lines into the peers' copies over NVLink,
+                            // every CTA starting at another peer so that 148 CTAs do not all write to one GPU at a time
+                            const int rot = np > 0 ? (int)((blockIdx.x + (unsigned)warp) % (unsigned)np) : 0;
+                            for (int qi = -1; qi < np; ++qi) {
+                                const int q = qi < 0 ? -1 : (qi + rot >= np ? qi + rot - np : qi + rot);
                                 uint8_t* base = (q < 0 ? cbase_ptr : (uint8_t*)p.peer_c[q]) + off0;
 #pragma unroll
                                 for (int i = 0; i < 8; ++i) {

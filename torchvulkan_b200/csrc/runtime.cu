@@ -52,6 +52,17 @@ static uint64_t round_size(uint64_t size) {
     return (size + step - 1) / step * step;
 }
 
+// Blocks a captured graph refers to. A graph bakes device addresses into its nodes, so every block handed out while the
+// capture ran belongs to the graph from then on: freed blocks are parked here (and reused only inside the same
+// capture), never returned to the shared cache or to the driver while the graph exists. Without this a block freed
+// during the capture could be handed to an unrelated allocation between two replays, and the next replay would write
+// into it; tvk_empty_cache or the out-of-memory ladder could even cudaFree it under the graph.
+struct GraphPool {
+    std::map<uint64_t, std::vector<void*>> parked;   // freed blocks of this pool by size
+    std::unordered_map<void*, uint64_t> owned;       // every block of the pool (live or parked) -> size
+    uint64_t parked_bytes = 0;
+};
+
 class CachingAllocator {
 public:
     int allocate(uint64_t bytes, void** out) {
@@ -60,14 +71,32 @@ public:
         const uint64_t rounded = round_size(bytes);
         std::lock_guard<std::mutex> lock(mu_);
         void* p = nullptr;
+        if (capturing_) {
+            auto pit = capturing_->parked.find(rounded);
+            if (pit != capturing_->parked.end() && !pit->second.empty()) {
+                p = pit->second.back();
+                pit->second.pop_back();
+                capturing_->parked_bytes -= rounded;
+                parked_total_ -= rounded;
+                ++stats_.num_cache_hits;
+            }
+        }
         auto it = free_.find(rounded);
-        if (it != free_.end() && !it->second.empty()) {
+        if (p) {
+            // reused inside the capture
+        } else if (it != free_.end() && !it->second.empty()) {
             p = it->second.back();  // newest first: it is the most likely to still sit in L2
             it->second.pop_back();
             cached_ -= rounded;
             ++stats_.num_cache_hits;
         } else {
             int rc = raw_alloc(&p, rounded);
+            if (rc != 0 && capturing_) {
+                // no retry ladder inside a capture: it would wait for the device and free blocks, both of which
+                // invalidate the capture
+                return set_error(TVK_ERR_OOM, "torchvulkan [ERROR]: out of memory during a graph capture: tried to allocate %llu bytes",
+                                 (unsigned long long)rounded);
+            }
             if (rc != 0) {
                 // Ladder of VulkanAllocator::allocate: give the cache back to the driver, retry.
                 ++stats_.num_oom_retries;
@@ -84,12 +113,48 @@ public:
             ++stats_.num_device_mallocs;
         }
         live_[p] = rounded;
+        if (capturing_) {
+            capturing_->owned[p] = rounded;
+            owner_[p] = capturing_;
+        }
         stats_.allocated_bytes += rounded;
         stats_.total_allocated_bytes += rounded;
         if (stats_.allocated_bytes > stats_.peak_allocated_bytes)
             stats_.peak_allocated_bytes = stats_.allocated_bytes;
         *out = p;
         return TVK_OK;
+    }
+
+    // Capture bracket of the device's graph: between the two calls every allocation joins a new pool.
+    int begin_capture() {
+        std::lock_guard<std::mutex> lock(mu_);
+        if (capturing_) return set_error(TVK_ERR_INVALID, "tvk_graph_begin_capture: a capture is already running on this device");
+        capturing_ = new GraphPool();
+        return TVK_OK;
+    }
+    GraphPool* end_capture() {
+        std::lock_guard<std::mutex> lock(mu_);
+        GraphPool* pool = capturing_;
+        capturing_ = nullptr;
+        return pool;
+    }
+    // The graph is gone: its parked blocks go to the shared cache, its live blocks become ordinary blocks.
+    void release_pool(GraphPool* pool) {
+        if (!pool) return;
+        std::lock_guard<std::mutex> lock(mu_);
+        if (capturing_ == pool) capturing_ = nullptr;
+        for (auto& kv : pool->owned) owner_.erase(kv.first);
+        for (auto& kv : pool->parked)
+            for (void* p : kv.second) {
+                free_[kv.first].push_back(p);
+                cached_ += kv.first;
+                parked_total_ -= kv.first;
+            }
+        delete pool;
+    }
+    bool capturing() {
+        std::lock_guard<std::mutex> lock(mu_);
+        return capturing_ != nullptr;
     }
 
     int release(void* p) {
@@ -102,6 +167,14 @@ public:
         live_.erase(it);
         stats_.allocated_bytes -= rounded;
         stats_.total_freed_bytes += rounded;
+        auto own = owner_.find(p);
+        if (own != owner_.end()) {
+            // a graph refers to this address: park it with the graph
+            own->second->parked[rounded].push_back(p);
+            own->second->parked_bytes += rounded;
+            parked_total_ += rounded;
+            return TVK_OK;
+        }
         free_[rounded].push_back(p);
         cached_ += rounded;
         return TVK_OK;
@@ -109,14 +182,15 @@ public:
 
     void empty_cache() {
         std::lock_guard<std::mutex> lock(mu_);
+        if (capturing_) return;      // waiting for the device or freeing blocks would invalidate the running capture
         release_cached_locked(/*sync=*/true);
     }
 
     void get_stats(tvk_mem_stats* s) {
         std::lock_guard<std::mutex> lock(mu_);
         *s = stats_;
-        s->cached_bytes = cached_;
-        s->reserved_bytes = stats_.allocated_bytes + cached_;
+        s->cached_bytes = cached_ + parked_total_;
+        s->reserved_bytes = stats_.allocated_bytes + cached_ + parked_total_;
     }
     void reset_peak() {
         std::lock_guard<std::mutex> lock(mu_);
@@ -149,6 +223,9 @@ private:
     std::mutex mu_;
     std::map<uint64_t, std::vector<void*>> free_;
     std::unordered_map<void*, uint64_t> live_;
+    std::unordered_map<void*, GraphPool*> owner_;     // blocks that belong to a graph's pool
+    GraphPool* capturing_ = nullptr;                  // the pool of the capture that is running, if any
+    uint64_t parked_total_ = 0;
     uint64_t cached_ = 0;
     tvk_mem_stats stats_ = {};
 };
@@ -249,6 +326,7 @@ struct DeviceScope {
 
 static int ensure_stream(Device* d) {
     if (d->stream_ready) return TVK_OK;
+    if (g_fake_devices > 0) return TVK_OK;      // host-only unit tests: no CUDA calls at all
     std::lock_guard<std::mutex> lock(d->mu);
     if (d->stream_ready) return TVK_OK;
     DeviceScope scope;
@@ -556,6 +634,13 @@ int tvk_memcpy_d2d(int dev, void* dst, const void* src, uint64_t bytes) {
     return TVK_OK;
 }
 
+int tvk_memcpy_async(void* dst, const void* src, uint64_t bytes, void* stream) {
+    if (bytes == 0) return TVK_OK;
+    TVK_REQUIRE(dst && src, "tvk_memcpy_async: null pointer");
+    TVK_CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    return TVK_OK;
+}
+
 int tvk_memcpy_peer(int dst_dev, void* dst, int src_dev, const void* src, uint64_t bytes) {
     if (bytes == 0) return TVK_OK;
     TVK_REQUIRE(dst && src, "tvk_memcpy_peer: null pointer");
@@ -716,14 +801,28 @@ int tvk_event_elapsed_ms(void* start, void* end, float* ms) {
     return TVK_OK;
 }
 
+// What tvk_graph_end_capture hands out: the executable graph and the memory pool its nodes point into.
+struct GraphHandle {
+    cudaGraphExec_t exec = nullptr;
+    GraphPool* pool = nullptr;
+    int device = 0;
+};
+
 int tvk_graph_begin_capture(int dev) {
     Device* d;
     int rc = get_dev(dev, &d);
     if (rc) return rc;
     rc = ensure_stream(d);
     if (rc) return rc;
+    rc = d->alloc.begin_capture();
+    if (rc) return rc;
+    if (g_fake_devices > 0) return TVK_OK;
     // Relaxed: a cache miss of the allocator may still call cudaMalloc, from this thread or from autograd's
-    TVK_CUDA_CHECK(cudaStreamBeginCapture(d->stream, cudaStreamCaptureModeRelaxed));
+    cudaError_t e = cudaStreamBeginCapture(d->stream, cudaStreamCaptureModeRelaxed);
+    if (e != cudaSuccess) {
+        d->alloc.release_pool(d->alloc.end_capture());
+        return set_error(TVK_ERR_CUDA, "cudaStreamBeginCapture failed: %s", cudaGetErrorString(e));
+    }
     return TVK_OK;
 }
 
@@ -735,21 +834,33 @@ int tvk_graph_end_capture(int dev, void** graph) {
     if (rc) return rc;
     if (!graph) return set_error(TVK_ERR_INVALID, "tvk_graph_end_capture: null output");
     *graph = nullptr;
+    GraphPool* pool = d->alloc.end_capture();
+    if (!pool) return set_error(TVK_ERR_INVALID, "tvk_graph_end_capture: no capture is running on device %d", dev);
+    GraphHandle* h = new GraphHandle();
+    h->pool = pool;
+    h->device = dev;
+    if (g_fake_devices > 0) {
+        *graph = h;
+        return TVK_OK;
+    }
     cudaGraph_t g = nullptr;
     cudaError_t e = cudaStreamEndCapture(d->stream, &g);
     if (e != cudaSuccess || !g) {
         cudaGetLastError();
+        d->alloc.release_pool(pool);
+        delete h;
         return set_error(TVK_ERR_CUDA, "the capture was invalidated (a call that waits for the device, or a copy from pageable host memory, ran inside it): %s",
                          cudaGetErrorString(e));
     }
-    cudaGraphExec_t exec = nullptr;
-    e = cudaGraphInstantiate(&exec, g, 0);
+    e = cudaGraphInstantiate(&h->exec, g, 0);
     cudaGraphDestroy(g);
     if (e != cudaSuccess) {
         cudaGetLastError();
+        d->alloc.release_pool(pool);
+        delete h;
         return set_error(TVK_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
     }
-    *graph = (void*)exec;
+    *graph = (void*)h;
     return TVK_OK;
 }
 
@@ -760,13 +871,31 @@ int tvk_graph_launch(int dev, void* graph) {
     rc = ensure_stream(d);
     if (rc) return rc;
     if (!graph) return set_error(TVK_ERR_INVALID, "tvk_graph_launch: null graph");
-    TVK_CUDA_CHECK(cudaGraphLaunch((cudaGraphExec_t)graph, d->stream));
+    GraphHandle* h = (GraphHandle*)graph;
+    if (h->device != dev) return set_error(TVK_ERR_INVALID, "tvk_graph_launch: the graph was captured on device %d, not %d", h->device, dev);
+    if (g_fake_devices > 0) return TVK_OK;
+    TVK_CUDA_CHECK(cudaGraphLaunch(h->exec, d->stream));
     return TVK_OK;
 }
 
 int tvk_graph_destroy(void* graph) {
     if (!graph) return TVK_OK;
-    TVK_CUDA_CHECK(cudaGraphExecDestroy((cudaGraphExec_t)graph));
+    GraphHandle* h = (GraphHandle*)graph;
+    Device* d;
+    int rc = get_dev(h->device, &d);
+    if (rc) return rc;
+    if (h->exec) {
+        // the graph may still be running: its blocks must not reach other users before it has finished
+        if (g_fake_devices == 0) {
+            DeviceScope scope;
+            rc = scope.enter(h->device);
+            if (rc) return rc;
+            if (d->stream_ready) cudaStreamSynchronize(d->stream);
+            cudaGraphExecDestroy(h->exec);
+        }
+    }
+    d->alloc.release_pool(h->pool);
+    delete h;
     return TVK_OK;
 }
 

@@ -322,6 +322,88 @@ def rmsnorm_backward(grad_y, x, weight, rstd, need_weight_grad=True):
     return gx, gw
 
 
+def layernorm_forward(x, weight=None, bias=None, norm_dims=1, eps=1e-5):
+    cols = 1
+    for d in x.shape[x.dim() - norm_dims:]:
+        cols *= d
+    rows = x.numel() // max(cols, 1)
+    y = torch.empty_like(x)
+    mean = torch.empty(x.shape[:x.dim() - norm_dims], dtype=torch.float32, device=x.device)
+    rstd = torch.empty_like(mean)
+    capi.call("tvk_layernorm_forward", dt(x), ptr(y), ptr(mean), ptr(rstd), ptr(x), ptr(weight), ptr(bias), rows, cols, float(eps), stream())
+    return y, mean, rstd
+
+
+def layernorm_backward(grad_y, x, weight, mean, rstd, norm_dims=1, need_params=True):
+    cols = 1
+    for d in x.shape[x.dim() - norm_dims:]:
+        cols *= d
+    rows = x.numel() // max(cols, 1)
+    gx = torch.empty_like(x)
+    gw = torch.empty(x.shape[x.dim() - norm_dims:], dtype=x.dtype, device=x.device) if need_params else None
+    gb = torch.empty_like(gw) if need_params else None
+    nbytes = C.c_uint64(0)
+    capi.call("tvk_layernorm_backward_workspace_size", rows, cols, C.byref(nbytes))
+    ws = _ws(nbytes.value, x.device)
+    capi.call("tvk_layernorm_backward", dt(x), ptr(gx), ptr(gw), ptr(gb), ptr(grad_y), ptr(x), ptr(weight), ptr(mean), ptr(rstd), rows, cols,
+              ptr(ws), nbytes.value, stream())
+    return gx, gw, gb
+
+
+def groupnorm_forward(x, groups, weight=None, bias=None, eps=1e-5):
+    n, c = x.shape[0], x.shape[1]
+    hw = x.numel() // max(n * c, 1)
+    y = torch.empty_like(x)
+    mean = torch.empty((n, groups), dtype=torch.float32, device=x.device)
+    rstd = torch.empty_like(mean)
+    capi.call("tvk_groupnorm_forward", dt(x), ptr(y), ptr(mean), ptr(rstd), ptr(x), ptr(weight), ptr(bias), n, c, hw, groups, float(eps), stream())
+    return y, mean, rstd
+
+
+def groupnorm_backward(grad_y, x, weight, mean, rstd, groups):
+    n, c = x.shape[0], x.shape[1]
+    hw = x.numel() // max(n * c, 1)
+    gx = torch.empty_like(x)
+    gw = torch.empty(c, dtype=x.dtype, device=x.device)
+    gb = torch.empty_like(gw)
+    capi.call("tvk_groupnorm_backward", dt(x), ptr(gx), ptr(gw), ptr(gb), ptr(grad_y), ptr(x), ptr(weight), ptr(mean), ptr(rstd), n, c, hw, groups,
+              stream())
+    return gx, gw, gb
+
+
+def cross_entropy_forward(logits, target, weight=None, reduction="mean", ignore_index=-100):
+    n, c = logits.shape
+    loss = torch.empty((n,) if reduction == "none" else (), dtype=logits.dtype, device=logits.device)
+    total = torch.empty((), dtype=logits.dtype, device=logits.device)
+    lse = torch.empty(n, dtype=torch.float32, device=logits.device)
+    nbytes = C.c_uint64(0)
+    capi.call("tvk_cross_entropy_workspace_size", n, C.byref(nbytes))
+    ws = _ws(max(nbytes.value, 8), logits.device)
+    capi.call("tvk_cross_entropy_forward", dt(logits), ptr(loss), ptr(total), ptr(lse), ptr(logits), ptr(target), ptr(weight), n, c, _RED[reduction],
+              ignore_index, ptr(ws), ws.numel(), stream())
+    return loss, total, lse
+
+
+def cross_entropy_backward(grad_out, logits, lse, target, weight=None, reduction="mean", ignore_index=-100, total_weight=None):
+    n, c = logits.shape
+    g = torch.empty_like(logits)
+    capi.call("tvk_cross_entropy_backward", dt(logits), ptr(g), ptr(grad_out), ptr(logits), ptr(lse), ptr(target), ptr(weight), ptr(total_weight), n, c,
+              _RED[reduction], ignore_index, stream())
+    return g
+
+
+SCAN = {"cumsum": capi.SCAN_SUM, "cumprod": capi.SCAN_PROD, "logcumsumexp": capi.SCAN_LOGADDEXP}
+
+
+def scan(op, x, dim):
+    assert x.is_contiguous()
+    dim %= x.dim()
+    outer, n, inner = _split(x.shape, dim)
+    out = torch.empty_like(x)
+    capi.call("tvk_scan", SCAN[op], dt(x), ptr(out), ptr(x), outer, n, inner, stream())
+    return out
+
+
 def batchnorm_forward(x, weight, bias, running_mean, running_var, momentum=0.1, eps=1e-5):
     n, c = x.shape[0], x.shape[1]
     hw = x.numel() // max(n * c, 1)

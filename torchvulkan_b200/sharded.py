@@ -8,6 +8,9 @@ r, one process per GPU (`torch.distributed`), and three ways of completing the o
   "push"       the GEMM epilogue stores every finished tile into all ranks' copies of C (peer-mapped
                pointers over NVLink, `tvk_gemm_desc.peer_c`), so the gather costs no extra pass over C and
                overlaps the tensor-core work tile by tile; one barrier orders the step.
+  "copy"       the local batches are cut into chunks; as soon as a chunk is multiplied it is copied into every
+               peer's C by the copy engines (one `tvk_memcpy_async` per chunk and peer on side streams, peers'
+               buffers mapped as for "push"), which take no SM away from the product of the next chunk.
   "pipelined"  the local batches are cut into chunks; chunk i's NCCL exchange runs on a side stream while
                chunk i+1 is multiplied.
   "allgather"  the whole local GEMM, then one NCCL all-gather: the unfused baseline.
@@ -80,7 +83,7 @@ class ShardedBmm:
     """
 
     def __init__(self, out_full: torch.Tensor, mode: str = "push", group=None, chunks: int = 4, compute=None):
-        if mode not in ("push", "pipelined", "allgather"):
+        if mode not in ("push", "copy", "pipelined", "allgather"):
             raise ValueError(f"unknown mode {mode!r}")
         self.out, self.mode, self.group = out_full, mode, group
         # without a process group this is the single-device case: one rank that owns every batch
@@ -95,9 +98,12 @@ class ShardedBmm:
         self._side = None
         self._descs = {}
         self._flag = None
-        if self.world > 1 and mode == "push":
+        self._copy_streams = []
+        if self.world > 1 and mode in ("push", "copy"):
             self._peers = PeerViews(out_full, group)
             self._flag = torch.zeros(1, device=out_full.device)
+        if self.world > 1 and mode == "copy":
+            self._copy_streams = [torch.cuda.Stream(device=out_full.device) for _ in range(self.world - 1)]
         if self.world > 1 and mode == "pipelined" and out_full.is_cuda:
             self._side = torch.cuda.Stream(device=out_full.device)
 
@@ -157,6 +163,29 @@ class ShardedBmm:
                 self._gemm(a_shard, b_shard, self.mine, peers)
             # Stream-ordered rendezvous: a rank leaves it only after every rank's GEMM, and with it every store into
             # this rank's copy, has completed.
+            dist.all_reduce(self._flag, group=self.group)
+            return self.out
+        if self.mode == "copy":
+            from . import capi
+            dist.all_reduce(self._flag, group=self.group)       # as for "push": nobody still reads the previous result
+            main = torch.cuda.current_stream()
+            esz = self.out.element_size()
+            step = max(1, (nb + self.chunks - 1) // self.chunks) if nb else 1
+            for c0 in range(0, nb, step):
+                c1 = min(c0 + step, nb)
+                self._gemm(a_shard[c0:c1], b_shard[c0:c1], self.mine[c0:c1])
+                done = torch.cuda.Event()
+                done.record(main)
+                off = (self.lo + c0) * self.out.stride(0) * esz
+                nbytes = (c1 - c0) * self.out.stride(0) * esz
+                # peers in rotated order so that the ranks do not all send to the same GPU first
+                for j in range(1, self.world):
+                    r = (self.rank + j) % self.world
+                    st = self._copy_streams[j - 1]
+                    st.wait_event(done)
+                    capi.call("tvk_memcpy_async", self._peers.ptrs[r] + off, self.out.data_ptr() + off, nbytes, st.cuda_stream)
+            for st in self._copy_streams:
+                main.wait_stream(st)
             dist.all_reduce(self._flag, group=self.group)
             return self.out
         if self.mode == "allgather":

@@ -70,6 +70,7 @@ class MLPStep:
         self.gh = [e(batch, sizes[i + 1]) for i in range(self.nl - 1)]     # grads wrt activations
         self.logp = e(batch, sizes[-1])
         self.glogp = e(batch, sizes[-1])
+        self.lse = torch.empty(batch, dtype=torch.float32, device=dev)       # row log-sum-exp of the logits (fused cross-entropy)
         self.loss = e(())
         self.total_w = e(())
         # gradient of the (scaled) loss with respect to the mean loss: backward runs on loss * loss_scale. fp16 moments of
@@ -126,7 +127,9 @@ class MLPStep:
             n = C.c_uint64(0)
             capi.call("tvk_reduce_workspace_size", 1, self.batch, self.sizes[i + 1], C.byref(n))
             need = max(need, n.value)
-        return max(need, 256)
+        n = C.c_uint64(0)
+        capi.call("tvk_cross_entropy_workspace_size", self.batch, C.byref(n))
+        return max(need, n.value, 256)
 
     def _timed(self, tag, fn):
         """Runs one launch; with `self.trace` set, brackets it with CUDA events on the launch stream."""
@@ -162,10 +165,17 @@ class MLPStep:
             if i < s.nl - 1 and not s._fused_fwd[i]:
                 s._call("tvk_unary", capi.U_GELU, dtc, s.h[i].data_ptr(), s.z[i].data_ptr(), s.z[i].numel())
         n, c = s.batch, s.sizes[-1]
-        s._call("tvk_softmax_forward", 1, dtc, dtc, s.logp.data_ptr(), s.z[-1].data_ptr(), n, c)
-        s._call("tvk_nll_loss_forward", dtc, s.loss.data_ptr(), s.total_w.data_ptr(), s.logp.data_ptr(), labels.data_ptr(), None, n, c, 1, -100)
-        s._call("tvk_nll_loss_backward", dtc, s.glogp.data_ptr(), s.one.data_ptr(), labels.data_ptr(), None, s.total_w.data_ptr(), n, c, 1, -100)
-        s._call("tvk_softmax_backward", 1, dtc, s.gz[-1].data_ptr(), s.glogp.data_ptr(), s.logp.data_ptr(), n, c)
+        if s.fused:
+            # cross-entropy as one pass over the logits each way (log_softmax + nll_loss without the table of log-probabilities)
+            s._call("tvk_cross_entropy_forward", dtc, s.loss.data_ptr(), s.total_w.data_ptr(), s.lse.data_ptr(), s.z[-1].data_ptr(), labels.data_ptr(),
+                    None, n, c, 1, -100, s._ws.data_ptr(), s._ws.numel())
+            s._call("tvk_cross_entropy_backward", dtc, s.gz[-1].data_ptr(), s.one.data_ptr(), s.z[-1].data_ptr(), s.lse.data_ptr(), labels.data_ptr(),
+                    None, s.total_w.data_ptr(), n, c, 1, -100)
+        else:
+            s._call("tvk_softmax_forward", 1, dtc, dtc, s.logp.data_ptr(), s.z[-1].data_ptr(), n, c)
+            s._call("tvk_nll_loss_forward", dtc, s.loss.data_ptr(), s.total_w.data_ptr(), s.logp.data_ptr(), labels.data_ptr(), None, n, c, 1, -100)
+            s._call("tvk_nll_loss_backward", dtc, s.glogp.data_ptr(), s.one.data_ptr(), labels.data_ptr(), None, s.total_w.data_ptr(), n, c, 1, -100)
+            s._call("tvk_softmax_backward", 1, dtc, s.gz[-1].data_ptr(), s.glogp.data_ptr(), s.logp.data_ptr(), n, c)
         for i in reversed(range(s.nl)):
             s._gemm(descs[k]); k += 1                                                    # grad W_i
             s._call("tvk_reduce", capi.R_SUM, dtc, dtc, s.gb[i].data_ptr(), s.gz[i].data_ptr(), 1, n, s.sizes[i + 1],
