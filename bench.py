@@ -214,6 +214,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     from torchvulkan_b200.workloads import MLPStep
 
     capi.lib()  # fail loudly before anything is timed if the CUDA library is missing
+    if args.profile_run and args.workload in KERNEL_WORKLOADS:
+        profile_kernels(args, dev)
+        return
     pk = peaks()
     # one list launch for AdamW over all six parameter tensors, its step count in device memory: the whole step is
     # then a fixed sequence of launches that can be replayed as a CUDA graph
@@ -542,6 +545,100 @@ def run_sharded_bmm(rank, world, dev, pk):
     return res
 
 
+KERNEL_WORKLOADS = ("k_gemm4096", "k_gemm_mlp", "k_wgrad", "k_add", "k_exp", "k_sum", "k_argmax", "k_softmax", "k_rmsnorm", "k_layernorm",
+                    "k_bn", "k_sort", "k_embedding", "k_xent")
+
+
+def profile_kernels(args, dev):
+    """--profile-run --workload k_*: warm-up + K launches of ONE kernel family at a size a profiler can capture (inputs
+    beyond L2, a few GB at most), nothing else. Prints the algorithmic bytes / flops per launch so that a profile summary
+    can put the counters next to them."""
+    import torch
+    from torchvulkan_b200 import cuda_ops as ops
+
+    w = args.workload
+    torch.manual_seed(0)
+    h = torch.float16
+    info = {}
+    if w in ("k_gemm4096", "k_gemm_mlp", "k_wgrad"):
+        m, n, k, ta, tb = {"k_gemm4096": (4096, 4096, 4096, False, False), "k_gemm_mlp": (256, 8192, 8192, False, True),
+                           "k_wgrad": (8192, 8192, 256, True, False)}[w]
+        a = torch.randn((k, m) if ta else (m, k), device=dev, dtype=h)
+        b = torch.randn((n, k) if tb else (k, n), device=dev, dtype=h)
+        A, B = (a.t() if ta else a), (b.t() if tb else b)
+        out = torch.empty(m, n, device=dev, dtype=h)
+        run = lambda: ops.gemm(A, B, out=out)  # noqa: E731
+        info = {"flops": 2.0 * m * n * k, "bytes": 2.0 * (m * k + k * n + m * n), "shape": [m, n, k]}
+    elif w in ("k_add", "k_exp", "k_sum", "k_argmax"):
+        n = 1 << 28          # 1 GiB per fp32 tensor: the code path of the 2^30 config at a quarter of its footprint
+        x = torch.randn(n, device=dev)
+        if w == "k_add":
+            y, z = torch.randn(n, device=dev), torch.empty(n, device=dev)
+            run, nbytes = (lambda: ops.binary("add", x, y, out=z)), 12 * n
+        elif w == "k_exp":
+            z = torch.empty(n, device=dev)
+            run, nbytes = (lambda: ops.unary("exp", x, out=z)), 8 * n
+        elif w == "k_sum":
+            run, nbytes = (lambda: ops.reduce("sum", x)), 4 * n
+        else:
+            run, nbytes = (lambda: ops.argreduce(x)), 4 * n
+        info = {"bytes": float(nbytes), "elements": n}
+    elif w == "k_softmax":
+        x = torch.randn(8192 * 32, 128, device=dev, dtype=h)          # the config-3 logits shape, 32x the rows (64 MiB)
+        g = torch.randn_like(x)
+        def run():
+            yv = ops.softmax(x, log=True)
+            ops.softmax_backward(g, yv, log=True)
+        info = {"bytes_fwd": 2.0 * x.numel() * 2, "bytes_bwd": 3.0 * x.numel() * 2, "shape": list(x.shape)}
+    elif w in ("k_rmsnorm", "k_layernorm"):
+        x = torch.randn(8192 * 16, 512, device=dev, dtype=h)          # config-3 rows x16 (128 MiB)
+        wt, g = torch.rand(512, device=dev, dtype=h) + 0.5, torch.randn_like(x)
+        if w == "k_rmsnorm":
+            def run():
+                yv, rstd = ops.rmsnorm_forward(x, wt)
+                ops.rmsnorm_backward(g, x, wt, rstd)
+        else:
+            bs = torch.randn(512, device=dev, dtype=h)
+            def run():
+                yv, mean, rstd = ops.layernorm_forward(x, wt, bs)
+                ops.layernorm_backward(g, x, wt, mean, rstd)
+        info = {"bytes_fwd": 2.0 * x.numel() * 2, "bytes_bwd": 3.0 * x.numel() * 2, "shape": list(x.shape)}
+    elif w == "k_bn":
+        x = torch.randn(256 * 4, 64, 32, 32, device=dev, dtype=h).contiguous(memory_format=torch.channels_last)   # config-4 stage 1, batch x4 (128 MiB)
+        wt, bs = torch.rand(64, device=dev, dtype=h) + 0.5, torch.randn(64, device=dev, dtype=h)
+        rm, rv = torch.zeros(64, device=dev, dtype=h), torch.ones(64, device=dev, dtype=h)
+        g = torch.randn_like(x)
+        def run():
+            yv, mean, invstd = ops.batchnorm_forward(x, wt, bs, rm, rv)
+            ops.batchnorm_backward(g, x, wt, mean, invstd)
+        info = {"bytes_fwd": 3.0 * x.numel() * 2, "bytes_bwd": 5.0 * x.numel() * 2, "shape": list(x.shape), "layout": "channels_last"}
+    elif w == "k_sort":
+        x = torch.randn(4096, 8192, device=dev)
+        run = lambda: ops.topk(x, 8192)  # noqa: E731
+        info = {"bytes": 4.0 * x.numel() * 4, "shape": list(x.shape)}
+    elif w == "k_embedding":
+        table = torch.randn(128, 512, device=dev, dtype=h)
+        idx = torch.randint(0, 128, (8192 * 16,), device=dev)
+        g = torch.randn(8192 * 16, 512, device=dev, dtype=h)
+        def run():
+            ops.embedding_forward(table, idx)
+            ops.embedding_backward(g, idx, 128)
+        info = {"bytes_fwd": 2.0 * idx.numel() * 512, "bytes_bwd": 2.0 * idx.numel() * 512, "shape": [idx.numel(), 512]}
+    else:   # k_xent
+        x = torch.randn(8192 * 32, 128, device=dev, dtype=h)
+        t = torch.randint(0, 128, (x.shape[0],), device=dev)
+        one = torch.ones((), device=dev, dtype=h)
+        def run():
+            loss, total, lse = ops.cross_entropy_forward(x, t)
+            ops.cross_entropy_backward(one, x, lse, t, None, "mean", -100, total)
+        info = {"bytes_fwd": 1.0 * x.numel() * 2, "bytes_bwd": 2.0 * x.numel() * 2, "shape": list(x.shape)}
+    for _ in range(args.warmup + args.steps):
+        run()
+    torch.cuda.synchronize()
+    ops.check_device_status(dev.index or 0)
+    print(json.dumps({"profile_run": True, "workload": w, "launch_groups": args.warmup + args.steps, **info}), flush=True)
+
+
 def profile_model_steps(args):
     """Warm-up + K steps of the config-3 / config-4 training script on the "vulkan" device, nothing else (for a profiler)."""
     import torch
@@ -726,8 +823,9 @@ def main():
     ap.add_argument("--extras", action="store_true", help="accepted for compatibility: the other configs are part of the default line now")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-run", action="store_true", help="only warm-up + K device-resident steps (for ncu)")
-    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c4cl"],
-                    help="with --profile-run: which BASELINE config's step to run (c4cl: config 4 in channels-last memory)")
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c4cl", *KERNEL_WORKLOADS],
+                    help="with --profile-run: which BASELINE config's step to run (c4cl: config 4 in channels-last memory), or one "
+                         "kernel family alone (k_*)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

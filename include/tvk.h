@@ -135,6 +135,11 @@ TVK_API int tvk_host_free(void* host_ptr);
 typedef int (*tvk_raw_alloc_fn)(void** ptr, uint64_t bytes);
 typedef int (*tvk_raw_free_fn)(void* ptr);
 TVK_API int tvk_debug_set_raw_allocator(tvk_raw_alloc_fn a, tvk_raw_free_fn f, int fake_device_count);
+/* Test hook for the timeout convention: launches a one-thread kernel that polls a flag nothing ever sets, gives up
+ * after `polls` tries (100 ns apart, polls <= 10^6, i.e. at most a tenth of a second) and records the time-out in the
+ * device status word exactly as the waits inside the GEMM, convolution and attention kernels do. The next
+ * tvk_check_device_status(dev) answers TVK_ERR_TIMEOUT, and the device stays usable. */
+TVK_API int tvk_debug_bounded_wait(int dev, int polls, void* stream);
 
 /* Copies (VulkanAllocator::copy_host_to_device / copy_device_to_host / copy_device_to_device,
  * src/vulkan/allocator.cpp:90-162). h2d/d2d are asynchronous on the device's compute stream;
@@ -296,6 +301,8 @@ typedef enum tvk_binary_op {
     TVK_B_SIGMOID_BACKWARD,   /* a = grad, b = y                                            */
     TVK_B_TANH_BACKWARD,      /* a = grad, b = y                                            */
     TVK_B_GELU_TANH_BACKWARD, /* a = grad, b = x (src/shaders/core/dtype.slang:745-751)     */
+    TVK_B_ADD_RELU,           /* out = relu(a + alpha*b): _add_relu, which the reference runs as add then relu
+                                 (src/api/ops/binary.cpp:655-673), in one pass; NaN propagates as in relu */
     TVK_B_COUNT_
 } tvk_binary_op;
 

@@ -530,6 +530,9 @@ def binary(op, a, b, alpha=1.0):
     with np.errstate(all="ignore"):
         if op == "add":
             return a + alpha * b
+        if op == "add_relu":        # relu(add(a, b, alpha)), src/api/ops/binary.cpp:655-657
+            v = a + alpha * b
+            return np.where(np.isnan(v), v, np.maximum(v, 0.0))
         if op == "sub":
             return a - alpha * b
         if op == "mul":

@@ -353,3 +353,22 @@ def test_adam_and_sgd_steps(cuda, dtype):
         tol = 1e-6 if dtype == torch.float32 else TOL[dtype]
         check_float(pd, rp.astype(np.float64), dtype, tol)
         check_float(bd, rb.astype(np.float64), dtype, tol)
+
+
+def test_bounded_wait_times_out_and_the_device_stays_usable(cuda):
+    """The failure convention of every device-side wait (mbarrier waits of the tensor-core kernels): a wait that runs out
+    raises the device status word, the kernel ends normally, tvk_check_device_status reports TVK_ERR_TIMEOUT once, and
+    later work on the same context is unaffected. The wait here polls a flag nothing sets, 2000 times."""
+    from torchvulkan_b200 import capi
+
+    lib = capi.lib()
+    ops().check_device_status()
+    capi.call("tvk_debug_bounded_wait", 0, 2000, ops().stream())
+    rc = lib.tvk_check_device_status(0)
+    assert rc == capi.ERR_TIMEOUT
+    msg = lib.tvk_last_error().decode()
+    assert "bounded device-side wait ran out" in msg and "site 99" in msg
+    assert lib.tvk_check_device_status(0) == capi.OK             # reported once, then cleared
+    x = cpu_randn(4096, torch.float32, 77)
+    assert torch.equal(ops().unary("neg", x.to(cuda)).cpu(), -x)  # the context still works
+    ops().check_device_status()

@@ -219,6 +219,29 @@ def test_layer_norm_group_norm_and_scans(vk, dtype, tol):
     assert torch.equal(torch.cumsum(i.to(vk), 1).cpu(), torch.cumsum(i, 1)) and torch.equal(i.to(vk).cumsum(0).cpu(), i.cumsum(0))
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.float16, 2e-3), (torch.bfloat16, 1e-2)])
+def test_addbmm_mv_dot_and_add_relu(vk, dtype, tol):
+    """The remaining matmul-shaped entry points on the same product kernel (addbmm, addmv / mv, dot:
+    src/api/decompositions.cpp:46-58, 109-124, 1114-1129) and _add_relu as one kernel (src/api/ops/binary.cpp:655-673)."""
+    torch.manual_seed(31)
+    f = lambda t: t.float()  # noqa: E731
+    b1, b2, inp = torch.randn(5, 40, 72).to(dtype), torch.randn(5, 72, 56).to(dtype), torch.randn(40, 56).to(dtype)
+    close(torch.addbmm(inp.to(vk), b1.to(vk), b2.to(vk), beta=0.5, alpha=2.0), torch.addbmm(f(inp), f(b1), f(b2), beta=0.5, alpha=2.0), tol)
+    close(torch.addbmm(inp[0].to(vk), b1.to(vk), b2.to(vk)), torch.addbmm(f(inp[0]), f(b1), f(b2)), tol)          # broadcast row
+    mat, vec, v0 = torch.randn(300, 520).to(dtype), torch.randn(520).to(dtype), torch.randn(300).to(dtype)
+    close(torch.mv(mat.to(vk), vec.to(vk)), torch.mv(f(mat), f(vec)), tol)
+    close(torch.addmv(v0.to(vk), mat.to(vk), vec.to(vk), beta=0.25, alpha=1.5), torch.addmv(f(v0), f(mat), f(vec), beta=0.25, alpha=1.5), tol)
+    close(torch.mv(mat.t()[:256].to(vk), v0[:300].to(vk)), torch.mv(f(mat.t()[:256]), f(v0[:300])), tol)          # transposed matrix
+    x, y = torch.randn(70001).to(dtype), torch.randn(70001).to(dtype)
+    ref = torch.dot(f(x), f(y))
+    assert abs(torch.dot(x.to(vk), y.to(vk)).item() - ref.item()) <= max(tol, 1e-4) * (f(x).abs() * f(y).abs()).sum().item() ** 0.5 * 4
+    a, b = torch.randn(33, 65).to(dtype), torch.randn(33, 65).to(dtype)
+    close(torch._add_relu(a.to(vk), b.to(vk)), torch.relu(f(a) + f(b)), tol)
+    c = a.to(vk).clone()
+    torch._add_relu_(c, b.to(vk), alpha=0.5)
+    close(c, torch.relu(f(a) + 0.5 * f(b)), tol)
+
+
 def make_mlp(sizes):
     layers = []
     for i in range(len(sizes) - 1):
@@ -555,3 +578,38 @@ def test_hot_ops_raise_instead_of_falling_back(vk):
         torch.ones(3, 4, device=vk) @ torch.ones(5, 6, device=vk)
     with pytest.raises((RuntimeError, NotImplementedError), match="NOT IMPLEMENTED"):
         F.conv2d(torch.ones(1, 4, 5, 5, device=vk), torch.ones(4, 2, 3, 3, device=vk), groups=2)
+
+
+def test_environment_switches_of_the_reference(vk):
+    """TORCHVULKAN_VALIDATION / TORCHVULKAN_PROFILE / TORCHVULKAN_STRICT (src/vulkan/vulkan_context.cpp:195-248) in a fresh
+    process: the checked mode counts nothing on healthy operators, counts the time-out a bounded wait leaves behind (made
+    on purpose by the test hook that polls a flag nothing sets) and the device stays usable; the NVTX ranges of the profile
+    switch and the strict switch change no result."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    code = textwrap.dedent("""
+        import torch, torchvulkan
+        from torchvulkan_b200 import capi
+        C = torchvulkan._load_backend()
+        vk = torch.device("vulkan:0")
+        x = torch.randn(300, 200).to(vk)
+        y = (x @ x.t()).relu().sum().item()
+        assert C._validation_error_count() == 0
+        capi.call("tvk_debug_bounded_wait", 0, 2000, None)       # legacy stream: ordered with the device's own stream by the check's synchronize
+        import warnings
+        with warnings.catch_warnings(record=True) as seen:
+            warnings.simplefilter("always")
+            z = (x + 1).sum().item()
+        assert C._validation_error_count() == 1, C._validation_error_count()
+        assert any("bounded device-side wait ran out" in str(w.message) for w in seen)
+        assert abs((x + 1).sum().item() - z) < 1e-3 and C._validation_error_count() == 1
+        print("ENV-OK", y)
+    """)
+    env = dict(os.environ, PYTHONPATH=str(root), TORCHVULKAN_VALIDATION="1", TORCHVULKAN_PROFILE="1", TORCHVULKAN_STRICT="1")
+    p = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0 and "ENV-OK" in p.stdout, p.stdout[-2000:] + p.stderr[-3000:]

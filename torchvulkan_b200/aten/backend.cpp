@@ -93,5 +93,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         info["has_int8"] = true;
         return info;
     });
-    m.def("_validation_error_count", []() -> uint64_t { return 0; });
+    // the number of problems the checked mode (TORCHVULKAN_VALIDATION=1) has seen: the counterpart of the reference's count of
+    // validation-layer messages (src/api/backend.cpp:127-129)
+    m.def("_validation_error_count", []() -> uint64_t { return tvk_aten::validation_error_count(); });
 }

@@ -30,6 +30,8 @@ def build(verbose: bool = False) -> Path:
     headers = list(HERE.glob("*.h")) + list((PKG.parent / "include").glob("*.h"))
     newest_header = max(h.stat().st_mtime for h in headers)
     includes = [f"-I{p}" for p in ce.include_paths()] + [f"-I{sysconfig.get_paths()['include']}"]
+    cuda_home = os.environ.get("CUDA_HOME") or "/usr/local/cuda"
+    includes.append(f"-I{cuda_home}/include")      # nvtx3 (header-only) for TORCHVULKAN_PROFILE ranges
     abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
     flags = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wno-unused-function", "-Wno-unknown-pragmas",
              f"-D_GLIBCXX_USE_CXX11_ABI={abi}", "-DTORCH_EXTENSION_NAME=_C", "-DTORCH_API_INCLUDE_EXTENSION_H"]

@@ -14,8 +14,29 @@ namespace tvk_aten {
 // (TORCH_CHECK / OutOfMemoryError, messages prefixed "torchvulkan [ERROR]:").
 void throw_status(int status, const char* what);
 
+// The reference's environment switches (src/vulkan/vulkan_context.cpp:195-248), read once:
+//   TORCHVULKAN_PROFILE=1     every C-ABI call made by an operator is wrapped in an NVTX range named after the call (the
+//                             reference captures pipeline statistics per dispatch, src/vulkan/shader.cpp:428-431)
+//   TORCHVULKAN_VALIDATION=1  checked mode: after every operator the device is synchronised and its status word and CUDA's
+//                             error state are read; problems are warned about and counted (_validation_error_count), as
+//                             the reference counts the messages of the Vulkan validation layer
+//   TORCHVULKAN_STRICT        accepted; this backend never falls back to the CPU, so it is always strict
+struct EnvFlags {
+    bool profile = false, validation = false, strict = true;
+};
+const EnvFlags& env_flags();
+uint64_t validation_error_count();
+void profile_push(const char* name);
+void profile_pop();
+struct ProfileRange {
+    explicit ProfileRange(const char* name) : on(env_flags().profile) { if (on) profile_push(name); }
+    ~ProfileRange() { if (on) profile_pop(); }
+    bool on;
+};
+
 #define TVK_CALL(expr)                                        \
     do {                                                      \
+        ::tvk_aten::ProfileRange _tvk_range(#expr);           \
         int _tvk_rc = (expr);                                 \
         if (_tvk_rc != TVK_OK) ::tvk_aten::throw_status(_tvk_rc, #expr); \
     } while (0)

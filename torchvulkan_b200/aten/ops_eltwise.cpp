@@ -135,6 +135,10 @@ at::Tensor binary_impl(int op, const at::Tensor& a_in, const at::Tensor& b_in, d
 at::Tensor add(const at::Tensor& a, const at::Tensor& b, const at::Scalar& alpha) { return binary_impl(TVK_B_ADD, a, b, alpha.toDouble(), {}, "add", true); }
 at::Tensor& add_(at::Tensor& a, const at::Tensor& b, const at::Scalar& alpha) { binary_impl(TVK_B_ADD, a, b, alpha.toDouble(), a, "add_", true); return a; }
 at::Tensor& add_out(const at::Tensor& a, const at::Tensor& b, const at::Scalar& alpha, at::Tensor& out) { binary_impl(TVK_B_ADD, a, b, alpha.toDouble(), out, "add.out", true); return out; }
+// _add_relu: the reference composes relu(add(...)) (src/api/ops/binary.cpp:655-673); one kernel here
+at::Tensor add_relu(const at::Tensor& a, const at::Tensor& b, const at::Scalar& alpha) { return binary_impl(TVK_B_ADD_RELU, a, b, alpha.toDouble(), {}, "_add_relu", false); }
+at::Tensor& add_relu_(at::Tensor& a, const at::Tensor& b, const at::Scalar& alpha) { binary_impl(TVK_B_ADD_RELU, a, b, alpha.toDouble(), a, "_add_relu_", false); return a; }
+at::Tensor& add_relu_out(const at::Tensor& a, const at::Tensor& b, const at::Scalar& alpha, at::Tensor& out) { binary_impl(TVK_B_ADD_RELU, a, b, alpha.toDouble(), out, "_add_relu.out", false); return out; }
 at::Tensor sub(const at::Tensor& a, const at::Tensor& b, const at::Scalar& alpha) { return binary_impl(TVK_B_SUB, a, b, alpha.toDouble(), {}, "sub", true); }
 at::Tensor& sub_(at::Tensor& a, const at::Tensor& b, const at::Scalar& alpha) { binary_impl(TVK_B_SUB, a, b, alpha.toDouble(), a, "sub_", true); return a; }
 at::Tensor& sub_out(const at::Tensor& a, const at::Tensor& b, const at::Scalar& alpha, at::Tensor& out) { binary_impl(TVK_B_SUB, a, b, alpha.toDouble(), out, "sub.out", true); return out; }
@@ -325,6 +329,9 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("add.Tensor", &add);
     m.impl("add_.Tensor", &add_);
     m.impl("add.out", &add_out);
+    m.impl("_add_relu.Tensor", &add_relu);
+    m.impl("_add_relu_.Tensor", &add_relu_);
+    m.impl("_add_relu.out", &add_relu_out);
     m.impl("sub.Tensor", &sub);
     m.impl("sub_.Tensor", &sub_);
     m.impl("sub.out", &sub_out);

@@ -113,6 +113,57 @@ at::Tensor addmm_activation(const at::Tensor& input, const at::Tensor& mat1, con
     return run_gemm(mat1, mat2, input, alpha.toDouble(), beta.toDouble(), use_gelu ? TVK_ACT_GELU : TVK_ACT_RELU);
 }
 
+// addbmm: beta * self + alpha * sum over the batches of batch1[b] @ batch2[b]. The sum over b is folded into the contraction
+// (addbmm_vulkan, src/api/decompositions.cpp:1114-1129): batch1 as one [n, b*k] matrix (a copy: the batch index is not a
+// plain stride of a matrix column), batch2 as [b*k, p] in place, and ONE product with the whole epilogue (alpha, beta * self).
+at::Tensor addbmm(const at::Tensor& self, const at::Tensor& batch1, const at::Tensor& batch2, const at::Scalar& beta, const at::Scalar& alpha) {
+    TORCH_CHECK(batch1.dim() == 3 && batch2.dim() == 3, "batch1 and batch2 must be 3D tensors");
+    TORCH_CHECK(batch1.size(0) == batch2.size(0), "batch1 and batch2 must have same number of batches, got ", batch1.size(0), " and ", batch2.size(0));
+    TORCH_CHECK(batch1.size(2) == batch2.size(1), "Incompatible matrix sizes for bmm (", batch1.size(1), "x", batch1.size(2), " and ", batch2.size(1), "x",
+                batch2.size(2), ")");
+    const int64_t b = batch1.size(0), n = batch1.size(1), k = batch1.size(2), p = batch2.size(2);
+    if (!is_hot_float(self.scalar_type())) TVK_NOT_IMPLEMENTED("addbmm for dtype ", self.scalar_type(), " on the vulkan device");
+    if (b == 0 || k == 0) return at::mul(self.expand({n, p}), beta).contiguous();
+    at::Tensor a2 = batch1.permute({1, 0, 2}).reshape({n, b * k});
+    at::Tensor b2 = batch2.is_contiguous() ? batch2.view({b * k, p}) : batch2.reshape({b * k, p});
+    return run_gemm(a2, b2, self, alpha.toDouble(), beta.toDouble(), TVK_ACT_NONE);
+}
+at::Tensor& addbmm_out(const at::Tensor& self, const at::Tensor& b1, const at::Tensor& b2, const at::Scalar& beta, const at::Scalar& alpha, at::Tensor& out) {
+    return fill_out(out, (addbmm)(self, b1, b2, beta, alpha));
+}
+at::Tensor& addbmm_(at::Tensor& self, const at::Tensor& b1, const at::Tensor& b2, const at::Scalar& beta, const at::Scalar& alpha) {
+    return fill_out(self, (addbmm)(self, b1, b2, beta, alpha));
+}
+
+// addmv / mv: a product with one output column (addmv_out_vulkan, src/api/decompositions.cpp:109-124); the vector and the
+// result are addressed as [k, 1] and [m, 1] views, so nothing is copied.
+at::Tensor& addmv_out(const at::Tensor& self, const at::Tensor& mat, const at::Tensor& vec, const at::Scalar& beta, const at::Scalar& alpha,
+                      at::Tensor& out) {
+    TORCH_CHECK(mat.dim() == 2 && vec.dim() == 1, "vector + matrix @ vector expected, got ", self.dim(), ", ", mat.dim(), ", ", vec.dim());
+    TORCH_CHECK(mat.size(1) == vec.size(0), "size mismatch, got input (", self.size(0), "), mat (", mat.size(0), "x", mat.size(1), "), vec (", vec.size(0), ")");
+    TORCH_CHECK(out.scalar_type() == mat.scalar_type(), "Expected out tensor to have dtype ", mat.scalar_type(), ", but got ", out.scalar_type(), " instead");
+    if (!is_hot_float(mat.scalar_type())) TVK_NOT_IMPLEMENTED("addmv for dtype ", mat.scalar_type(), " on the vulkan device");
+    const bool use_self = beta.toDouble() != 0.0;
+    at::Tensor bias = use_self ? self.expand({mat.size(0)}).unsqueeze(1) : at::Tensor();
+    at::Tensor r = mat.size(1) == 0 ? (use_self ? at::mul(self.expand({mat.size(0)}), beta).contiguous() : at::zeros({mat.size(0)}, mat.options()))
+                                    : run_gemm(mat, vec.unsqueeze(1), use_self ? c10::optional<at::Tensor>(bias) : c10::nullopt, alpha.toDouble(),
+                                               beta.toDouble(), TVK_ACT_NONE).squeeze(1);
+    return fill_out(out, r);
+}
+
+// dot: the reference multiplies and sums in fp32 (dot_vulkan, src/api/decompositions.cpp:46-58); as a [1, k] x [k, 1]
+// product the accumulation is fp32 too and nothing is materialised.
+at::Tensor dot(const at::Tensor& self, const at::Tensor& other) {
+    TORCH_CHECK(self.dim() == 1 && other.dim() == 1, "1D tensors expected, but got ", self.dim(), "D and ", other.dim(), "D tensors");
+    TORCH_CHECK(self.scalar_type() == other.scalar_type(), "dot : expected both vectors to have same dtype, but found ", self.scalar_type(), " and ",
+                other.scalar_type());
+    TORCH_CHECK(self.numel() == other.numel(), "inconsistent tensor size, expected tensor [", self.numel(), "] and src [", other.numel(),
+                "] to have the same number of elements, but got ", self.numel(), " and ", other.numel(), " elements respectively");
+    if (!is_hot_float(self.scalar_type())) TVK_NOT_IMPLEMENTED("dot for dtype ", self.scalar_type(), " on the vulkan device");
+    if (self.numel() == 0) return at::zeros({}, self.options());
+    return run_gemm(self.unsqueeze(0), other.unsqueeze(1), c10::nullopt, 1.0, 0.0, TVK_ACT_NONE).reshape({});
+}
+
 at::Tensor& mm_out(const at::Tensor& self, const at::Tensor& other, at::Tensor& out) { return fill_out(out, (mm)(self, other)); }
 at::Tensor& bmm_out(const at::Tensor& self, const at::Tensor& other, at::Tensor& out) { return fill_out(out, (bmm)(self, other)); }
 at::Tensor& addmm_out(const at::Tensor& input, const at::Tensor& m1, const at::Tensor& m2, const at::Scalar& beta, const at::Scalar& alpha,
@@ -147,6 +198,11 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("baddbmm", &baddbmm);
     m.impl("baddbmm.out", &baddbmm_out);
     m.impl("baddbmm_", &baddbmm_);
+    m.impl("addbmm", &addbmm);
+    m.impl("addbmm.out", &addbmm_out);
+    m.impl("addbmm_", &addbmm_);
+    m.impl("addmv.out", &addmv_out);
+    m.impl("dot", &dot);
     m.impl("_addmm_activation", &addmm_activation);
     m.impl("_addmm_activation.out", &addmm_activation_out);
 }

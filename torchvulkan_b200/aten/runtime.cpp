@@ -8,6 +8,11 @@
 // is one in-order compute stream per device (stream id 0), and events are device events.
 #include "common.h"
 
+#include <atomic>
+#include <cstdlib>
+
+#include <nvtx3/nvToolsExt.h>
+
 #include <ATen/core/GeneratorForPrivateuseone.h>
 #include <ATen/detail/PrivateUse1HooksInterface.h>
 #include <c10/core/CachingDeviceAllocator.h>
@@ -34,6 +39,34 @@ void throw_status(int status, const char* what) {
     TORCH_CHECK(false, msg);
 }
 
+const EnvFlags& env_flags() {
+    static const EnvFlags flags = [] {
+        auto set = [](const char* name) {
+            const char* v = std::getenv(name);
+            return v != nullptr && v[0] != '\0' && !(v[0] == '0' && v[1] == '\0');
+        };
+        EnvFlags f;
+        f.profile = set("TORCHVULKAN_PROFILE");
+        f.validation = set("TORCHVULKAN_VALIDATION");
+        f.strict = true;     // TORCHVULKAN_STRICT: there is no CPU fallback to switch off
+        return f;
+    }();
+    return flags;
+}
+
+static std::atomic<uint64_t> g_validation_errors{0};
+uint64_t validation_error_count() { return g_validation_errors.load(); }
+
+void profile_push(const char* name) {
+    // "tvk_gemm(&d, ws.ptr, ...)" -> "tvk_gemm"
+    char label[64];
+    size_t n = 0;
+    while (name[n] && name[n] != '(' && n + 1 < sizeof(label)) { label[n] = name[n]; ++n; }
+    label[n] = '\0';
+    nvtxRangePushA(label);
+}
+void profile_pop() { nvtxRangePop(); }
+
 DeviceScope::DeviceScope(c10::DeviceIndex index) {
     TVK_CALL(tvk_get_device(&previous));
     device = index < 0 ? previous : (int)index;
@@ -41,6 +74,14 @@ DeviceScope::DeviceScope(c10::DeviceIndex index) {
     TVK_CALL(tvk_get_stream(device, &stream));
 }
 DeviceScope::~DeviceScope() {
+    if (env_flags().validation) {
+        // checked mode: the operator that just ran must have left neither a device-side status nor a CUDA error behind
+        // (a destructor cannot raise: problems are warned about and counted)
+        if (tvk_check_device_status(device) != TVK_OK) {
+            g_validation_errors.fetch_add(1);
+            TORCH_WARN("torchvulkan [WARNING]: validation: ", tvk_last_error());
+        }
+    }
     if (previous != device) tvk_set_device(previous);
 }
 

@@ -18,7 +18,7 @@ ACT_NONE, ACT_RELU, ACT_GELU = range(3)
 (U_NEG, U_EXP, U_LOG, U_SQRT, U_RSQRT, U_SIGMOID, U_RELU, U_GELU, U_TANH, U_ABS, U_SILU, U_RECIPROCAL, U_SQUARE,
  U_SIN, U_COS, U_GELU_TANH) = range(16)
 (B_ADD, B_SUB, B_MUL, B_DIV, B_MAXIMUM, B_MINIMUM, B_POW, B_GELU_BACKWARD, B_THRESHOLD_BACKWARD, B_SILU_BACKWARD,
- B_SIGMOID_BACKWARD, B_TANH_BACKWARD, B_GELU_TANH_BACKWARD) = range(13)
+ B_SIGMOID_BACKWARD, B_TANH_BACKWARD, B_GELU_TANH_BACKWARD, B_ADD_RELU) = range(14)
 C_EQ, C_NE, C_LT, C_LE, C_GT, C_GE = range(6)
 T_ADDCMUL, T_ADDCDIV, T_LERP, T_WHERE = range(4)
 R_SUM, R_MEAN, R_AMAX, R_AMIN = range(4)
@@ -112,6 +112,7 @@ SIGNATURES = {
     "tvk_host_alloc": (_i, [_u64, _P(_p)]),
     "tvk_host_free": (_i, [_p]),
     "tvk_debug_set_raw_allocator": (_i, [_p, _p, _i]),
+    "tvk_debug_bounded_wait": (_i, [_i, _i, _p]),
     "tvk_memcpy_h2d": (_i, [_i, _p, _p, _u64]),
     "tvk_memcpy_d2h": (_i, [_i, _p, _p, _u64]),
     "tvk_memcpy_d2d": (_i, [_i, _p, _p, _u64]),

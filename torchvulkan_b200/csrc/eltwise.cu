@@ -34,6 +34,7 @@ template <int OP> __device__ __forceinline__ float unary_apply(float x) {
 
 template <int OP> __device__ __forceinline__ float binary_apply(float a, float b, float alpha) {
     if constexpr (OP == TVK_B_ADD) return a + alpha * b;
+    else if constexpr (OP == TVK_B_ADD_RELU) { const float v = a + alpha * b; return (v != v) ? v : fmaxf(v, 0.f); }
     else if constexpr (OP == TVK_B_SUB) return a - alpha * b;
     else if constexpr (OP == TVK_B_MUL) return a * b;
     else if constexpr (OP == TVK_B_DIV) return a / b;
@@ -583,7 +584,7 @@ template <typename F> static int dispatch_binary_op(int op, F&& f) {
 #define C(OPV) case OPV: return f(std::integral_constant<int, OPV>{});
         C(TVK_B_ADD) C(TVK_B_SUB) C(TVK_B_MUL) C(TVK_B_DIV) C(TVK_B_MAXIMUM) C(TVK_B_MINIMUM) C(TVK_B_POW)
         C(TVK_B_GELU_BACKWARD) C(TVK_B_THRESHOLD_BACKWARD) C(TVK_B_SILU_BACKWARD) C(TVK_B_SIGMOID_BACKWARD) C(TVK_B_TANH_BACKWARD)
-        C(TVK_B_GELU_TANH_BACKWARD)
+        C(TVK_B_GELU_TANH_BACKWARD) C(TVK_B_ADD_RELU)
 #undef C
         default: return set_error(TVK_ERR_INVALID, "unknown binary op %d", op);
     }

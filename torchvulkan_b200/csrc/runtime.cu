@@ -230,6 +230,23 @@ private:
     tvk_mem_stats stats_ = {};
 };
 
+// The shape of every device-side wait in this library, alone in a kernel: poll a flag (here one that nothing ever sets),
+// give up after `polls` tries, record where in the status word and leave through the normal end of the kernel.
+__device__ int g_never_set_flag = 0;
+__global__ void bounded_wait_probe_kernel(int* status, int polls) {
+    if (threadIdx.x != 0) return;
+    volatile int* flag = &g_never_set_flag;
+    for (int it = 0; it < polls; ++it) {
+        if (*flag) return;
+        __nanosleep(100);
+    }
+    if (atomicCAS(status, 0, 1) == 0) {
+        status[1] = 99;           // site: the probe
+        status[2] = (int)blockIdx.x;
+        status[3] = polls;
+    }
+}
+
 // ---- devices ------------------------------------------------------------------
 struct RngState {
     std::mutex mu;
@@ -469,6 +486,7 @@ int tvk_check_device_status(int dev) {
     if (rc) return rc;
     int* w = device_status_word();
     if (!w) return set_error(TVK_ERR_CUDA, "could not allocate the device status word");
+    if (d->alloc.capturing()) return TVK_OK;      // waiting for the device would invalidate the capture that is running
     TVK_CUDA_CHECK(cudaDeviceSynchronize());
     int host[4] = {0, 0, 0, 0};
     TVK_CUDA_CHECK(cudaMemcpy(host, w, sizeof(host), cudaMemcpyDeviceToHost));
@@ -486,6 +504,21 @@ int tvk_check_device_status(int dev) {
 }
 
 uint64_t tvk_round_size(uint64_t bytes) { return round_size(bytes); }
+
+int tvk_debug_bounded_wait(int dev, int polls, void* stream) {
+    Device* d;
+    int rc = get_dev(dev, &d);
+    if (rc) return rc;
+    TVK_REQUIRE(polls >= 1 && polls <= 1000000, "tvk_debug_bounded_wait: %d polls outside [1, 1000000]", polls);
+    if (g_fake_devices > 0) return TVK_OK;
+    DeviceScope scope;
+    rc = scope.enter(dev);
+    if (rc) return rc;
+    int* w = device_status_word();
+    if (!w) return set_error(TVK_ERR_CUDA, "could not allocate the device status word");
+    bounded_wait_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(w, polls);
+    return launch_status("bounded-wait probe");
+}
 
 int tvk_malloc(int dev, uint64_t bytes, void** ptr) {
     if (!ptr) return set_error(TVK_ERR_INVALID, "tvk_malloc: null output");

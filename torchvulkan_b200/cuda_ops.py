@@ -24,7 +24,7 @@ BINARY = {"add": capi.B_ADD, "sub": capi.B_SUB, "mul": capi.B_MUL, "div": capi.B
           "minimum": capi.B_MINIMUM, "pow": capi.B_POW, "gelu_backward": capi.B_GELU_BACKWARD,
           "threshold_backward": capi.B_THRESHOLD_BACKWARD, "silu_backward": capi.B_SILU_BACKWARD,
           "sigmoid_backward": capi.B_SIGMOID_BACKWARD, "tanh_backward": capi.B_TANH_BACKWARD,
-          "gelu_tanh_backward": capi.B_GELU_TANH_BACKWARD}
+          "gelu_tanh_backward": capi.B_GELU_TANH_BACKWARD, "add_relu": capi.B_ADD_RELU}
 COMPARE = {"eq": capi.C_EQ, "ne": capi.C_NE, "lt": capi.C_LT, "le": capi.C_LE, "gt": capi.C_GT, "ge": capi.C_GE}
 TERNARY = {"addcmul": capi.T_ADDCMUL, "addcdiv": capi.T_ADDCDIV, "lerp": capi.T_LERP, "where": capi.T_WHERE}
 REDUCE = {"sum": capi.R_SUM, "mean": capi.R_MEAN, "amax": capi.R_AMAX, "amin": capi.R_AMIN}
