@@ -194,7 +194,7 @@ def test_layer_norm_group_norm_and_scans(vk, dtype, tol):
         ln_c.weight.copy_(torch.rand(96) + 0.5); ln_c.bias.copy_(torch.randn(96))
         ln_d.weight.copy_(ln_c.weight.to(dtype)); ln_d.bias.copy_(ln_c.bias.to(dtype))
         ln_c.weight.copy_(ln_d.weight.cpu().float()); ln_c.bias.copy_(ln_d.bias.cpu().float())
-    xc, xd = x.float().requires_grad_(), x.to(vk).requires_grad_()
+    xc, xd = x.float().clone().requires_grad_(), x.detach().to(vk).requires_grad_()
     g = torch.randn(6, 17, 96).to(dtype)
     ln_d(xd).backward(g.to(vk)); ln_c(xc).backward(g.float())
     close(ln_d(xd), ln_c(xc), tol); close(xd.grad, xc.grad, tol); close(ln_d.weight.grad, ln_c.weight.grad, tol); close(ln_d.bias.grad, ln_c.bias.grad, tol)
@@ -205,7 +205,7 @@ def test_layer_norm_group_norm_and_scans(vk, dtype, tol):
         gn_c.weight.copy_(torch.rand(12) + 0.5); gn_c.bias.copy_(torch.randn(12))
         gn_d.weight.copy_(gn_c.weight.to(dtype)); gn_d.bias.copy_(gn_c.bias.to(dtype))
         gn_c.weight.copy_(gn_d.weight.cpu().float()); gn_c.bias.copy_(gn_d.bias.cpu().float())
-    ic, idv = xi.float().requires_grad_(), xi.to(vk).requires_grad_()
+    ic, idv = xi.float().clone().requires_grad_(), xi.detach().to(vk).requires_grad_()
     gi = torch.randn(4, 12, 6, 5).to(dtype)
     gn_d(idv).backward(gi.to(vk)); gn_c(ic).backward(gi.float())
     close(gn_d(idv), gn_c(ic), tol); close(idv.grad, ic.grad, tol); close(gn_d.weight.grad, gn_c.weight.grad, tol); close(gn_d.bias.grad, gn_c.bias.grad, tol)

@@ -137,19 +137,215 @@ __global__ void __launch_bounds__(kNormThreads) layernorm_bwd_kernel(T* __restri
     }
 }
 
-// out_w[c] = sum over parts of partial[part][0][c], out_b[c] = ... [1][c]
-template <typename T>
-__global__ void __launch_bounds__(256) ln_fold_kernel(T* __restrict__ out_w, T* __restrict__ out_b, const float* __restrict__ partial, int64_t nparts,
-                                                     int64_t cols) {
-    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= cols) return;
-    float sw = 0.f, sb = 0.f;
-    for (int64_t k = 0; k < nparts; ++k) {
-        sw += partial[(k * 2 + 0) * cols + c];
-        sb += partial[(k * 2 + 1) * cols + c];
+// Warp-per-row LayerNorm for rows of whole 16-byte packets, at most MAXP packets per lane (rows of up to 128 packets; longer rows take the CTA-per-row kernels): the
+// row lives in registers, both statistics are warp shuffles, every access is 128-bit, and each warp keeps R rows in
+// flight (one 1 KB row per warp leaves an SM with too few bytes outstanding to cover the memory latency).
+template <typename T, int MAXP, int R>
+__global__ void __launch_bounds__(256) layernorm_fwd_warp_kernel(T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                                const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
+                                                                int64_t rows, int cols, float eps) {
+    constexpr int N = Vec16<T>::N;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int npk = cols / N;
+    Vec16<T> wv[MAXP], bv[MAXP];
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+        const int pk = i * 32 + lane;
+        if (pk < npk) {
+            if (w) wv[i] = load16(w + (int64_t)pk * N);
+            if (b) bv[i] = load16(b + (int64_t)pk * N);
+        }
     }
-    if (out_w) out_w[c] = from_f32<T>(sw);
-    if (out_b) out_b[c] = from_f32<T>(sb);
+    const float inv_cols = 1.0f / (float)cols;
+    const int64_t stride = (int64_t)gridDim.x * 8;
+    for (int64_t row0 = (int64_t)blockIdx.x * 8 + warp; row0 < rows; row0 += stride * R) {
+        Vec16<T> xv[R][MAXP];
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int64_t row = row0 + q * stride;
+#pragma unroll
+            for (int i = 0; i < MAXP; ++i) {
+                const int pk = i * 32 + lane;
+                if (row < rows && pk < npk) xv[q][i] = load16_stream(x + row * cols + (int64_t)pk * N);
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int64_t row = row0 + q * stride;
+            if (row >= rows) continue;               // uniform across the warp
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < MAXP; ++i) {
+                if (i * 32 + lane < npk) {
+#pragma unroll
+                    for (int j = 0; j < N; ++j) s += to_f32(xv[q][i].v[j]);
+                }
+            }
+            const float mean = warp_sum(s) * inv_cols;
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < MAXP; ++i) {
+                if (i * 32 + lane < npk) {
+#pragma unroll
+                    for (int j = 0; j < N; ++j) { const float d = to_f32(xv[q][i].v[j]) - mean; ss += d * d; }
+                }
+            }
+            const float rstd = rsqrtf(warp_sum(ss) * inv_cols + eps);
+            if (lane == 0) {
+                if (mean_out) mean_out[row] = mean;
+                if (rstd_out) rstd_out[row] = rstd;
+            }
+#pragma unroll
+            for (int i = 0; i < MAXP; ++i) {
+                const int pk = i * 32 + lane;
+                if (pk < npk) {
+                    Vec16<T> o;
+#pragma unroll
+                    for (int j = 0; j < N; ++j) {
+                        float v = (to_f32(xv[q][i].v[j]) - mean) * rstd;
+                        if (w) v *= to_f32(wv[i].v[j]);
+                        if (b) v += to_f32(bv[i].v[j]);
+                        o.v[j] = from_f32<T>(v);
+                    }
+                    store16_stream(y + row * cols + (int64_t)pk * N, o);
+                }
+            }
+        }
+    }
+}
+
+// The backward pass in the same shape: each lane also keeps the grad_w / grad_b sums of the columns it owns over all the
+// rows its warp walks; the CTA's eight warps fold them through shared memory into partial[cta][2][cols].
+template <typename T, int MAXP, int R>
+__global__ void __launch_bounds__(256) layernorm_bwd_warp_kernel(T* __restrict__ gx, float* __restrict__ partial, const T* __restrict__ gy,
+                                                                const T* __restrict__ x, const T* __restrict__ w, const float* __restrict__ mean,
+                                                                const float* __restrict__ rstd, int64_t rows, int cols) {
+    constexpr int N = Vec16<T>::N;
+    __shared__ float fold[8][32 * N];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int npk = cols / N;
+    float wacc[MAXP][N], bacc[MAXP][N];
+    Vec16<T> wv[MAXP];
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) { wacc[i][j] = 0.f; bacc[i][j] = 0.f; }
+        const int pk = i * 32 + lane;
+        if (w && pk < npk) wv[i] = load16(w + (int64_t)pk * N);
+        else {
+#pragma unroll
+            for (int j = 0; j < N; ++j) wv[i].v[j] = from_f32<T>(1.f);
+        }
+    }
+    const float inv_cols = 1.0f / (float)cols;
+    const int64_t stride = (int64_t)gridDim.x * 8;
+    for (int64_t row0 = (int64_t)blockIdx.x * 8 + warp; row0 < rows; row0 += stride * R) {
+        Vec16<T> gv[R][MAXP], xv[R][MAXP];
+        float mu[R], rs[R];
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int64_t row = row0 + q * stride;
+            mu[q] = row < rows ? mean[row] : 0.f;
+            rs[q] = row < rows ? rstd[row] : 0.f;
+#pragma unroll
+            for (int i = 0; i < MAXP; ++i) {
+                const int pk = i * 32 + lane;
+                if (row < rows && pk < npk) {
+                    gv[q][i] = load16_stream(gy + row * cols + (int64_t)pk * N);
+                    xv[q][i] = load16_stream(x + row * cols + (int64_t)pk * N);
+                }
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int64_t row = row0 + q * stride;
+            if (row >= rows) continue;               // uniform across the warp
+            float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+            for (int i = 0; i < MAXP; ++i) {
+                if (i * 32 + lane < npk) {
+#pragma unroll
+                    for (int j = 0; j < N; ++j) {
+                        const float g0 = to_f32(gv[q][i].v[j]), xh = (to_f32(xv[q][i].v[j]) - mu[q]) * rs[q];
+                        const float g = g0 * to_f32(wv[i].v[j]);
+                        s1 += g;
+                        s2 += g * xh;
+                        wacc[i][j] += g0 * xh;
+                        bacc[i][j] += g0;
+                    }
+                }
+            }
+            s1 = warp_sum(s1) * inv_cols;
+            s2 = warp_sum(s2) * inv_cols;
+            if (gx) {
+#pragma unroll
+                for (int i = 0; i < MAXP; ++i) {
+                    const int pk = i * 32 + lane;
+                    if (pk < npk) {
+                        Vec16<T> o;
+#pragma unroll
+                        for (int j = 0; j < N; ++j) {
+                            const float xh = (to_f32(xv[q][i].v[j]) - mu[q]) * rs[q];
+                            o.v[j] = from_f32<T>(rs[q] * (to_f32(gv[q][i].v[j]) * to_f32(wv[i].v[j]) - s1 - xh * s2));
+                        }
+                        store16_stream(gx + row * cols + (int64_t)pk * N, o);
+                    }
+                }
+            }
+        }
+    }
+    if (!partial) return;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+#pragma unroll
+        for (int i = 0; i < MAXP; ++i) {
+            if (i * 32 * N >= cols) break;          // uniform
+            __syncthreads();
+#pragma unroll
+            for (int j = 0; j < N; ++j) fold[warp][lane * N + j] = which ? bacc[i][j] : wacc[i][j];
+            __syncthreads();
+            for (int c = threadIdx.x; c < 32 * N; c += 256) {
+                const int col = i * 32 * N + c;
+                if (col < cols) {
+                    float t = 0.f;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) t += fold[k][c];
+                    partial[((int64_t)blockIdx.x * 2 + which) * cols + col] = t;
+                }
+            }
+        }
+    }
+}
+
+// out_w[c] = sum over parts of partial[part][0][c], out_b[c] = ... [1][c]: 32 columns x 32 part-lanes per CTA, every thread
+// issues its loads together (a few hundred parts cost about one memory latency); blockIdx.y selects weight / bias.
+template <typename T>
+__global__ void __launch_bounds__(1024) ln_fold_kernel(T* __restrict__ out_w, T* __restrict__ out_b, const float* __restrict__ partial, int64_t nparts,
+                                                      int64_t cols) {
+    __shared__ float acc[32][33];
+    const int which = blockIdx.y;
+    T* out = which ? out_b : out_w;
+    if (!out) return;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int64_t c = (int64_t)blockIdx.x * 32 + tx;
+    float s = 0.f;
+    if (c < cols) {
+        for (int64_t k = ty; k < nparts; k += 32 * 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = (k + 32 * u < nparts) ? partial[((k + 32 * u) * 2 + which) * cols + c] : 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) s += v[u];
+        }
+    }
+    acc[ty][tx] = s;
+    __syncthreads();
+    if (ty == 0 && c < cols) {
+        float t = 0.f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) t += acc[k][tx];
+        out[c] = from_f32<T>(t);
+    }
 }
 
 // ---- GroupNorm backward ------------------------------------------------------------------------------------------------
@@ -206,38 +402,72 @@ __global__ void __launch_bounds__(kNormThreads) groupnorm_bwd_params_kernel(T* _
 }
 
 // ---- cross-entropy ---------------------------------------------------------------------------------------------------
-// One warp per row of `c` logits: row maximum, log-sum-exp (fp32, natural log), then the row's loss (lse - x[t]) * w[t].
-// Targets equal to ignore_index or outside [0, c) contribute nothing (src/shaders/ops/nllloss.slang:20-39).
+// G lanes per row (a power of two up to 32, chosen so that a row of c logits is about one 16-byte packet per lane), 32 / G
+// rows per warp: row maximum, log-sum-exp (fp32, natural log), then the row's loss (lse - x[t]) * w[t]. Targets equal to
+// ignore_index or outside [0, c) contribute nothing (src/shaders/ops/nllloss.slang:20-39). CTAs walk the row groups with a
+// grid stride, so the number of partial sums does not grow with n.
 // reduction 0: loss_rows[i] is the output; otherwise per-CTA partial sums of loss and weight go to part[cta][2].
+template <int OPMAX> __device__ __forceinline__ float group_reduce(float v, int G) {
+    for (int o = G >> 1; o > 0; o >>= 1) {
+        const float u = __shfl_xor_sync(0xffffffffu, v, o);
+        v = OPMAX ? fmaxf(v, u) : v + u;
+    }
+    return v;
+}
 template <typename T>
 __global__ void __launch_bounds__(256) xent_fwd_kernel(T* __restrict__ loss_rows, float* __restrict__ lse_out, float* __restrict__ part,
                                                       const T* __restrict__ logits, const int64_t* __restrict__ target, const T* __restrict__ weight,
-                                                      int64_t n, int64_t c, int64_t ignore_index) {
+                                                      int64_t n, int64_t c, int64_t ignore_index, int G, int vec) {
+    constexpr int N = Vec16<T>::N;
     __shared__ float sl[8], swt[8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t row = (int64_t)blockIdx.x * 8 + warp;
-    float loss = 0.f, wt = 0.f;
-    if (row < n) {
-        const T* p = logits + row * c;
+    const int lg = lane & (G - 1), grp = lane / G, rpw = 32 / G;
+    float loss_acc = 0.f, wt_acc = 0.f;
+    const int64_t groups = (n + rpw - 1) / rpw;
+    for (int64_t wg = (int64_t)blockIdx.x * 8 + warp; wg < groups; wg += (int64_t)gridDim.x * 8) {
+        const int64_t row = wg * rpw + grp;
+        const bool live_row = row < n;
+        const T* p = logits + (live_row ? row : 0) * c;
         float m = -INFINITY;
-        for (int64_t j = lane; j < c; j += 32) m = fmaxf(m, to_f32(p[j]));
-        m = warp_max(m);
+        if (vec) {
+            for (int64_t pk = lg; pk < c / N; pk += G) {
+                const Vec16<T> v = load16(p + pk * N);
+#pragma unroll
+                for (int j = 0; j < N; ++j) m = fmaxf(m, to_f32(v.v[j]));
+            }
+        } else {
+            for (int64_t j = lg; j < c; j += G) m = fmaxf(m, to_f32(p[j]));
+        }
+        m = group_reduce<1>(m, G);
         float s = 0.f;
-        for (int64_t j = lane; j < c; j += 32) s += expf(to_f32(p[j]) - m);
-        s = warp_sum(s);
+        if (vec) {
+            for (int64_t pk = lg; pk < c / N; pk += G) {
+                const Vec16<T> v = load16(p + pk * N);
+#pragma unroll
+                for (int j = 0; j < N; ++j) s += expf(to_f32(v.v[j]) - m);
+            }
+        } else {
+            for (int64_t j = lg; j < c; j += G) s += expf(to_f32(p[j]) - m);
+        }
+        s = group_reduce<0>(s, G);
         const float lse = m + logf(s);
-        const int64_t t = target[row];
-        if (lane == 0) {
+        if (live_row && lg == 0) {
+            const int64_t t = target[row];
+            float loss = 0.f;
             if (lse_out) lse_out[row] = lse;
             if (t != ignore_index && t >= 0 && t < c) {
-                wt = weight ? to_f32(weight[t]) : 1.f;
+                const float wt = weight ? to_f32(weight[t]) : 1.f;
                 loss = (lse - to_f32(p[t])) * wt;
+                wt_acc += wt;
             }
+            loss_acc += loss;
             if (loss_rows) loss_rows[row] = from_f32<T>(loss);
         }
     }
     if (part) {
-        if (lane == 0) { sl[warp] = loss; swt[warp] = wt; }
+        loss_acc = warp_sum(loss_acc);
+        wt_acc = warp_sum(wt_acc);
+        if (lane == 0) { sl[warp] = loss_acc; swt[warp] = wt_acc; }
         __syncthreads();
         if (threadIdx.x == 0) {
             float a = 0.f, b = 0.f;
@@ -267,23 +497,38 @@ template <typename T>
 __global__ void __launch_bounds__(256) xent_bwd_kernel(T* __restrict__ gl, const T* __restrict__ gout, const T* __restrict__ logits,
                                                       const float* __restrict__ lse, const int64_t* __restrict__ target,
                                                       const T* __restrict__ weight, const T* __restrict__ total_weight, int64_t n, int64_t c,
-                                                      int reduction, int64_t ignore_index) {
+                                                      int reduction, int64_t ignore_index, int G, int vec) {
+    constexpr int N = Vec16<T>::N;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t row = (int64_t)blockIdx.x * 8 + warp;
-    if (row >= n) return;
-    const int64_t t = target[row];
-    const bool live = t != ignore_index && t >= 0 && t < c;
-    float scale = 0.f;
-    if (live) {
-        scale = to_f32(gout[reduction == 0 ? row : 0]) * (weight ? to_f32(weight[t]) : 1.f);
-        if (reduction == 1) scale /= to_f32(total_weight[0]);
-    }
-    const float l = lse[row];
-    const T* p = logits + row * c;
-    T* o = gl + row * c;
-    for (int64_t j = lane; j < c; j += 32) {
-        const float sm = expf(to_f32(p[j]) - l);
-        o[j] = from_f32<T>(live ? (sm - (j == t ? 1.f : 0.f)) * scale : 0.f);
+    const int lg = lane & (G - 1), grp = lane / G, rpw = 32 / G;
+    const int64_t groups = (n + rpw - 1) / rpw;
+    const float inv_total = reduction == 1 ? 1.0f / to_f32(total_weight[0]) : 1.0f;
+    for (int64_t wg = (int64_t)blockIdx.x * 8 + warp; wg < groups; wg += (int64_t)gridDim.x * 8) {
+        const int64_t row = wg * rpw + grp;
+        if (row >= n) continue;
+        const int64_t t = target[row];
+        const bool live = t != ignore_index && t >= 0 && t < c;
+        float scale = 0.f;
+        if (live) scale = to_f32(gout[reduction == 0 ? row : 0]) * (weight ? to_f32(weight[t]) : 1.f) * inv_total;
+        const float l = lse[row];
+        const T* p = logits + row * c;
+        T* o = gl + row * c;
+        if (vec) {
+            for (int64_t pk = lg; pk < c / N; pk += G) {
+                Vec16<T> v = load16_stream(p + pk * N);
+#pragma unroll
+                for (int j = 0; j < N; ++j) {
+                    const float sm = expf(to_f32(v.v[j]) - l);
+                    v.v[j] = from_f32<T>(live ? (sm - ((pk * N + j) == t ? 1.f : 0.f)) * scale : 0.f);
+                }
+                store16_stream(o + pk * N, v);
+            }
+        } else {
+            for (int64_t j = lg; j < c; j += G) {
+                const float sm = expf(to_f32(p[j]) - l);
+                o[j] = from_f32<T>(live ? (sm - (j == t ? 1.f : 0.f)) * scale : 0.f);
+            }
+        }
     }
 }
 
@@ -364,9 +609,26 @@ __global__ void __launch_bounds__(256) scan_i64_kernel(int64_t* __restrict__ out
     }
 }
 
+static int xent_max_ctas() { return sm_count() * 8; }
+// lanes per row and whether rows are walked in 16-byte packets
+static void xent_shape(int dtype, const void* logits, int64_t c, int* G, int* vec) {
+    const int N = (int)(16 / dtype_size(dtype));
+    *vec = (c % N == 0) && aligned16(logits);
+    const int64_t units = *vec ? c / N : c;
+    int g = 1;
+    while (g < 32 && g < units) g <<= 1;
+    *G = g;
+}
+static int64_t xent_ctas(int64_t n, int G) {
+    const int64_t groups = (n + (32 / G) - 1) / (32 / G);
+    int64_t ctas = (groups + 7) / 8;
+    if (ctas > xent_max_ctas()) ctas = xent_max_ctas();
+    return ctas < 1 ? 1 : ctas;
+}
+
 static int ln_bwd_ctas(int64_t rows) {
-    int64_t c = (int64_t)sm_count() * 4;
-    if (c > rows) c = rows;
+    int64_t c = (int64_t)sm_count() * 2;
+    if (c > (rows + 7) / 8) c = (rows + 7) / 8;
     return (int)(c < 1 ? 1 : c);
 }
 
@@ -383,6 +645,22 @@ int tvk_layernorm_forward(int dtype, void* y, float* mean, float* rstd, const vo
     TVK_REQUIRE(y && x, "tvk_layernorm_forward: null pointer");
     TVK_REQUIRE(rows <= 0x7fffffffLL, "tvk_layernorm_forward: too many rows");
     cudaStream_t s = (cudaStream_t)stream;
+    const int64_t es = (int64_t)dtype_size(dtype);
+    const int64_t npk = es ? cols * es / 16 : 0;
+    const bool packets = es && (cols * es) % 16 == 0 && aligned16(x) && aligned16(y) && (!weight || aligned16(weight)) && (!bias || aligned16(bias));
+    if (packets && npk <= 4 * 32) {
+        // warp-per-row kernels: enough CTAs to fill the GPU a few times over, each warp walking rows with a grid stride
+        int64_t ctas = (rows + 7) / 8;
+        const int64_t cap = (int64_t)sm_count() * 8;
+        if (ctas > cap) ctas = cap;
+#define TVK_LN_FWD(MAXP_, R_)                                                                                                                       \
+    TVK_DISPATCH_FLOAT(dtype, T, (layernorm_fwd_warp_kernel<T, MAXP_, R_><<<(unsigned)ctas, 256, 0, s>>>((T*)y, mean, rstd, (const T*)x, (const T*)weight, \
+                                                                                                         (const T*)bias, rows, (int)cols, (float)eps)))
+        if (npk <= 64) { TVK_LN_FWD(2, 4); }
+        else { TVK_LN_FWD(4, 2); }
+#undef TVK_LN_FWD
+        return launch_status("layer norm forward");
+    }
     TVK_DISPATCH_FLOAT(dtype, T, (rownorm_fwd_kernel<T><<<(unsigned)rows, kNormThreads, 0, s>>>((T*)y, mean, rstd, (const T*)x, (const T*)weight, (const T*)bias,
                                                                                                 cols, (float)eps, 1, 0, 0)));
     return launch_status("layer norm forward");
@@ -419,6 +697,22 @@ int tvk_layernorm_backward(int dtype, void* grad_x, void* grad_w, void* grad_b, 
                     (unsigned long long)workspace_bytes);
         partial = (float*)workspace;
     }
+    const int64_t es = (int64_t)dtype_size(dtype);
+    const int64_t npk = cols * es / 16;
+    const bool packets = (cols * es) % 16 == 0 && aligned16(x) && aligned16(grad_y) && (!grad_x || aligned16(grad_x)) && (!weight || aligned16(weight));
+    if (packets && npk <= 4 * 32) {
+#define TVK_LN_BWDW(MAXP_, R_)                                                                                                                       \
+    TVK_DISPATCH_FLOAT(dtype, T, (layernorm_bwd_warp_kernel<T, MAXP_, R_><<<ctas, 256, 0, s>>>((T*)grad_x, partial, (const T*)grad_y, (const T*)x,   \
+                                                                                               (const T*)weight, mean, rstd, rows, (int)cols)))
+        if (npk <= 64) { TVK_LN_BWDW(2, 2); }
+        else { TVK_LN_BWDW(4, 1); }
+#undef TVK_LN_BWDW
+        if (params) {
+            const dim3 grid((unsigned)((cols + 31) / 32), 2);
+            TVK_DISPATCH_FLOAT(dtype, T, (ln_fold_kernel<T><<<grid, 1024, 0, s>>>((T*)grad_w, (T*)grad_b, partial, ctas, cols)));
+        }
+        return launch_status("layer norm backward");
+    }
     const int cpt = (int)((cols + kNormThreads - 1) / kNormThreads);
 #define TVK_LN_BWD(CPT_)                                                                                                                             \
     TVK_DISPATCH_FLOAT(dtype, T, (layernorm_bwd_kernel<T, CPT_><<<ctas, kNormThreads, 0, s>>>((T*)grad_x, partial, (const T*)grad_y, (const T*)x,   \
@@ -430,7 +724,8 @@ int tvk_layernorm_backward(int dtype, void* grad_x, void* grad_w, void* grad_b, 
     else { TVK_LN_BWD(32); }
 #undef TVK_LN_BWD
     if (params) {
-        TVK_DISPATCH_FLOAT(dtype, T, (ln_fold_kernel<T><<<(unsigned)((cols + 255) / 256), 256, 0, s>>>((T*)grad_w, (T*)grad_b, partial, ctas, cols)));
+        const dim3 grid((unsigned)((cols + 31) / 32), 2);
+        TVK_DISPATCH_FLOAT(dtype, T, (ln_fold_kernel<T><<<grid, 1024, 0, s>>>((T*)grad_w, (T*)grad_b, partial, ctas, cols)));
     }
     return launch_status("layer norm backward");
 }
@@ -475,7 +770,7 @@ int tvk_groupnorm_backward(int dtype, void* grad_x, void* grad_w, void* grad_b, 
 int tvk_cross_entropy_workspace_size(int64_t n, uint64_t* bytes) {
     if (!bytes) return set_error(TVK_ERR_INVALID, "tvk_cross_entropy_workspace_size: null output");
     TVK_REQUIRE(n >= 0, "tvk_cross_entropy_workspace_size: negative extent");
-    *bytes = (uint64_t)((n + 7) / 8) * 2 * sizeof(float);
+    *bytes = (uint64_t)xent_max_ctas() * 2 * sizeof(float);
     return TVK_OK;
 }
 
@@ -485,9 +780,10 @@ int tvk_cross_entropy_forward(int dtype, void* loss, void* total_weight, float* 
     TVK_REQUIRE(reduction >= 0 && reduction <= 2, "tvk_cross_entropy_forward: unknown reduction %d", reduction);
     TVK_REQUIRE(loss, "tvk_cross_entropy_forward: null output");
     cudaStream_t s = (cudaStream_t)stream;
-    const int64_t ctas = (n + 7) / 8;
-    TVK_REQUIRE(ctas <= 0x7fffffffLL, "tvk_cross_entropy_forward: too many rows");
     if (n > 0) TVK_REQUIRE(logits && target && c > 0, "tvk_cross_entropy_forward: null pointer or no classes");
+    int G = 1, vec = 0;
+    xent_shape(dtype, logits, c > 0 ? c : 1, &G, &vec);
+    const int64_t ctas = xent_ctas(n, G);
     float* part = nullptr;
     if (reduction != 0) {
         const uint64_t need = (uint64_t)ctas * 2 * sizeof(float);
@@ -497,10 +793,10 @@ int tvk_cross_entropy_forward(int dtype, void* loss, void* total_weight, float* 
     }
     if (n > 0) {
         TVK_DISPATCH_FLOAT(dtype, T, (xent_fwd_kernel<T><<<(unsigned)ctas, 256, 0, s>>>(reduction == 0 ? (T*)loss : nullptr, lse, part, (const T*)logits, target,
-                                                                                        (const T*)weight, n, c, ignore_index)));
+                                                                                        (const T*)weight, n, c, ignore_index, G, vec)));
     }
     if (reduction != 0) {
-        TVK_DISPATCH_FLOAT(dtype, T, (xent_finalize_kernel<T><<<1, 256, 0, s>>>((T*)loss, (T*)total_weight, part, ctas, reduction == 1)));
+        TVK_DISPATCH_FLOAT(dtype, T, (xent_finalize_kernel<T><<<1, 256, 0, s>>>((T*)loss, (T*)total_weight, part, n > 0 ? ctas : 0, reduction == 1)));
     }
     return launch_status("cross entropy forward");
 }
@@ -513,11 +809,13 @@ int tvk_cross_entropy_backward(int dtype, void* grad_logits, const void* grad_ou
     if (n == 0 || c == 0) return TVK_OK;
     TVK_REQUIRE(grad_logits && grad_out && logits && lse && target, "tvk_cross_entropy_backward: null pointer");
     TVK_REQUIRE(reduction != 1 || total_weight, "tvk_cross_entropy_backward: the mean needs total_weight");
-    const int64_t ctas = (n + 7) / 8;
-    TVK_REQUIRE(ctas <= 0x7fffffffLL, "tvk_cross_entropy_backward: too many rows");
+    int G = 1, vec = 0;
+    xent_shape(dtype, logits, c, &G, &vec);
+    if (vec && !aligned16(grad_logits)) vec = 0;
+    const int64_t ctas = xent_ctas(n, G);
     cudaStream_t s = (cudaStream_t)stream;
     TVK_DISPATCH_FLOAT(dtype, T, (xent_bwd_kernel<T><<<(unsigned)ctas, 256, 0, s>>>((T*)grad_logits, (const T*)grad_out, (const T*)logits, lse, target,
-                                                                                    (const T*)weight, (const T*)total_weight, n, c, reduction, ignore_index)));
+                                                                                    (const T*)weight, (const T*)total_weight, n, c, reduction, ignore_index, G, vec)));
     return launch_status("cross entropy backward");
 }
 

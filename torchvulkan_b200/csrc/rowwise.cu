@@ -120,9 +120,163 @@ __global__ void __launch_bounds__(256) softmax_bwd_block_kernel(T* __restrict__ 
     }
 }
 
+// Packet variants for rows of whole 16-byte packets: G lanes share a row (a power of two, about one packet per lane, at
+// most P), a warp holds 32 / G rows and keeps R such groups in flight, every access is 128-bit and the reductions are
+// shuffles inside the G lanes. Warps walk the row groups with a grid stride.
+template <bool OPMAX> __device__ __forceinline__ float lanes_reduce(float v, int G) {
+    for (int o = G >> 1; o > 0; o >>= 1) {
+        const float u = __shfl_xor_sync(0xffffffffu, v, o);
+        v = OPMAX ? fmaxf(v, u) : v + u;
+    }
+    return v;
+}
+template <typename TO, int N> __device__ __forceinline__ void store_packet(TO* q, const float (&v)[N]) {
+    constexpr int NO = Vec16<TO>::N;
+#pragma unroll
+    for (int h = 0; h < N / NO; ++h) {
+        Vec16<TO> o;
+#pragma unroll
+        for (int j = 0; j < NO; ++j) o.v[j] = from_f32<TO>(v[h * NO + j]);
+        store16_stream(q + h * NO, o);
+    }
+}
+template <typename TI, typename TO, bool LOG, int P, int R>
+__global__ void __launch_bounds__(256) softmax_fwd_vec_kernel(TO* __restrict__ out, const TI* __restrict__ in, int64_t rows, int cols, int G) {
+    constexpr int N = Vec16<TI>::N;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int lg = lane & (G - 1), grp = lane / G, rpw = 32 / G;
+    const int npk = cols / N;
+    const int64_t groups = (rows + rpw - 1) / rpw, stride = (int64_t)gridDim.x * 8;
+    for (int64_t g0 = (int64_t)blockIdx.x * 8 + warp; g0 < groups; g0 += stride * R) {
+        Vec16<TI> xv[R][P];
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int64_t row = (g0 + q * stride) * rpw + grp;
+#pragma unroll
+            for (int i = 0; i < P; ++i) {
+                const int pk = i * G + lg;
+                if (row < rows && pk < npk) xv[q][i] = load16_stream(in + row * cols + (int64_t)pk * N);
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            if (g0 + q * stride >= groups) continue;       // uniform across the warp
+            const int64_t row = (g0 + q * stride) * rpw + grp;
+            const bool live = row < rows;
+            float m = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < P; ++i) {
+                if (live && i * G + lg < npk) {
+#pragma unroll
+                    for (int j = 0; j < N; ++j) m = fmaxf(m, to_f32(xv[q][i].v[j]));
+                }
+            }
+            m = lanes_reduce<true>(m, G);
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < P; ++i) {
+                if (live && i * G + lg < npk) {
+#pragma unroll
+                    for (int j = 0; j < N; ++j) s += expf(to_f32(xv[q][i].v[j]) - m);
+                }
+            }
+            s = lanes_reduce<false>(s, G);
+            const float ls = logf(s), inv = 1.0f / s;
+#pragma unroll
+            for (int i = 0; i < P; ++i) {
+                const int pk = i * G + lg;
+                if (live && pk < npk) {
+                    float o[N];
+#pragma unroll
+                    for (int j = 0; j < N; ++j) {
+                        const float x = to_f32(xv[q][i].v[j]);
+                        o[j] = LOG ? (x - m) - ls : expf(x - m) * inv;
+                    }
+                    store_packet<TO, N>(out + row * cols + (int64_t)pk * N, o);
+                }
+            }
+        }
+    }
+}
+template <typename T, bool LOG, int P, int R>
+__global__ void __launch_bounds__(256) softmax_bwd_vec_kernel(T* __restrict__ gin, const T* __restrict__ gout, const T* __restrict__ y, int64_t rows,
+                                                             int cols, int G) {
+    constexpr int N = Vec16<T>::N;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int lg = lane & (G - 1), grp = lane / G, rpw = 32 / G;
+    const int npk = cols / N;
+    const int64_t groups = (rows + rpw - 1) / rpw, stride = (int64_t)gridDim.x * 8;
+    for (int64_t g0 = (int64_t)blockIdx.x * 8 + warp; g0 < groups; g0 += stride * R) {
+        Vec16<T> gv[R][P], yv[R][P];
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int64_t row = (g0 + q * stride) * rpw + grp;
+#pragma unroll
+            for (int i = 0; i < P; ++i) {
+                const int pk = i * G + lg;
+                if (row < rows && pk < npk) {
+                    gv[q][i] = load16_stream(gout + row * cols + (int64_t)pk * N);
+                    yv[q][i] = load16_stream(y + row * cols + (int64_t)pk * N);
+                }
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            if (g0 + q * stride >= groups) continue;       // uniform across the warp
+            const int64_t row = (g0 + q * stride) * rpw + grp;
+            const bool live = row < rows;
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < P; ++i) {
+                if (live && i * G + lg < npk) {
+#pragma unroll
+                    for (int j = 0; j < N; ++j) s += LOG ? to_f32(gv[q][i].v[j]) : to_f32(gv[q][i].v[j]) * to_f32(yv[q][i].v[j]);
+                }
+            }
+            s = lanes_reduce<false>(s, G);
+#pragma unroll
+            for (int i = 0; i < P; ++i) {
+                const int pk = i * G + lg;
+                if (live && pk < npk) {
+                    float o[N];
+#pragma unroll
+                    for (int j = 0; j < N; ++j) {
+                        const float g = to_f32(gv[q][i].v[j]), yy = to_f32(yv[q][i].v[j]);
+                        o[j] = LOG ? g - expf(yy) * s : yy * (g - s);
+                    }
+                    store_packet<T, N>(gin + row * cols + (int64_t)pk * N, o);
+                }
+            }
+        }
+    }
+}
+// Lanes per row for the packet kernels: the smallest power of two with npk <= G * 4, at least enough for one packet per lane
+// when the row has 32 or more packets. Returns 0 when the row does not fit (more than 128 packets).
+static int vec_row_lanes(int64_t npk, int* P) {
+    if (npk < 1 || npk > 128) return 0;
+    int g = 1;
+    while (g < 32 && g < npk) g <<= 1;
+    *P = (int)((npk + g - 1) / g);
+    return g;
+}
+static unsigned vec_row_ctas(int64_t rows, int G, int R) {
+    const int64_t groups = (rows + (32 / G) - 1) / (32 / G);
+    int64_t ctas = (groups + 8 * R - 1) / (8 * R);
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (ctas > cap) ctas = cap;
+    return (unsigned)(ctas < 1 ? 1 : ctas);
+}
+
 template <typename TI, typename TO, bool LOG>
 static int softmax_fwd_launch(TO* out, const TI* in, int64_t rows, int64_t cols, cudaStream_t s) {
-    if (cols <= 1024) {
+    constexpr int N = Vec16<TI>::N;
+    int P = 0;
+    const int G = (cols % N == 0 && aligned16(in) && aligned16(out)) ? vec_row_lanes(cols / N, &P) : 0;
+    if (G) {
+        if (P <= 1) softmax_fwd_vec_kernel<TI, TO, LOG, 1, 4><<<vec_row_ctas(rows, G, 4), 256, 0, s>>>(out, in, rows, (int)cols, G);
+        else if (P <= 2) softmax_fwd_vec_kernel<TI, TO, LOG, 2, 2><<<vec_row_ctas(rows, G, 2), 256, 0, s>>>(out, in, rows, (int)cols, G);
+        else softmax_fwd_vec_kernel<TI, TO, LOG, 4, 1><<<vec_row_ctas(rows, G, 1), 256, 0, s>>>(out, in, rows, (int)cols, G);
+    } else if (cols <= 1024) {
         const unsigned blocks = (unsigned)((rows + 3) / 4);
 #define L(I) softmax_fwd_warp_kernel<TI, TO, LOG, I><<<blocks, 128, 0, s>>>(out, in, rows, cols)
         if (cols <= 32) L(1); else if (cols <= 64) L(2); else if (cols <= 128) L(4); else if (cols <= 256) L(8);
@@ -136,7 +290,14 @@ static int softmax_fwd_launch(TO* out, const TI* in, int64_t rows, int64_t cols,
 
 template <typename T, bool LOG>
 static int softmax_bwd_launch(T* gin, const T* gout, const T* y, int64_t rows, int64_t cols, cudaStream_t s) {
-    if (cols <= 512) {
+    constexpr int N = Vec16<T>::N;
+    int P = 0;
+    const int G = (cols % N == 0 && aligned16(gin) && aligned16(gout) && aligned16(y)) ? vec_row_lanes(cols / N, &P) : 0;
+    if (G) {
+        if (P <= 1) softmax_bwd_vec_kernel<T, LOG, 1, 4><<<vec_row_ctas(rows, G, 4), 256, 0, s>>>(gin, gout, y, rows, (int)cols, G);
+        else if (P <= 2) softmax_bwd_vec_kernel<T, LOG, 2, 2><<<vec_row_ctas(rows, G, 2), 256, 0, s>>>(gin, gout, y, rows, (int)cols, G);
+        else softmax_bwd_vec_kernel<T, LOG, 4, 1><<<vec_row_ctas(rows, G, 1), 256, 0, s>>>(gin, gout, y, rows, (int)cols, G);
+    } else if (cols <= 512) {
         const unsigned blocks = (unsigned)((rows + 3) / 4);
 #define L(I) softmax_bwd_warp_kernel<T, LOG, I><<<blocks, 128, 0, s>>>(gin, gout, y, rows, cols)
         if (cols <= 32) L(1); else if (cols <= 64) L(2); else if (cols <= 128) L(4); else if (cols <= 256) L(8); else L(16);
@@ -235,6 +396,63 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(T* __restrict__ y, flo
     } else {
         for (int64_t c = threadIdx.x; c < cols; c += blockDim.x)
             q[c] = from_f32<T>(to_f32(p[c]) * rstd * (w ? to_f32(w[c]) : 1.f));
+    }
+}
+
+// Warp-per-row forward for rows of up to MAXP 16-byte packets per lane: the row stays in registers between the sum of
+// squares and the scaling, the reduction is a warp shuffle, and each warp keeps R rows in flight.
+template <typename T, int MAXP, int R>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_warp_kernel(T* __restrict__ y, float* __restrict__ rstd_out, const T* __restrict__ x,
+                                                              const T* __restrict__ w, int64_t rows, int cols, float eps) {
+    constexpr int N = Vec16<T>::N;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int npk = cols / N;
+    Vec16<T> wv[MAXP];
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+        const int pk = i * 32 + lane;
+        if (w && pk < npk) wv[i] = load16(w + (int64_t)pk * N);
+    }
+    const int64_t stride = (int64_t)gridDim.x * 8;
+    for (int64_t row0 = (int64_t)blockIdx.x * 8 + warp; row0 < rows; row0 += stride * R) {
+        Vec16<T> xv[R][MAXP];
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int64_t row = row0 + q * stride;
+#pragma unroll
+            for (int i = 0; i < MAXP; ++i) {
+                const int pk = i * 32 + lane;
+                if (row < rows && pk < npk) xv[q][i] = load16_stream(x + row * cols + (int64_t)pk * N);
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int64_t row = row0 + q * stride;
+            if (row >= rows) continue;               // uniform across the warp
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < MAXP; ++i) {
+                if (i * 32 + lane < npk) {
+#pragma unroll
+                    for (int j = 0; j < N; ++j) { const float f = to_f32(xv[q][i].v[j]); ss += f * f; }
+                }
+            }
+            const float rstd = rsqrtf(warp_sum(ss) / (float)cols + eps);
+            if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+            for (int i = 0; i < MAXP; ++i) {
+                const int pk = i * 32 + lane;
+                if (pk < npk) {
+                    Vec16<T> o;
+#pragma unroll
+                    for (int j = 0; j < N; ++j) {
+                        const float f = to_f32(xv[q][i].v[j]) * rstd;
+                        o.v[j] = from_f32<T>(w ? f * to_f32(wv[i].v[j]) : f);
+                    }
+                    store16_stream(y + row * cols + (int64_t)pk * N, o);
+                }
+            }
+        }
     }
 }
 
@@ -613,6 +831,18 @@ int tvk_rmsnorm_forward(int dtype, void* y, float* rstd, const void* x, const vo
     const size_t es = dtype_size(dtype);
     const int n = es ? (int)(16 / es) : 1;
     const int vec = aligned16(y) && aligned16(x) && (!weight || aligned16(weight)) && cols % n == 0;
+    const int64_t npk = cols / n;
+    if (vec && npk <= 4 * 32) {
+        int64_t ctas = (rows + 7) / 8;
+        const int64_t cap = (int64_t)sm_count() * 8;
+        if (ctas > cap) ctas = cap;
+        if (npk <= 64) {
+            TVK_DISPATCH_FLOAT(dtype, T, (rmsnorm_fwd_warp_kernel<T, 2, 4><<<(unsigned)ctas, 256, 0, s>>>((T*)y, rstd, (const T*)x, (const T*)weight, rows, (int)cols, (float)eps)));
+        } else {
+            TVK_DISPATCH_FLOAT(dtype, T, (rmsnorm_fwd_warp_kernel<T, 4, 2><<<(unsigned)ctas, 256, 0, s>>>((T*)y, rstd, (const T*)x, (const T*)weight, rows, (int)cols, (float)eps)));
+        }
+        return launch_status("rmsnorm forward");
+    }
     int threads = 32;
     while (threads < 256 && (int64_t)threads * n < cols) threads <<= 1;
     TVK_DISPATCH_FLOAT(dtype, T, (rmsnorm_fwd_kernel<T><<<(unsigned)rows, threads, 0, s>>>((T*)y, rstd, (const T*)x, (const T*)weight, cols, (float)eps, vec)));
