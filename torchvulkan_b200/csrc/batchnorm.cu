@@ -231,7 +231,9 @@ static ClGeom cl_geom(int64_t rows, int64_t c, int packet) {
     g.tpr = g.ppr < kBnThreads ? g.ppr : kBnThreads;
     g.lanes = kBnThreads / g.tpr;
     g.col_tiles = (g.ppr + g.tpr - 1) / g.tpr;
-    int64_t want = ((int64_t)sm_count() * 2 + g.col_tiles - 1) / g.col_tiles;   // two CTAs of 256 threads per SM
+    // four CTAs of 256 threads per SM: with two, an SM had 32-64 KB of loads outstanding and the kernels ran at about half
+    // of the HBM rate
+    int64_t want = ((int64_t)sm_count() * 4 + g.col_tiles - 1) / g.col_tiles;
     const int64_t max_by_rows = (rows + g.lanes - 1) / g.lanes;
     if (want > max_by_rows) want = max_by_rows;
     if (want > kClMaxSplits) want = kClMaxSplits;
@@ -263,7 +265,7 @@ __global__ void __launch_bounds__(kBnThreads) bn_cl_stats_kernel(float* __restri
         }
         const int64_t per = (rows + g.splits - 1) / g.splits;
         const int64_t r0 = (int64_t)blockIdx.y * per, r1 = (r0 + per) < rows ? (r0 + per) : rows;
-        constexpr int U = 4;   // rows in flight per thread
+        constexpr int U = MODE == 0 ? 8 : 4;   // rows in flight per thread (16 bytes each, twice that with dy)
         auto accumulate = [&](const Vec16<T>& vx, const Vec16<T>& vg) {
             if (MODE == 0) {
 #pragma unroll

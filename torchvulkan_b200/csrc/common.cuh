@@ -95,6 +95,21 @@ template <typename T> __device__ __forceinline__ void store16_stream(T* p, const
     __stcs(reinterpret_cast<uint4*>(p), v.raw);
 }
 
+// exp for row kernels that read 16-bit data: the hardware exponential (its error is far below half a unit of a 16-bit
+// result); fp32 data keeps expf.
+template <typename T> __device__ __forceinline__ float exp_for(float x) { return sizeof(T) == 2 ? __expf(x) : expf(x); }
+// 2^x by the hardware unit alone (about two units in the last place of fp32 for the small |x| used here).
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// exp(x - m) for row kernels: 16-bit data folds the subtraction and the change of base into one fused multiply-add
+// (m_log2e = m * log2(e)) ahead of the hardware exponential; fp32 data keeps expf(x - m).
+constexpr float kLog2e = 1.4426950408889634f;
+template <typename T> __device__ __forceinline__ float exp_shifted(float x, float m, float m_log2e) {
+    return sizeof(T) == 2 ? ex2_approx(fmaf(x, kLog2e, -m_log2e)) : expf(x - m);
+}
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // ---- warp / block reductions --------------------------------------------------

@@ -141,21 +141,12 @@ __global__ void __launch_bounds__(kNormThreads) layernorm_bwd_kernel(T* __restri
 // row lives in registers, both statistics are warp shuffles, every access is 128-bit, and each warp keeps R rows in
 // flight (one 1 KB row per warp leaves an SM with too few bytes outstanding to cover the memory latency).
 template <typename T, int MAXP, int R>
-__global__ void __launch_bounds__(256) layernorm_fwd_warp_kernel(T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+__global__ void __launch_bounds__(256, MAXP <= 2 ? 3 : 2) layernorm_fwd_warp_kernel(T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                                                 const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b,
                                                                 int64_t rows, int cols, float eps) {
     constexpr int N = Vec16<T>::N;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int npk = cols / N;
-    Vec16<T> wv[MAXP], bv[MAXP];
-#pragma unroll
-    for (int i = 0; i < MAXP; ++i) {
-        const int pk = i * 32 + lane;
-        if (pk < npk) {
-            if (w) wv[i] = load16(w + (int64_t)pk * N);
-            if (b) bv[i] = load16(b + (int64_t)pk * N);
-        }
-    }
     const float inv_cols = 1.0f / (float)cols;
     const int64_t stride = (int64_t)gridDim.x * 8;
     for (int64_t row0 = (int64_t)blockIdx.x * 8 + warp; row0 < rows; row0 += stride * R) {
@@ -199,12 +190,15 @@ __global__ void __launch_bounds__(256) layernorm_fwd_warp_kernel(T* __restrict__
             for (int i = 0; i < MAXP; ++i) {
                 const int pk = i * 32 + lane;
                 if (pk < npk) {
-                    Vec16<T> o;
+                    // weight and bias come from L1 at each use: holding them in registers costs a resident CTA per SM
+                    Vec16<T> o, wv, bv;
+                    if (w) wv = load16(w + (int64_t)pk * N);
+                    if (b) bv = load16(b + (int64_t)pk * N);
 #pragma unroll
                     for (int j = 0; j < N; ++j) {
                         float v = (to_f32(xv[q][i].v[j]) - mean) * rstd;
-                        if (w) v *= to_f32(wv[i].v[j]);
-                        if (b) v += to_f32(bv[i].v[j]);
+                        if (w) v *= to_f32(wv.v[j]);
+                        if (b) v += to_f32(bv.v[j]);
                         o.v[j] = from_f32<T>(v);
                     }
                     store16_stream(y + row * cols + (int64_t)pk * N, o);
@@ -217,7 +211,7 @@ __global__ void __launch_bounds__(256) layernorm_fwd_warp_kernel(T* __restrict__
 // The backward pass in the same shape: each lane also keeps the grad_w / grad_b sums of the columns it owns over all the
 // rows its warp walks; the CTA's eight warps fold them through shared memory into partial[cta][2][cols].
 template <typename T, int MAXP, int R>
-__global__ void __launch_bounds__(256) layernorm_bwd_warp_kernel(T* __restrict__ gx, float* __restrict__ partial, const T* __restrict__ gy,
+__global__ void __launch_bounds__(256, MAXP <= 2 ? 2 : 1) layernorm_bwd_warp_kernel(T* __restrict__ gx, float* __restrict__ partial, const T* __restrict__ gy,
                                                                 const T* __restrict__ x, const T* __restrict__ w, const float* __restrict__ mean,
                                                                 const float* __restrict__ rstd, int64_t rows, int cols) {
     constexpr int N = Vec16<T>::N;
@@ -478,6 +472,146 @@ __global__ void __launch_bounds__(256) xent_fwd_kernel(T* __restrict__ loss_rows
         }
     }
 }
+// Packet variants of the two kernels above for rows of up to P packets per lane: the row is read once into registers, and
+// each warp keeps R row groups in flight (with a single 16-byte load per lane outstanding the kernels are bound by memory
+// latency at about a fifth of the HBM rate).
+template <typename T, int P, int R>
+__global__ void __launch_bounds__(256) xent_fwd_vec_kernel(T* __restrict__ loss_rows, float* __restrict__ lse_out, float* __restrict__ part,
+                                                          const T* __restrict__ logits, const int64_t* __restrict__ target,
+                                                          const T* __restrict__ weight, int64_t n, int c, int64_t ignore_index, int G) {
+    constexpr int N = Vec16<T>::N;
+    __shared__ float sl[8], swt[8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int lg = lane & (G - 1), grp = lane / G, rpw = 32 / G;
+    const int npk = c / N;
+    float loss_acc = 0.f, wt_acc = 0.f;
+    const int64_t groups = (n + rpw - 1) / rpw, stride = (int64_t)gridDim.x * 8;
+    for (int64_t g0 = ((int64_t)blockIdx.x * 8 + warp) * R; g0 < groups; g0 += stride * R) {
+        Vec16<T> xv[R][P];
+        int64_t tg[R];
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int64_t row = (g0 + q) * rpw + grp;
+            tg[q] = (row < n && lg == 0) ? target[row] : -1;
+#pragma unroll
+            for (int i = 0; i < P; ++i) {
+                const int pk = i * G + lg;
+                if (row < n && pk < npk) xv[q][i] = load16_stream(logits + row * c + (int64_t)pk * N);
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            if (g0 + q >= groups) continue;       // uniform across the warp
+            const int64_t row = (g0 + q) * rpw + grp;
+            const bool live_row = row < n;
+            float m = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < P; ++i) {
+                if (live_row && i * G + lg < npk) {
+#pragma unroll
+                    for (int j = 0; j < N; ++j) m = fmaxf(m, to_f32(xv[q][i].v[j]));
+                }
+            }
+            m = group_reduce<1>(m, G);
+            const float m2 = m * kLog2e;
+            float sum = 0.f;
+#pragma unroll
+            for (int i = 0; i < P; ++i) {
+                if (live_row && i * G + lg < npk) {
+#pragma unroll
+                    for (int j = 0; j < N; ++j) sum += exp_shifted<T>(to_f32(xv[q][i].v[j]), m, m2);
+                }
+            }
+            sum = group_reduce<0>(sum, G);
+            const float lse = m + logf(sum);
+            if (live_row && lg == 0) {
+                const int64_t t = tg[q];
+                float loss = 0.f;
+                if (lse_out) lse_out[row] = lse;
+                if (t != ignore_index && t >= 0 && t < c) {
+                    const float wt = weight ? to_f32(weight[t]) : 1.f;
+                    loss = (lse - to_f32(logits[row * c + t])) * wt;     // the row was just read: an L1 / L2 hit
+                    wt_acc += wt;
+                }
+                loss_acc += loss;
+                if (loss_rows) loss_rows[row] = from_f32<T>(loss);
+            }
+        }
+    }
+    if (part) {
+        loss_acc = warp_sum(loss_acc);
+        wt_acc = warp_sum(wt_acc);
+        if (lane == 0) { sl[warp] = loss_acc; swt[warp] = wt_acc; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float a = 0.f, b = 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { a += sl[k]; b += swt[k]; }
+            part[(int64_t)blockIdx.x * 2] = a;
+            part[(int64_t)blockIdx.x * 2 + 1] = b;
+        }
+    }
+}
+template <typename T, int P, int R>
+__global__ void __launch_bounds__(256) xent_bwd_vec_kernel(T* __restrict__ gl, const T* __restrict__ gout, const T* __restrict__ logits,
+                                                          const float* __restrict__ lse, const int64_t* __restrict__ target,
+                                                          const T* __restrict__ weight, const T* __restrict__ total_weight, int64_t n, int c,
+                                                          int reduction, int64_t ignore_index, int G) {
+    constexpr int N = Vec16<T>::N;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int lg = lane & (G - 1), grp = lane / G, rpw = 32 / G;
+    const int npk = c / N;
+    const int64_t groups = (n + rpw - 1) / rpw, stride = (int64_t)gridDim.x * 8;
+    const float inv_total = reduction == 1 ? 1.0f / to_f32(total_weight[0]) : 1.0f;
+    const float g_all = reduction == 0 ? 0.f : to_f32(gout[0]);
+    for (int64_t g0 = ((int64_t)blockIdx.x * 8 + warp) * R; g0 < groups; g0 += stride * R) {
+        Vec16<T> xv[R][P];
+        int64_t tg[R];
+        float ls[R], gr[R];
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int64_t row = (g0 + q) * rpw + grp;
+            const bool in = row < n;
+            tg[q] = in ? target[row] : -1;
+            ls[q] = in ? lse[row] : 0.f;
+            gr[q] = (in && reduction == 0) ? to_f32(gout[row]) : g_all;
+#pragma unroll
+            for (int i = 0; i < P; ++i) {
+                const int pk = i * G + lg;
+                if (in && pk < npk) xv[q][i] = load16_stream(logits + row * c + (int64_t)pk * N);
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int64_t row = (g0 + q) * rpw + grp;
+            if (row >= n) continue;
+            const int64_t t = tg[q];
+            const bool live = t != ignore_index && t >= 0 && t < c;
+            const float scale = live ? gr[q] * (weight ? to_f32(weight[t]) : 1.f) * inv_total : 0.f;
+            const int tt = live ? (int)t : -1;
+            const float l2 = ls[q] * kLog2e;
+#pragma unroll
+            for (int i = 0; i < P; ++i) {
+                const int pk = i * G + lg;
+                if (pk < npk) {
+                    Vec16<T> o;
+                    if (live) {
+                        const int tp = tt - pk * N;      // position of the target inside this packet, if it is there
+#pragma unroll
+                        for (int j = 0; j < N; ++j) {
+                            const float sm = exp_shifted<T>(to_f32(xv[q][i].v[j]), ls[q], l2);
+                            o.v[j] = from_f32<T>((sm - (j == tp ? 1.f : 0.f)) * scale);
+                        }
+                    } else {
+                        o.raw = make_uint4(0, 0, 0, 0);
+                    }
+                    store16_stream(gl + row * c + (int64_t)pk * N, o);
+                }
+            }
+        }
+    }
+}
+
 // loss = sum(part loss) [/ sum(part weight) for the mean]; total_weight also returned (nll_loss_forward's second output).
 template <typename T>
 __global__ void __launch_bounds__(256) xent_finalize_kernel(T* __restrict__ loss, T* __restrict__ total_weight, const float* __restrict__ part,
@@ -610,19 +744,20 @@ __global__ void __launch_bounds__(256) scan_i64_kernel(int64_t* __restrict__ out
 }
 
 static int xent_max_ctas() { return sm_count() * 8; }
-// lanes per row and whether rows are walked in 16-byte packets
+// lanes per row (the smallest power of two that leaves at most four packets, or elements, per lane) and whether rows are
+// walked in 16-byte packets
 static void xent_shape(int dtype, const void* logits, int64_t c, int* G, int* vec) {
     const int N = (int)(16 / dtype_size(dtype));
     *vec = (c % N == 0) && aligned16(logits);
     const int64_t units = *vec ? c / N : c;
     int g = 1;
-    while (g < 32 && g < units) g <<= 1;
+    while (g < 32 && (int64_t)g * 4 < units) g <<= 1;
     *G = g;
 }
-static int64_t xent_ctas(int64_t n, int G) {
+static int64_t xent_ctas(int64_t n, int G, int per_sm) {
     const int64_t groups = (n + (32 / G) - 1) / (32 / G);
     int64_t ctas = (groups + 7) / 8;
-    if (ctas > xent_max_ctas()) ctas = xent_max_ctas();
+    if (ctas > (int64_t)sm_count() * per_sm) ctas = (int64_t)sm_count() * per_sm;
     return ctas < 1 ? 1 : ctas;
 }
 
@@ -783,7 +918,7 @@ int tvk_cross_entropy_forward(int dtype, void* loss, void* total_weight, float* 
     if (n > 0) TVK_REQUIRE(logits && target && c > 0, "tvk_cross_entropy_forward: null pointer or no classes");
     int G = 1, vec = 0;
     xent_shape(dtype, logits, c > 0 ? c : 1, &G, &vec);
-    const int64_t ctas = xent_ctas(n, G);
+    const int64_t ctas = xent_ctas(n, G, 8);      // the partial sums are sized for eight CTAs per SM
     float* part = nullptr;
     if (reduction != 0) {
         const uint64_t need = (uint64_t)ctas * 2 * sizeof(float);
@@ -791,7 +926,15 @@ int tvk_cross_entropy_forward(int dtype, void* loss, void* total_weight, float* 
                     (unsigned long long)need, (unsigned long long)workspace_bytes);
         part = (float*)workspace;
     }
-    if (n > 0) {
+    const int64_t npk = vec ? c / (int64_t)(16 / dtype_size(dtype)) : 0;
+    const int P = vec ? (int)((npk + G - 1) / G) : 0;
+    if (n > 0 && vec && P <= 4 && c <= 0x7fffffffLL) {
+#define TVK_XENT_FWD(P_, R_)                                                                                                                          \
+    TVK_DISPATCH_FLOAT(dtype, T, (xent_fwd_vec_kernel<T, P_, R_><<<(unsigned)ctas, 256, 0, s>>>(reduction == 0 ? (T*)loss : nullptr, lse, part, (const T*)logits, \
+                                                                                                target, (const T*)weight, n, (int)c, ignore_index, G)))
+        if (P <= 1) { TVK_XENT_FWD(1, 4); } else if (P <= 2) { TVK_XENT_FWD(2, 2); } else { TVK_XENT_FWD(4, 1); }
+#undef TVK_XENT_FWD
+    } else if (n > 0) {
         TVK_DISPATCH_FLOAT(dtype, T, (xent_fwd_kernel<T><<<(unsigned)ctas, 256, 0, s>>>(reduction == 0 ? (T*)loss : nullptr, lse, part, (const T*)logits, target,
                                                                                         (const T*)weight, n, c, ignore_index, G, vec)));
     }
@@ -812,8 +955,19 @@ int tvk_cross_entropy_backward(int dtype, void* grad_logits, const void* grad_ou
     int G = 1, vec = 0;
     xent_shape(dtype, logits, c, &G, &vec);
     if (vec && !aligned16(grad_logits)) vec = 0;
-    const int64_t ctas = xent_ctas(n, G);
+    const int64_t ctas = xent_ctas(n, G, 32);
     cudaStream_t s = (cudaStream_t)stream;
+    const int64_t npk = vec ? c / (int64_t)(16 / dtype_size(dtype)) : 0;
+    const int P = vec ? (int)((npk + G - 1) / G) : 0;
+    if (vec && P <= 4 && c <= 0x7fffffffLL) {
+#define TVK_XENT_BWD(P_, R_)                                                                                                                          \
+    TVK_DISPATCH_FLOAT(dtype, T, (xent_bwd_vec_kernel<T, P_, R_><<<(unsigned)ctas, 256, 0, s>>>((T*)grad_logits, (const T*)grad_out, (const T*)logits, lse, target, \
+                                                                                                (const T*)weight, (const T*)total_weight, n, (int)c, reduction,     \
+                                                                                                ignore_index, G)))
+        if (P <= 1) { TVK_XENT_BWD(1, 4); } else if (P <= 2) { TVK_XENT_BWD(2, 2); } else { TVK_XENT_BWD(4, 1); }
+#undef TVK_XENT_BWD
+        return launch_status("cross entropy backward");
+    }
     TVK_DISPATCH_FLOAT(dtype, T, (xent_bwd_kernel<T><<<(unsigned)ctas, 256, 0, s>>>((T*)grad_logits, (const T*)grad_out, (const T*)logits, lse, target,
                                                                                     (const T*)weight, (const T*)total_weight, n, c, reduction, ignore_index, G, vec)));
     return launch_status("cross entropy backward");

@@ -121,8 +121,8 @@ __global__ void __launch_bounds__(256) softmax_bwd_block_kernel(T* __restrict__ 
 }
 
 // Packet variants for rows of whole 16-byte packets: G lanes share a row (a power of two, about one packet per lane, at
-// most P), a warp holds 32 / G rows and keeps R such groups in flight, every access is 128-bit and the reductions are
-// shuffles inside the G lanes. Warps walk the row groups with a grid stride.
+// most P), a warp holds 32 / G rows and keeps R consecutive such groups in flight, every access is 128-bit and the
+// reductions are shuffles inside the G lanes. Warps walk the row groups with a grid stride.
 template <bool OPMAX> __device__ __forceinline__ float lanes_reduce(float v, int G) {
     for (int o = G >> 1; o > 0; o >>= 1) {
         const float u = __shfl_xor_sync(0xffffffffu, v, o);
@@ -147,11 +147,11 @@ __global__ void __launch_bounds__(256) softmax_fwd_vec_kernel(TO* __restrict__ o
     const int lg = lane & (G - 1), grp = lane / G, rpw = 32 / G;
     const int npk = cols / N;
     const int64_t groups = (rows + rpw - 1) / rpw, stride = (int64_t)gridDim.x * 8;
-    for (int64_t g0 = (int64_t)blockIdx.x * 8 + warp; g0 < groups; g0 += stride * R) {
+    for (int64_t g0 = ((int64_t)blockIdx.x * 8 + warp) * R; g0 < groups; g0 += stride * R) {
         Vec16<TI> xv[R][P];
 #pragma unroll
         for (int q = 0; q < R; ++q) {
-            const int64_t row = (g0 + q * stride) * rpw + grp;
+            const int64_t row = (g0 + q) * rpw + grp;
 #pragma unroll
             for (int i = 0; i < P; ++i) {
                 const int pk = i * G + lg;
@@ -160,8 +160,8 @@ __global__ void __launch_bounds__(256) softmax_fwd_vec_kernel(TO* __restrict__ o
         }
 #pragma unroll
         for (int q = 0; q < R; ++q) {
-            if (g0 + q * stride >= groups) continue;       // uniform across the warp
-            const int64_t row = (g0 + q * stride) * rpw + grp;
+            if (g0 + q >= groups) continue;       // uniform across the warp
+            const int64_t row = (g0 + q) * rpw + grp;
             const bool live = row < rows;
             float m = -INFINITY;
 #pragma unroll
@@ -172,12 +172,13 @@ __global__ void __launch_bounds__(256) softmax_fwd_vec_kernel(TO* __restrict__ o
                 }
             }
             m = lanes_reduce<true>(m, G);
+            const float m2 = m * kLog2e;
             float s = 0.f;
 #pragma unroll
             for (int i = 0; i < P; ++i) {
                 if (live && i * G + lg < npk) {
 #pragma unroll
-                    for (int j = 0; j < N; ++j) s += expf(to_f32(xv[q][i].v[j]) - m);
+                    for (int j = 0; j < N; ++j) s += exp_shifted<TI>(to_f32(xv[q][i].v[j]), m, m2);
                 }
             }
             s = lanes_reduce<false>(s, G);
@@ -190,7 +191,7 @@ __global__ void __launch_bounds__(256) softmax_fwd_vec_kernel(TO* __restrict__ o
 #pragma unroll
                     for (int j = 0; j < N; ++j) {
                         const float x = to_f32(xv[q][i].v[j]);
-                        o[j] = LOG ? (x - m) - ls : expf(x - m) * inv;
+                        o[j] = LOG ? (x - m) - ls : exp_shifted<TI>(x, m, m2) * inv;
                     }
                     store_packet<TO, N>(out + row * cols + (int64_t)pk * N, o);
                 }
@@ -206,11 +207,11 @@ __global__ void __launch_bounds__(256) softmax_bwd_vec_kernel(T* __restrict__ gi
     const int lg = lane & (G - 1), grp = lane / G, rpw = 32 / G;
     const int npk = cols / N;
     const int64_t groups = (rows + rpw - 1) / rpw, stride = (int64_t)gridDim.x * 8;
-    for (int64_t g0 = (int64_t)blockIdx.x * 8 + warp; g0 < groups; g0 += stride * R) {
+    for (int64_t g0 = ((int64_t)blockIdx.x * 8 + warp) * R; g0 < groups; g0 += stride * R) {
         Vec16<T> gv[R][P], yv[R][P];
 #pragma unroll
         for (int q = 0; q < R; ++q) {
-            const int64_t row = (g0 + q * stride) * rpw + grp;
+            const int64_t row = (g0 + q) * rpw + grp;
 #pragma unroll
             for (int i = 0; i < P; ++i) {
                 const int pk = i * G + lg;
@@ -222,8 +223,8 @@ __global__ void __launch_bounds__(256) softmax_bwd_vec_kernel(T* __restrict__ gi
         }
 #pragma unroll
         for (int q = 0; q < R; ++q) {
-            if (g0 + q * stride >= groups) continue;       // uniform across the warp
-            const int64_t row = (g0 + q * stride) * rpw + grp;
+            if (g0 + q >= groups) continue;       // uniform across the warp
+            const int64_t row = (g0 + q) * rpw + grp;
             const bool live = row < rows;
             float s = 0.f;
 #pragma unroll
@@ -242,7 +243,7 @@ __global__ void __launch_bounds__(256) softmax_bwd_vec_kernel(T* __restrict__ gi
 #pragma unroll
                     for (int j = 0; j < N; ++j) {
                         const float g = to_f32(gv[q][i].v[j]), yy = to_f32(yv[q][i].v[j]);
-                        o[j] = LOG ? g - expf(yy) * s : yy * (g - s);
+                        o[j] = LOG ? g - exp_for<T>(yy) * s : yy * (g - s);
                     }
                     store_packet<T, N>(gin + row * cols + (int64_t)pk * N, o);
                 }
@@ -250,19 +251,20 @@ __global__ void __launch_bounds__(256) softmax_bwd_vec_kernel(T* __restrict__ gi
         }
     }
 }
-// Lanes per row for the packet kernels: the smallest power of two with npk <= G * 4, at least enough for one packet per lane
-// when the row has 32 or more packets. Returns 0 when the row does not fit (more than 128 packets).
+// Lanes per row for the packet kernels: the smallest power of two that leaves at most four packets per lane (measured on
+// 128-column fp16 rows: four packets of one row per lane ran at 5.7 TB/s, one packet per lane with four row groups in
+// flight at 3.9). Returns 0 when the row does not fit (more than 128 packets).
 static int vec_row_lanes(int64_t npk, int* P) {
     if (npk < 1 || npk > 128) return 0;
     int g = 1;
-    while (g < 32 && g < npk) g <<= 1;
+    while (g < 32 && (int64_t)g * 4 < npk) g <<= 1;
     *P = (int)((npk + g - 1) / g);
     return g;
 }
-static unsigned vec_row_ctas(int64_t rows, int G, int R) {
+static unsigned vec_row_ctas(int64_t rows, int G, int R, int per_sm) {
     const int64_t groups = (rows + (32 / G) - 1) / (32 / G);
     int64_t ctas = (groups + 8 * R - 1) / (8 * R);
-    const int64_t cap = (int64_t)sm_count() * 8;
+    const int64_t cap = (int64_t)sm_count() * per_sm;
     if (ctas > cap) ctas = cap;
     return (unsigned)(ctas < 1 ? 1 : ctas);
 }
@@ -273,9 +275,9 @@ static int softmax_fwd_launch(TO* out, const TI* in, int64_t rows, int64_t cols,
     int P = 0;
     const int G = (cols % N == 0 && aligned16(in) && aligned16(out)) ? vec_row_lanes(cols / N, &P) : 0;
     if (G) {
-        if (P <= 1) softmax_fwd_vec_kernel<TI, TO, LOG, 1, 4><<<vec_row_ctas(rows, G, 4), 256, 0, s>>>(out, in, rows, (int)cols, G);
-        else if (P <= 2) softmax_fwd_vec_kernel<TI, TO, LOG, 2, 2><<<vec_row_ctas(rows, G, 2), 256, 0, s>>>(out, in, rows, (int)cols, G);
-        else softmax_fwd_vec_kernel<TI, TO, LOG, 4, 1><<<vec_row_ctas(rows, G, 1), 256, 0, s>>>(out, in, rows, (int)cols, G);
+        if (P <= 1) softmax_fwd_vec_kernel<TI, TO, LOG, 1, 4><<<vec_row_ctas(rows, G, 4, 16), 256, 0, s>>>(out, in, rows, (int)cols, G);
+        else if (P <= 2) softmax_fwd_vec_kernel<TI, TO, LOG, 2, 2><<<vec_row_ctas(rows, G, 2, 16), 256, 0, s>>>(out, in, rows, (int)cols, G);
+        else softmax_fwd_vec_kernel<TI, TO, LOG, 4, 1><<<vec_row_ctas(rows, G, 1, 32), 256, 0, s>>>(out, in, rows, (int)cols, G);
     } else if (cols <= 1024) {
         const unsigned blocks = (unsigned)((rows + 3) / 4);
 #define L(I) softmax_fwd_warp_kernel<TI, TO, LOG, I><<<blocks, 128, 0, s>>>(out, in, rows, cols)
@@ -294,9 +296,9 @@ static int softmax_bwd_launch(T* gin, const T* gout, const T* y, int64_t rows, i
     int P = 0;
     const int G = (cols % N == 0 && aligned16(gin) && aligned16(gout) && aligned16(y)) ? vec_row_lanes(cols / N, &P) : 0;
     if (G) {
-        if (P <= 1) softmax_bwd_vec_kernel<T, LOG, 1, 4><<<vec_row_ctas(rows, G, 4), 256, 0, s>>>(gin, gout, y, rows, (int)cols, G);
-        else if (P <= 2) softmax_bwd_vec_kernel<T, LOG, 2, 2><<<vec_row_ctas(rows, G, 2), 256, 0, s>>>(gin, gout, y, rows, (int)cols, G);
-        else softmax_bwd_vec_kernel<T, LOG, 4, 1><<<vec_row_ctas(rows, G, 1), 256, 0, s>>>(gin, gout, y, rows, (int)cols, G);
+        if (P <= 1) softmax_bwd_vec_kernel<T, LOG, 1, 4><<<vec_row_ctas(rows, G, 4, 8), 256, 0, s>>>(gin, gout, y, rows, (int)cols, G);
+        else if (P <= 2) softmax_bwd_vec_kernel<T, LOG, 2, 2><<<vec_row_ctas(rows, G, 2, 8), 256, 0, s>>>(gin, gout, y, rows, (int)cols, G);
+        else softmax_bwd_vec_kernel<T, LOG, 4, 1><<<vec_row_ctas(rows, G, 1, 32), 256, 0, s>>>(gin, gout, y, rows, (int)cols, G);
     } else if (cols <= 512) {
         const unsigned blocks = (unsigned)((rows + 3) / 4);
 #define L(I) softmax_bwd_warp_kernel<T, LOG, I><<<blocks, 128, 0, s>>>(gin, gout, y, rows, cols)
@@ -512,7 +514,7 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(T* __restrict__ gx, fl
 // MAXP = 16-byte packets per lane (cols <= MAXP * 32 packets), R = rows a warp keeps in flight: with one 512-column row
 // per warp an SM had 32 KB of loads outstanding, which bounds the kernel by latency, not bandwidth.
 template <typename T, int MAXP, int R>
-__global__ void __launch_bounds__(256) rmsnorm_bwd_warp_kernel(T* __restrict__ gx, float* __restrict__ partial_w, const T* __restrict__ gy,
+__global__ void __launch_bounds__(256, (MAXP * R <= 4) ? 2 : 1) rmsnorm_bwd_warp_kernel(T* __restrict__ gx, float* __restrict__ partial_w, const T* __restrict__ gy,
                                                               const T* __restrict__ x, const T* __restrict__ w, const float* __restrict__ rstd,
                                                               int64_t rows, int cols) {
     constexpr int N = Vec16<T>::N;
@@ -667,6 +669,43 @@ __global__ void embedding_fwd_kernel(T* __restrict__ out, const T* __restrict__ 
         }
     } else {
         for (int64_t c = threadIdx.x; c < dim; c += blockDim.x) q[c] = ok ? p[c] : from_f32<T>(0.f);
+    }
+}
+
+// Warp-per-index gather for rows of whole 16-byte packets: each warp reads R indices, then copies the R table rows with R
+// packets per lane in flight (one CTA per index with a single dependent load chain reached about a quarter of the HBM
+// write rate on long index lists). Out-of-range indices write zeros and record (index position, value) in the status word.
+template <typename T, int R>
+__global__ void __launch_bounds__(256) embedding_fwd_warp_kernel(T* __restrict__ out, const T* __restrict__ table, const int64_t* __restrict__ idx,
+                                                                int64_t num_idx, int64_t num_rows, int64_t dim, int* status) {
+    constexpr int N = Vec16<T>::N;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t npk = dim / N, stride = (int64_t)gridDim.x * 8;
+    for (int64_t i0 = (int64_t)blockIdx.x * 8 + warp; i0 < num_idx; i0 += stride * R) {
+        const T* p[R];
+        bool ok[R];
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int64_t i = i0 + q * stride;
+            const int64_t r = i < num_idx ? idx[i] : 0;
+            ok[q] = r >= 0 && r < num_rows;
+            if (!ok[q] && lane == 0 && status) {
+                if (atomicCAS(status, 0, 2) == 0) { status[1] = 1; status[2] = (int)i; status[3] = (int)r; }
+            }
+            p[q] = table + (ok[q] ? r : 0) * dim;
+        }
+        for (int64_t k = lane; k < npk; k += 32) {
+            Vec16<T> v[R];
+#pragma unroll
+            for (int q = 0; q < R; ++q) {
+                if (ok[q]) v[q] = load16(p[q] + k * N); else v[q].raw = make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int q = 0; q < R; ++q) {
+                const int64_t i = i0 + q * stride;
+                if (i < num_idx) store16_stream(out + i * dim + k * N, v[q]);
+            }
+        }
     }
 }
 
@@ -886,7 +925,7 @@ int tvk_rmsnorm_backward(int dtype, void* grad_x, void* grad_w, const void* grad
         nparts = (int)(want < 1 ? 1 : want);
         const int64_t lane_packets = (cols * (int64_t)dtype_size(dtype) / 16 + 31) / 32;      // packets per lane
         if (lane_packets <= 2) {
-            TVK_DISPATCH_FLOAT(dtype, T, (rmsnorm_bwd_warp_kernel<T, 2, 4><<<nparts, 256, 0, s>>>((T*)grad_x, partial, (const T*)grad_y, (const T*)x, (const T*)weight, rstd, rows, (int)cols)));
+            TVK_DISPATCH_FLOAT(dtype, T, (rmsnorm_bwd_warp_kernel<T, 2, 2><<<nparts, 256, 0, s>>>((T*)grad_x, partial, (const T*)grad_y, (const T*)x, (const T*)weight, rstd, rows, (int)cols)));
         } else if (lane_packets <= 4) {
             TVK_DISPATCH_FLOAT(dtype, T, (rmsnorm_bwd_warp_kernel<T, 4, 2><<<nparts, 256, 0, s>>>((T*)grad_x, partial, (const T*)grad_y, (const T*)x, (const T*)weight, rstd, rows, (int)cols)));
         } else {
@@ -916,6 +955,14 @@ int tvk_embedding_forward(int dtype, void* out, const void* table, const int64_t
     while (threads < 256 && (int64_t)threads * n < dim) threads <<= 1;
     int* status = device_status_word();
     // The copy does not interpret the values: run it on same-width integer types.
+    if (vec && num_idx >= 1024) {
+        int64_t ctas = (num_idx + 31) / 32;
+        const int64_t cap = (int64_t)sm_count() * 8;
+        if (ctas > cap) ctas = cap;
+        if (es == 2) embedding_fwd_warp_kernel<__half, 4><<<(unsigned)ctas, 256, 0, s>>>((__half*)out, (const __half*)table, idx, num_idx, num_rows, dim, status);
+        else embedding_fwd_warp_kernel<float, 4><<<(unsigned)ctas, 256, 0, s>>>((float*)out, (const float*)table, idx, num_idx, num_rows, dim, status);
+        return launch_status("embedding forward");
+    }
     if (es == 2) embedding_fwd_kernel<__half><<<(unsigned)num_idx, threads, 0, s>>>((__half*)out, (const __half*)table, idx, num_idx, num_rows, dim, vec, status);
     else embedding_fwd_kernel<float><<<(unsigned)num_idx, threads, 0, s>>>((float*)out, (const float*)table, idx, num_idx, num_rows, dim, vec, status);
     return launch_status("embedding forward");
