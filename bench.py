@@ -527,12 +527,19 @@ def run_sharded_bmm(rank, world, dev, pk):
             if not ok:
                 failed.append(mode)
         best = min(modes, key=lambda m: modes[m]["ms_per_step"])
+        # context for the NVLink bound: the library all-gather of the same bytes with no GEMM at all (what the link delivers
+        # when every GPU sends and receives at once, against the one-directional 770 GB/s the bound is computed from)
+        ms_ag = None
+        if 64 % world == 0:
+            mine = Cfull[lo:hi]
+            ms_ag = timed(lambda: dist.all_gather_into_tensor(Cfull.view(-1), mine.reshape(-1)))
         # the slower of the tensor-core time of the local GEMM and the NVLink time of the bytes each GPU must receive
         link_ms = recv / 770e9 * 1e3
         target = max(nb * 2 * 4096 ** 3 / (pk["bf16_tflops_sustained"] * 1e12) * 1e3, link_ms)
         res.update({"modes": modes, "best_mode": best, "ms_per_step": modes[best]["ms_per_step"], "tflops_total": modes[best]["tflops_total"],
                     "verified": not failed, "bytes_received_per_gpu": recv, "nvlink_ms_at_770GBs": link_ms, "roofline_target_ms": target,
                     "frac_of_roofline": target / modes[best]["ms_per_step"],
+                    "ms_nccl_allgather_only": ms_ag, "nccl_allgather_only_ingest_gbs": (recv / ms_ag / 1e6) if ms_ag else None,
                     "collective": {"allgather": "ncclAllGather after the GEMM", "pipelined": "NCCL send/recv of chunk i under the GEMM of chunk i+1",
                                    "copy": "chunk i copied into every peer's C by the copy engines under the GEMM of chunk i+1, then a 4-byte all-reduce",
                                    "push": "GEMM epilogue stores each tile into every peer's C over NVLink, then a 4-byte all-reduce"}})

@@ -558,6 +558,12 @@ TVK_API int tvk_conv2d_backward_input(const tvk_conv2d_desc* desc, void* dx, con
                                       void* workspace, uint64_t workspace_bytes, void* stream);
 TVK_API int tvk_conv2d_backward_weight(const tvk_conv2d_desc* desc, void* dw, const void* dy, const void* x,
                                        void* workspace, uint64_t workspace_bytes, void* stream);
+/* Both gradients of one convolution in one call, as the reference's convolution_backward_vulkan computes them
+ * (src/api/ops/conv.cpp:1126-1172): an NCHW dy is brought into the kernels' channels-last layout once for the two
+ * products instead of once in each. dx or dw may be null (that gradient is skipped). Workspace: mode 3 of
+ * tvk_conv2d_workspace_size. The results are bit-identical to the two separate calls. */
+TVK_API int tvk_conv2d_backward(const tvk_conv2d_desc* desc, void* dx, void* dw, const void* dy, const void* x, const void* w,
+                                void* workspace, uint64_t workspace_bytes, void* stream);
 
 /* Stable sort of every line of a contiguous [lines, n] view and top-k as "sort then take k"
  * (src/api/ops/sort.cpp:19-140): order by value (descending if `descending`), NaN largest,

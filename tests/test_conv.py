@@ -29,7 +29,8 @@ def test_descriptor_validation():
     n = C.c_uint64(0)
     ok = capi.Conv2dDesc(capi.F16, 2, 3, 8, 8, 4, 3, 3, 1, 1, 1, 1, 1, 1, 1)
     assert lib.tvk_conv2d_workspace_size(C.byref(ok), 0, C.byref(n)) == 0 and n.value > 0
-    assert lib.tvk_conv2d_workspace_size(C.byref(ok), 3, C.byref(n)) == 1
+    assert lib.tvk_conv2d_workspace_size(C.byref(ok), 3, C.byref(n)) == 0 and n.value > 0      # both gradients in one call
+    assert lib.tvk_conv2d_workspace_size(C.byref(ok), 4, C.byref(n)) == 1
     for field, value in (("groups", 2), ("dilation_h", 2), ("stride_h", 3), ("dtype", capi.I64), ("kh", 9)):
         d = capi.Conv2dDesc(capi.F16, 2, 3, 8, 8, 4, 3, 3, 1, 1, 1, 1, 1, 1, 1)
         setattr(d, field, value)
@@ -100,6 +101,17 @@ def test_conv2d_against_oracle(cuda, shape, dtype):
     assert rel_fro(f64(y), oracle.conv2d_forward(f64(x), f64(wt), st, pd)) < tol
     assert rel_fro(f64(gx), oracle.conv2d_backward_input(f64(gy), f64(wt), x.shape, st, pd)) < tol
     assert rel_fro(f64(gw), oracle.conv2d_backward_weight(f64(gy), f64(x), wt.shape, st, pd)) < tol
+    # both gradients in one call (dy transposed once for the two products): the same bits, and each alone as well
+    gx2, gw2 = ops.conv2d_backward(gyd, xd, wd, st, pd)
+    assert torch.equal(gx2, gx) and torch.equal(gw2, gw)
+    gx3, none = ops.conv2d_backward(gyd, xd, wd, st, pd, need_dw=False)
+    none2, gw3 = ops.conv2d_backward(gyd, xd, wd, st, pd, need_dx=False)
+    assert none is None and none2 is None and torch.equal(gx3, gx) and torch.equal(gw3, gw)
+    # a channels-last dy with NCHW x (the layouts are independent)
+    gx4, gw4 = ops.conv2d_backward(gyd.contiguous(memory_format=torch.channels_last), xd, wd, st, pd)
+    assert not gx4.is_contiguous(memory_format=torch.channels_last) or gx4.is_contiguous()
+    assert torch.equal(gx4, gx) and torch.equal(gw4, gw)
+    ops.check_device_status()
 
 
 @pytest.mark.gpu

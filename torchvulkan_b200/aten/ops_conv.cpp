@@ -72,25 +72,20 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> convolution_backward(const at::Te
                 input.scalar_type());
     DeviceScope scope(gy);
     at::Tensor gx, gw, gb;
-    if (output_mask[0]) {
+    if (output_mask[0] || output_mask[1]) {
         at::Tensor w = dense4(weight);
-        gx = empty4(input.sizes(), input, x_cl);
+        // dx follows x, dw follows w (whose layout the kernels read as it is)
+        if (output_mask[0]) gx = empty4(input.sizes(), input, x_cl);
+        if (output_mask[1]) gw = empty4(weight.sizes(), weight, w_cl);
         d.layout = (x_cl ? TVK_CONV_X_CHANNELS_LAST : 0) | (y_cl ? TVK_CONV_Y_CHANNELS_LAST : 0) | (is_channels_last(w) ? TVK_CONV_W_CHANNELS_LAST : 0);
-        if (gx.numel()) {
+        const bool want_gx = output_mask[0] && gx.numel() > 0;
+        if (want_gx || output_mask[1]) {
             uint64_t ws_bytes = 0;
-            TVK_CALL(tvk_conv2d_workspace_size(&d, 1, &ws_bytes));
+            TVK_CALL(tvk_conv2d_workspace_size(&d, 3, &ws_bytes));
             Workspace ws(scope.device, ws_bytes);
-            TVK_CALL(tvk_conv2d_backward_input(&d, gx.data_ptr(), gy.data_ptr(), w.data_ptr(), ws.ptr, ws.bytes, scope.stream));
+            TVK_CALL(tvk_conv2d_backward(&d, want_gx ? gx.data_ptr() : nullptr, output_mask[1] ? gw.data_ptr() : nullptr, gy.data_ptr(), xin.data_ptr(),
+                                         w.data_ptr(), ws.ptr, ws.bytes, scope.stream));
         }
-    }
-    if (output_mask[1]) {
-        const at::Tensor& x = xin;
-        gw = empty4(weight.sizes(), weight, w_cl);
-        d.layout = (x_cl ? TVK_CONV_X_CHANNELS_LAST : 0) | (y_cl ? TVK_CONV_Y_CHANNELS_LAST : 0) | (w_cl ? TVK_CONV_W_CHANNELS_LAST : 0);
-        uint64_t ws_bytes = 0;
-        TVK_CALL(tvk_conv2d_workspace_size(&d, 2, &ws_bytes));
-        Workspace ws(scope.device, ws_bytes);
-        TVK_CALL(tvk_conv2d_backward_weight(&d, gw.data_ptr(), gy.data_ptr(), x.data_ptr(), ws.ptr, ws.bytes, scope.stream));
     }
     if (output_mask[2]) gb = gy.sum(at::IntArrayRef({0, 2, 3}));
     return std::make_tuple(gx, gw, gb);

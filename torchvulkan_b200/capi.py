@@ -184,6 +184,7 @@ SIGNATURES = {
     "tvk_conv2d_forward": (_i, [_P(Conv2dDesc), _p, _p, _p, _p, _u64, _p]),
     "tvk_conv2d_backward_input": (_i, [_P(Conv2dDesc), _p, _p, _p, _p, _u64, _p]),
     "tvk_conv2d_backward_weight": (_i, [_P(Conv2dDesc), _p, _p, _p, _p, _u64, _p]),
+    "tvk_conv2d_backward": (_i, [_P(Conv2dDesc), _p, _p, _p, _p, _p, _p, _u64, _p]),
     "tvk_attention_workspace_size": (_i, [_i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _P(_u64)]),
     "tvk_attention_forward": (_i, [_i, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _d, _i, _p, _u64, _p]),
     "tvk_attention_backward": (_i, [_i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _d, _i, _p, _u64, _p]),

@@ -112,12 +112,6 @@ static void to_nhwc(T* dst, const T* src, int64_t N, int64_t C, int64_t HW, int6
     dim3 grid((unsigned)((HW + 31) / 32), (unsigned)((Cp + 31) / 32), (unsigned)N), block(32, 8);
     nchw_to_nhwc_kernel<T><<<grid, block, 0, s>>>(dst, src, (int)C, (int)HW, (int)Cp);
 }
-template <typename T>
-static void to_nchw(T* dst, const T* src, int64_t N, int64_t C, int64_t HW, int64_t Cp, cudaStream_t s) {
-    dim3 grid((unsigned)((HW + 31) / 32), (unsigned)((C + 31) / 32), (unsigned)N), block(32, 8);
-    nhwc_to_nchw_kernel<T><<<grid, block, 0, s>>>(dst, src, (int)C, (int)HW, (int)Cp);
-}
-
 // The channels-last tensor the kernels read, and its channel pitch: the caller's own buffer when it is already
 // channels-last with a pitch the TMA accepts (a multiple of 16 bytes), else a copy in `stage` with the channels
 // padded to `Cpad` (from NCHW: a transpose; from a narrow channels-last tensor: zero channels appended).
@@ -336,14 +330,24 @@ int tvk_conv2d_workspace_size(const tvk_conv2d_desc* d, int mode, uint64_t* byte
     if (rc) return rc;
     const uint64_t x_b = a256((uint64_t)g.N * g.H * g.W * g.Cip * 2), dy_b = a256((uint64_t)g.N * g.Ho * g.Wo * g.Cop * 2);
     const uint64_t w_b = a256((uint64_t)g.Cop * g.taps() * g.Cip * 2);   // covers [O, taps, Ip] and [I, taps, Op]
-    if (mode == 0) *bytes = x_b + w_b + a256((uint64_t)g.N * g.Ho * g.Wo * g.Co * 2);
-    else if (mode == 1) *bytes = dy_b + w_b + a256((uint64_t)g.N * g.H * g.W * g.Ci * 2);
+    if (mode == 0) *bytes = x_b + w_b;          // staged input and packed filter; the output is written in place
+    else if (mode == 1) *bytes = dy_b + w_b;
     else if (mode == 2) {
         const WgradPlan w = plan_wgrad(g);
         uint64_t splits = (uint64_t)w.splits;
         if (halo_eligible(g, g.Cip, g.Co) && (uint64_t)plan_halo_wgrad(g).splits > splits) splits = (uint64_t)plan_halo_wgrad(g).splits;
         *bytes = x_b + dy_b + a256(splits * g.taps() * g.Co * g.Cip * 4);
-    } else return set_error(TVK_ERR_INVALID, "tvk_conv2d_workspace_size: mode must be 0 (forward), 1 (input gradient) or 2 (weight gradient)");
+    } else if (mode == 3) {
+        // both gradients in one call: dy staged channels-last once, then the larger of the two workspaces
+        tvk_conv2d_desc d2 = *d;
+        d2.layout |= TVK_CONV_Y_CHANNELS_LAST;
+        uint64_t b1 = 0, b2 = 0;
+        int rc1 = tvk_conv2d_workspace_size(&d2, 1, &b1);
+        if (rc1) return rc1;
+        rc1 = tvk_conv2d_workspace_size(&d2, 2, &b2);
+        if (rc1) return rc1;
+        *bytes = dy_b + (b1 > b2 ? b1 : b2);
+    } else return set_error(TVK_ERR_INVALID, "tvk_conv2d_workspace_size: mode must be 0 (forward), 1 (input gradient), 2 (weight gradient) or 3 (both gradients)");
     return TVK_OK;
 }
 
@@ -368,7 +372,7 @@ int tvk_conv2d_forward(const tvk_conv2d_desc* d, void* y, const void* x, const v
     cudaStream_t s = (cudaStream_t)stream;
     uint16_t* xs = (uint16_t*)workspace;
     uint16_t* wp = (uint16_t*)((uint8_t*)xs + a256((uint64_t)g.N * g.H * g.W * g.Cip * 2));
-    uint16_t* ys = (uint16_t*)((uint8_t*)workspace + need - a256((uint64_t)g.N * g.Ho * g.Wo * g.Co * 2));
+    uint16_t* ys = nullptr;
     int64_t x_pitch = 0;
     const uint16_t* xa = stage_act((d->layout & TVK_CONV_X_CHANNELS_LAST) != 0, x, xs, g.N, g.Ci, g.H * g.W, g.Cip, &x_pitch, s);
     if ((d->layout & TVK_CONV_W_CHANNELS_LAST) && g.Cip == g.Ci && ((uintptr_t)w & 15) == 0) {
@@ -378,15 +382,16 @@ int tvk_conv2d_forward(const tvk_conv2d_desc* d, void* y, const void* x, const v
         pack_filter_kernel<uint16_t><<<sm_count() * 2, 256, 0, s>>>(wp, (const uint16_t*)w, (int)g.Co, (int)g.Ci, g.taps(), (int)g.Cip, 0,
                                                                     (d->layout & TVK_CONV_W_CHANNELS_LAST) ? 1 : 0);
     }
-    const bool y_direct = (d->layout & TVK_CONV_Y_CHANNELS_LAST) != 0;   // the kernel's own output layout
-    if (y_direct) ys = (uint16_t*)y;
+    // the kernels write the caller's tensor themselves in either layout (their native channels-last rows, or NCHW planes
+    // from the epilogue: a lane is a pixel, so a channel's stores run along the plane)
+    const int y_nchw = (d->layout & TVK_CONV_Y_CHANNELS_LAST) ? 0 : 1;
+    ys = (uint16_t*)y;
     if (halo_eligible(g, g.Cip, g.Co)) {
         HaloParams hp = {};
         for (int t = 0; t < 9; ++t) { hp.dh[t] = (int8_t)(t / 3 - 1); hp.dw[t] = (int8_t)(t % 3 - 1); hp.wtap[t] = (int16_t)t; }
-        hp.OC = (int)g.Co; hp.Cout = (int)g.Co; hp.out = ys;
+        hp.OC = (int)g.Co; hp.Cout = (int)g.Co; hp.out = ys; hp.out_nchw = y_nchw;
         rc = run_halo(d->dtype, xa, g.N, g.H, g.W, x_pitch, wp, g.Co, hp, s);
         if (rc) return rc;
-        if (!y_direct) to_nchw<uint16_t>((uint16_t*)y, ys, g.N, g.Co, g.Ho * g.Wo, g.Co, s);
         return launch_status("conv2d forward");
     }
     FwdParams p = {};
@@ -399,10 +404,9 @@ int tvk_conv2d_forward(const tvk_conv2d_desc* d, void* y, const void* x, const v
             p.dh[t] = (int8_t)(kh - g.ph); p.dw[t] = (int8_t)(kw - g.pw); p.wtap[t] = (int16_t)t;
         }
     p.OH = (int)g.Ho; p.OW = (int)g.Wo; p.os = 1; p.oh0 = 0; p.ow0 = 0; p.OC = (int)g.Co; p.Cout = (int)g.Co;
-    p.out = ys;
+    p.out = ys; p.out_nchw = y_nchw;
     rc = run_fwd(d->dtype, xa, g.N, g.H, g.W, x_pitch, wp, g.Co, (int64_t)g.taps() * g.Cip, p, s);
     if (rc) return rc;
-    if (!y_direct) to_nchw<uint16_t>((uint16_t*)y, ys, g.N, g.Co, g.Ho * g.Wo, g.Co, s);
     return launch_status("conv2d forward");
 }
 
@@ -421,22 +425,20 @@ int tvk_conv2d_backward_input(const tvk_conv2d_desc* d, void* dx, const void* dy
     cudaStream_t s = (cudaStream_t)stream;
     uint16_t* dys = (uint16_t*)workspace;
     uint16_t* wp = (uint16_t*)((uint8_t*)dys + a256((uint64_t)g.N * g.Ho * g.Wo * g.Cop * 2));
-    const uint64_t dx_b = a256((uint64_t)g.N * g.H * g.W * g.Ci * 2);
-    uint16_t* dxs = (uint16_t*)((uint8_t*)workspace + need - dx_b);
+    uint16_t* dxs = nullptr;
     int64_t dy_pitch = 0;
     const uint16_t* dya = stage_act((d->layout & TVK_CONV_Y_CHANNELS_LAST) != 0, dy, dys, g.N, g.Co, g.Ho * g.Wo, g.Cop, &dy_pitch, s);
     pack_filter_kernel<uint16_t><<<sm_count() * 2, 256, 0, s>>>(wp, (const uint16_t*)w, (int)g.Co, (int)g.Ci, g.taps(), (int)g.Cop, 1,
                                                                 (d->layout & TVK_CONV_W_CHANNELS_LAST) ? 1 : 0);
-    const bool dx_direct = (d->layout & TVK_CONV_X_CHANNELS_LAST) != 0;
-    if (dx_direct) dxs = (uint16_t*)dx;
+    const int dx_nchw = (d->layout & TVK_CONV_X_CHANNELS_LAST) ? 0 : 1;
+    dxs = (uint16_t*)dx;
     if (halo_eligible(g, g.Cop, g.Ci)) {
         // dx[h, w] = sum over taps of dy[h + 1 - kh, w + 1 - kw] * w[:, :, kh, kw]^T
         HaloParams hp = {};
         for (int t = 0; t < 9; ++t) { hp.dh[t] = (int8_t)(1 - t / 3); hp.dw[t] = (int8_t)(1 - t % 3); hp.wtap[t] = (int16_t)t; }
-        hp.OC = (int)g.Ci; hp.Cout = (int)g.Ci; hp.out = dxs;
+        hp.OC = (int)g.Ci; hp.Cout = (int)g.Ci; hp.out = dxs; hp.out_nchw = dx_nchw;
         rc = run_halo(d->dtype, dya, g.N, g.Ho, g.Wo, dy_pitch, wp, g.Ci, hp, s);
         if (rc) return rc;
-        if (!dx_direct) to_nchw<uint16_t>((uint16_t*)dx, dxs, g.N, g.Ci, g.H * g.W, g.Ci, s);
         return launch_status("conv2d input gradient");
     }
     const int S = (int)g.s;
@@ -474,12 +476,11 @@ int tvk_conv2d_backward_input(const tvk_conv2d_desc* d, void* dx, const void* dy
             if (nt == 0) continue;
             p.ntaps = nt;
             p.OH = (int)g.H; p.OW = (int)g.W; p.os = S; p.oh0 = php; p.ow0 = pwp; p.OC = (int)g.Ci; p.Cout = (int)g.Ci;
-            p.out = dxs;
+            p.out = dxs; p.out_nchw = dx_nchw;
             rc = run_fwd(d->dtype, dya, g.N, g.Ho, g.Wo, dy_pitch, wp, g.Ci, (int64_t)g.taps() * g.Cop, p, s);
             if (rc) return rc;
         }
     }
-    if (!dx_direct) to_nchw<uint16_t>((uint16_t*)dx, dxs, g.N, g.Ci, g.H * g.W, g.Ci, s);
     return launch_status("conv2d input gradient");
 }
 
@@ -550,6 +551,40 @@ int tvk_conv2d_backward_weight(const tvk_conv2d_desc* d, void* dw, const void* d
     if (d->dtype == TVK_F16) wgrad_finalize_kernel<__half><<<(unsigned)blocks, 256, 0, s>>>((__half*)dw, partial, p.splits, p.ntaps, p.O, p.I, p.Ip, dw_cl);
     else wgrad_finalize_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, s>>>((__nv_bfloat16*)dw, partial, p.splits, p.ntaps, p.O, p.I, p.Ip, dw_cl);
     return launch_status("conv2d weight gradient");
+}
+
+int tvk_conv2d_backward(const tvk_conv2d_desc* d, void* dx, void* dw, const void* dy, const void* x, const void* w, void* workspace,
+                        uint64_t workspace_bytes, void* stream) {
+    if (!d) return set_error(TVK_ERR_INVALID, "tvk_conv2d_backward: null descriptor");
+    TVK_REQUIRE(dx || dw, "tvk_conv2d_backward: neither gradient requested");
+    tvk_conv2d_desc d2 = *d;
+    const void* dy_used = dy;
+    uint8_t* ws = (uint8_t*)workspace;
+    uint64_t left = workspace_bytes;
+    if (d->dtype != TVK_F32) {
+        Geo g;
+        int rc = make_geo(d, &g);
+        if (rc) return rc;
+        TVK_CONV_WS_CHECK(3, "tvk_conv2d_backward");
+        // an NCHW dy would be transposed by each of the two kernels' staging: do it once here and hand both the channels-last copy
+        if (dx && dw && g.N > 0 && dy && !(d->layout & TVK_CONV_Y_CHANNELS_LAST) && g.Co % 8 == 0) {
+            to_nhwc<uint16_t>((uint16_t*)ws, (const uint16_t*)dy, g.N, g.Co, g.Ho * g.Wo, g.Co, (cudaStream_t)stream);
+            dy_used = ws;
+            d2.layout |= TVK_CONV_Y_CHANNELS_LAST;
+        }
+        const uint64_t dy_b = a256((uint64_t)g.N * g.Ho * g.Wo * g.Cop * 2);
+        ws += dy_b;
+        left -= dy_b;
+    }
+    if (dx) {
+        int rc = tvk_conv2d_backward_input(&d2, dx, dy_used, w, ws, left, stream);
+        if (rc) return rc;
+    }
+    if (dw) {
+        int rc = tvk_conv2d_backward_weight(&d2, dw, dy_used, x, ws, left, stream);
+        if (rc) return rc;
+    }
+    return TVK_OK;
 }
 
 }  // extern "C"

@@ -34,7 +34,8 @@ struct HaloParams {
     int8_t dh[9], dw[9];             // input offset of tap t (rows, columns), each in [-1, 1]
     int16_t wtap[9];                 // which 64-column block of the packed filter tap t multiplies
     int OC, Cout;                    // output channel pitch and count (<= 64)
-    void* out;                       // channels-last [N, H, W, OC]
+    void* out;                       // channels-last [N, H, W, OC], or [N, Cout, H, W] when out_nchw is set
+    int out_nchw;                    // the epilogue writes the caller's NCHW tensor itself (no staged copy, no transpose launch)
     int dtype;
     uint32_t idesc;
     int* status;
@@ -145,7 +146,7 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     } else {
         const int lane_window = (warp & 3) * 32;
         // full 64-channel rows of a 64-channel-pitch output go through this warp's staging rows for 128-byte line stores
-        const bool staged = p.Cout == 64 && p.OC == 64 && ((uintptr_t)p.out & 15) == 0;
+        const bool staged = !p.out_nchw && p.Cout == 64 && p.OC == 64 && ((uintptr_t)p.out & 15) == 0;
         uint8_t* stg = (uint8_t*)bars + 256 + (warp - 2) * (32 * kStagingPitch);
         bool ok = true;
         int64_t it = 0;
@@ -177,7 +178,16 @@ conv3x3_halo_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
                         else { __nv_bfloat162 hh = __floats2bfloat162_rn(a, b); packed[j] = *(uint32_t*)&hh; }
                     }
                     uint16_t* dst = orow + c0;
-                    if (staged) {
+                    if (p.out_nchw) {
+                        // a lane is a pixel: per channel the eight pixels of a tile row are 16 contiguous bytes of the plane
+                        const int64_t plane = (int64_t)p.H * p.W;
+                        uint16_t* q = (uint16_t*)p.out + ((int64_t)n * p.Cout + c0) * plane + (int64_t)h * p.W + w;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (2 * j < ncols) q[(int64_t)(2 * j) * plane] = (uint16_t)(packed[j] & 0xffffu);
+                            if (2 * j + 1 < ncols) q[(int64_t)(2 * j + 1) * plane] = (uint16_t)(packed[j] >> 16);
+                        }
+                    } else if (staged) {
 #pragma unroll
                         for (int j = 0; j < 16; j += 4)
                             *(uint4*)(stg + lane * kStagingPitch + c0 * 2 + j * 4) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);

@@ -112,8 +112,10 @@ struct FwdParams {
     int8_t dh[kMaxTaps], dw[kMaxTaps];
     int16_t wtap[kMaxTaps];          // index of the tap inside the packed filter (k offset = wtap * cblocks * 64)
     // output addressing: pixel (n, ho, wo), channel c -> out[((n*OH + ho*os + oh0)*OW + wo*os + ow0)*OC + c]
+    // with out_nchw set: out[((n*Cout + c)*OH + ho*os + oh0)*OW + wo*os + ow0], the caller's own NCHW tensor
     int OH, OW, os, oh0, ow0, OC, Cout;
     void* out;
+    int out_nchw;
     int dtype;
     uint32_t idesc;
     int* status;
@@ -250,7 +252,15 @@ conv_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                         else { __nv_bfloat162 h = __floats2bfloat162_rn(a, b); packed[j] = *(uint32_t*)&h; }
                     }
                     uint16_t* dst = orow + cbase;
-                    if (ncols == 32 && ((uintptr_t)dst & 15) == 0) {
+                    if (p.out_nchw) {
+                        const int64_t plane = (int64_t)p.OH * p.OW;
+                        uint16_t* q = (uint16_t*)p.out + ((int64_t)n * p.Cout + cbase) * plane + ((int64_t)ho * p.os + p.oh0) * p.OW + (int64_t)wo * p.os + p.ow0;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (2 * j < ncols) q[(int64_t)(2 * j) * plane] = (uint16_t)(packed[j] & 0xffffu);
+                            if (2 * j + 1 < ncols) q[(int64_t)(2 * j + 1) * plane] = (uint16_t)(packed[j] >> 16);
+                        }
+                    } else if (ncols == 32 && ((uintptr_t)dst & 15) == 0) {
 #pragma unroll
                         for (int j = 0; j < 16; j += 4) *(uint4*)(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
                     } else {

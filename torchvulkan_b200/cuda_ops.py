@@ -549,6 +549,19 @@ def conv2d_backward_weight(dy, x, w_shape, stride=1, padding=0, dilation=1, grou
     return dw
 
 
+def conv2d_backward(dy, x, w, stride=1, padding=0, dilation=1, groups=1, need_dx=True, need_dw=True):
+    """Both gradients in one call (an NCHW dy is brought into the kernels' layout once). dx follows x's memory format, dw
+    follows w's. Returns (dx, dw); a gradient that was not requested is None."""
+    xcl, ycl, wcl = _is_cl(x), _is_cl(dy), _is_cl(w)
+    layout = (capi.CONV_X_CHANNELS_LAST if xcl else 0) | (capi.CONV_Y_CHANNELS_LAST if ycl else 0) | (capi.CONV_W_CHANNELS_LAST if wcl else 0)
+    d = conv2d_desc(x.shape, w.shape, dy.dtype, stride, padding, dilation, groups, layout)
+    ws, nb = _conv_ws(d, 3, dy.device)
+    dx = _empty4(x.shape, dy, xcl) if need_dx else None
+    dw = _empty4(w.shape, dy, wcl) if need_dw else None
+    capi.call("tvk_conv2d_backward", C.byref(d), ptr(dx) if need_dx else None, ptr(dw) if need_dw else None, ptr(dy), ptr(x), ptr(w), ptr(ws), nb, stream())
+    return dx, dw
+
+
 # ------------------------------------------------------------------------------- optimizers
 def adam_step(p, g, m, v, step, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=1e-2, decoupled=True, maximize=False):
     capi.call("tvk_adam_step", dt(p), ptr(p), ptr(g), ptr(m), ptr(v), p.numel(), lr, beta1, beta2, eps, weight_decay, step,
