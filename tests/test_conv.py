@@ -132,6 +132,8 @@ def test_conv2d_fp32_against_oracle(cuda, shape, channels_last):
     y = ops.conv2d_forward(xd, wd, st, pd)
     gx = ops.conv2d_backward_input(gyd, wd, x.shape, st, pd)
     gw = ops.conv2d_backward_weight(gyd, xd, wt.shape, st, pd, channels_last_weight=channels_last)
+    gx2, gw2 = ops.conv2d_backward(gyd, xd, wd, st, pd)          # both gradients in one call: the same bits
+    assert torch.equal(gx2, gx) and torch.equal(gw2, gw)
     ops.check_device_status()
     if channels_last:
         assert all(t.is_contiguous(memory_format=torch.channels_last) for t in (y, gx, gw))

@@ -8,9 +8,11 @@
 // (pixel range split over CTAs into fp32 partials, conv.cpp:1034-1060). Winograd is not used: on
 // tcgen05 the direct form is faster at fp16 and has no transform error.
 //
-// The public tensors are NCHW / OIHW like the reference's (conv.cpp:1106-1108). Each call stages its
-// operands channels-last in the caller's workspace (a transpose each way); see conv_kernels.cuh for
-// why that layout makes every filter tap a plain TMA box.
+// The public tensors are NCHW / OIHW like the reference's (conv.cpp:1106-1108), or channels-last. The kernels read
+// channels-last operands (see conv_kernels.cuh for why that layout makes every filter tap a plain TMA box): an NCHW
+// input is transposed into the caller's workspace first (16-byte packets through shared memory); outputs are written
+// by the epilogue in the caller's layout, NCHW included, with no staged copy. tvk_conv2d_backward transposes an NCHW
+// dy once for both gradients.
 #include "conv_kernels.cuh"
 #include "conv_halo.cuh"
 
@@ -109,6 +111,11 @@ static int make_geo(const tvk_conv2d_desc* d, Geo* g) {
 
 template <typename T>
 static void to_nhwc(T* dst, const T* src, int64_t N, int64_t C, int64_t HW, int64_t Cp, cudaStream_t s) {
+    if (sizeof(T) == 2 && HW % 8 == 0 && Cp % 8 == 0 && (((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {
+        dim3 grid((unsigned)((HW + 63) / 64), (unsigned)((Cp + 63) / 64), (unsigned)N);
+        nchw_to_nhwc_packet_kernel<<<grid, 256, 0, s>>>((uint16_t*)dst, (const uint16_t*)src, (int)C, (int)HW, (int)Cp);
+        return;
+    }
     dim3 grid((unsigned)((HW + 31) / 32), (unsigned)((Cp + 31) / 32), (unsigned)N), block(32, 8);
     nchw_to_nhwc_kernel<T><<<grid, block, 0, s>>>(dst, src, (int)C, (int)HW, (int)Cp);
 }
@@ -324,7 +331,16 @@ extern "C" {
 
 int tvk_conv2d_workspace_size(const tvk_conv2d_desc* d, int mode, uint64_t* bytes) {
     if (!bytes) return set_error(TVK_ERR_INVALID, "tvk_conv2d_workspace_size: null output");
-    if (d && d->dtype == TVK_F32) return conv2d_f32_workspace_size(d, mode, bytes);
+    if (d && d->dtype == TVK_F32) {
+        if (mode != 3) return conv2d_f32_workspace_size(d, mode, bytes);
+        uint64_t b1 = 0, b2 = 0;      // both gradients: the two products run one after the other in the same workspace
+        int rc1 = conv2d_f32_workspace_size(d, 1, &b1);
+        if (rc1) return rc1;
+        rc1 = conv2d_f32_workspace_size(d, 2, &b2);
+        if (rc1) return rc1;
+        *bytes = b1 > b2 ? b1 : b2;
+        return TVK_OK;
+    }
     Geo g;
     int rc = make_geo(d, &g);
     if (rc) return rc;

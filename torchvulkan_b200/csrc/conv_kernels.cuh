@@ -36,6 +36,38 @@ __global__ void nchw_to_nhwc_kernel(T* __restrict__ dst, const T* __restrict__ s
     }
 }
 
+// The same move in 16-byte packets for 16-bit elements, HW a multiple of 8 and 16-byte aligned buffers: a CTA of 256 threads
+// carries a tile of 64 channels x 64 pixels through shared memory. It reads eight pixels of one channel per load, scatters
+// them into a [pixel][channel] tile whose 16-byte channel packets are XOR-swizzled by the pixel's packet index (so the eight
+// lanes that hold the same channels of different pixel packets hit different banks), and writes eight channels of one pixel
+// per store. Channels >= C come out as zero. grid (ceil(HW/64), ceil(Cp/64), N).
+__global__ void __launch_bounds__(256) nchw_to_nhwc_packet_kernel(uint16_t* __restrict__ dst, const uint16_t* __restrict__ src, int C, int HW, int Cp) {
+    __shared__ __align__(16) uint16_t tile[64 * 64];
+    const int n = blockIdx.z;
+    const int p0 = blockIdx.x * 64, c0 = blockIdx.y * 64;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int idx = threadIdx.x + 256 * k;
+        const int c = idx >> 3, pp = idx & 7;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (c0 + c < C && p0 + pp * 8 < HW) v = __ldcs((const uint4*)(src + ((int64_t)n * C + c0 + c) * HW + p0 + pp * 8));
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        const int col = ((((c >> 3) ^ pp) & 7) << 3) + (c & 7);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) tile[(pp * 8 + j) * 64 + col] = (uint16_t)((j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xffffu));
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int idx = threadIdx.x + 256 * k;
+        const int p = idx >> 3, cpk = idx & 7;
+        if (p0 + p < HW && c0 + cpk * 8 < Cp) {
+            const uint4 v = *(const uint4*)(tile + p * 64 + (((cpk ^ (p >> 3)) & 7) << 3));
+            __stcs((uint4*)(dst + ((int64_t)n * HW + p0 + p) * Cp + c0 + cpk * 8), v);
+        }
+    }
+}
+
 // src [N, HW, Cp] -> dst [N, C, HW]. grid (ceil(HW/32), ceil(C/32), N), block (32, 8)
 template <typename T>
 __global__ void nhwc_to_nchw_kernel(T* __restrict__ dst, const T* __restrict__ src, int C, int HW, int Cp) {
