@@ -269,6 +269,29 @@ TVK_API int tvk_gemm_workspace_size(const tvk_gemm_desc* d, uint64_t* bytes);
 TVK_API int tvk_gemm(const tvk_gemm_desc* d, void* workspace, uint64_t workspace_bytes, void* stream);
 /* Which path tvk_gemm would take: 1 = tcgen05 tensor-core kernel, 2 = CUDA-core kernel. */
 TVK_API int tvk_gemm_path(const tvk_gemm_desc* d, int* path);
+/* _scaled_mm: out = cast((A * scale_a) @ (B * scale_b) + bias), A [m, k] and B [k, n] float8 (e4m3fn or e5m2) with
+ * element strides, scales fp32 in device memory: one value each (stride 0) or one per row of A and one per column of B
+ * (stride 1). Replaces scaled_mm_out_vulkan (src/api/ops/matmul.cpp:706-747), which upcasts both operands to fp32, scales
+ * them and multiplies in fp32; here the float8 values are widened exactly to fp16 and multiplied on the tensor cores with
+ * fp32 accumulation, the scales applied to the accumulator. out is contiguous [m, n] of out_kind; bias ([n], fp32 / fp16
+ * / bf16) may be NULL; scale_result (may be NULL) divides the result only for float8 outputs, as in the reference.
+ * A float8 output is cast without saturation. The workspace must be 256-byte aligned. */
+enum { TVK_F8_E4M3 = 0, TVK_F8_E5M2 = 1 };
+enum { TVK_SCALED_OUT_F32 = 0, TVK_SCALED_OUT_F16 = 1, TVK_SCALED_OUT_BF16 = 2, TVK_SCALED_OUT_E4M3 = 3, TVK_SCALED_OUT_E5M2 = 4 };
+typedef struct tvk_scaled_mm_desc {
+    int32_t a_kind, b_kind, out_kind, bias_dtype;
+    int64_t m, n, k;
+    const void* a; int64_t a_rs, a_cs;
+    const void* b; int64_t b_rs, b_cs;
+    void* out;
+    const float* scale_a; int64_t sa_stride;
+    const float* scale_b; int64_t sb_stride;
+    const void* bias;
+    const float* scale_result;
+} tvk_scaled_mm_desc;
+TVK_API int tvk_scaled_mm_workspace_size(const tvk_scaled_mm_desc* d, uint64_t* bytes);
+TVK_API int tvk_scaled_mm(const tvk_scaled_mm_desc* d, void* workspace, uint64_t workspace_bytes, void* stream);
+
 /* Tuning hook of the tensor-core path, process-wide (the counterpart of pinning an entry of the reference's autotune
  * cache, src/vulkan/autotuner.cpp:123-178; used by sweeps and tests, not needed for normal use). 0 keeps the library's
  * choice. bn: tile width 32/64/128/256; mt: 128-row tiles per CTA block (1, 2); splits: K slices; group_m: tile rows
@@ -564,6 +587,15 @@ TVK_API int tvk_conv2d_backward_weight(const tvk_conv2d_desc* desc, void* dw, co
  * tvk_conv2d_workspace_size. The results are bit-identical to the two separate calls. */
 TVK_API int tvk_conv2d_backward(const tvk_conv2d_desc* desc, void* dx, void* dw, const void* dy, const void* x, const void* w,
                                 void* workspace, uint64_t workspace_bytes, void* stream);
+
+/* Depthwise 2-D convolution: groups == cin, cout a multiple of cin (one input channel per group). The reference sends
+ * these through the same grouped convolution as everything else (convolution_vulkan with groups > 1,
+ * src/api/ops/conv.cpp:1088-1117; the depthwise / slow aliases conv.cpp:218-230). Direct kernels, fp32 / fp16 / bf16 with
+ * fp32 accumulation, any stride, padding and dilation, NCHW tensors (layout must be 0): w and dw are [cout, 1, kh, kw].
+ * The weight gradient supports filters of up to 49 taps and sums in a fixed order. */
+TVK_API int tvk_depthwise_conv2d_forward(const tvk_conv2d_desc* desc, void* y, const void* x, const void* w, void* stream);
+TVK_API int tvk_depthwise_conv2d_backward_input(const tvk_conv2d_desc* desc, void* dx, const void* dy, const void* w, void* stream);
+TVK_API int tvk_depthwise_conv2d_backward_weight(const tvk_conv2d_desc* desc, void* dw, const void* dy, const void* x, void* stream);
 
 /* Stable sort of every line of a contiguous [lines, n] view and top-k as "sort then take k"
  * (src/api/ops/sort.cpp:19-140): order by value (descending if `descending`), NaN largest,

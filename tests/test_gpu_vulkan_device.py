@@ -352,7 +352,65 @@ def test_conv2d_autograd(vk, dtype, stride, pad, k):
     for name, d, c in (("y", yd, yc), ("gx", xd.grad, xc.grad), ("gw", wd.grad, wc.grad), ("gb", bd.grad, bc.grad)):
         assert rel_fro(d.detach().cpu().double().numpy(), c.detach().numpy()) <= (1e-2 if dtype != torch.float32 else 1e-5), name
     with pytest.raises(RuntimeError, match="NOT IMPLEMENTED"):
-        F.conv2d(xd, wd[:, :12].contiguous(), None, groups=2)
+        F.conv3d(xd.unsqueeze(2), wd.unsqueeze(2))
+
+
+def _conv_family_check(fn, tensors, dtype, **kw):
+    """fn(*tensors, **kw) on the device against ATen CPU in float64: the output and the gradient of every tensor."""
+    dev = [t.to("vulkan:0").requires_grad_() for t in tensors]
+    cpu = [t.double().requires_grad_() for t in tensors]
+    yd, yc = fn(*dev, **kw), fn(*cpu, **kw)
+    assert yd.shape == yc.shape
+    gy = torch.randn(yc.shape, generator=torch.Generator().manual_seed(9)).to(dtype)
+    yd.backward(gy.to("vulkan:0")); yc.backward(gy.double())
+    tol = 1e-2 if dtype != torch.float32 else 1e-4
+    assert rel_fro(yd.detach().cpu().double().numpy(), yc.detach().numpy()) <= tol, "output"
+    for i, (d, c) in enumerate(zip(dev, cpu)):
+        assert d.grad.shape == c.grad.shape
+        assert rel_fro(d.grad.cpu().double().numpy(), c.grad.numpy()) <= tol, f"gradient of argument {i}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("groups,cin,cout", [(2, 24, 40), (4, 16, 16), (24, 24, 24), (24, 24, 72)])
+def test_grouped_and_depthwise_conv2d(vk, dtype, groups, cin, cout):
+    """groups > 1 through convolution_overrideable(+backward): depthwise (groups == cin, with and without a channel
+    multiplier) on the direct kernels, other groupings group by group on the tensor-core kernels."""
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(3, cin, 11, 9, generator=g).to(dtype)
+    w = (torch.randn(cout, cin // groups, 3, 3, generator=g) / 3.0).to(dtype)
+    b = torch.randn(cout, generator=g).to(dtype)
+    for stride, pad in ((1, 1), (2, 1)):
+        _conv_family_check(F.conv2d, (x, w, b), dtype, stride=stride, padding=pad, groups=groups)
+    if groups == cin:          # the direct kernels also take dilation and unequal strides
+        _conv_family_check(F.conv2d, (x, w, b), dtype, stride=(2, 1), padding=(2, 0), dilation=(2, 1), groups=groups)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_conv_transpose2d(vk, dtype):
+    """Transposed convolution = the input-gradient product of the forward one; stride 2 with output_padding, and groups."""
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(3, 16, 7, 6, generator=g).to(dtype)
+    w = (torch.randn(16, 24, 3, 3, generator=g) / 12.0).to(dtype)
+    b = torch.randn(24, generator=g).to(dtype)
+    _conv_family_check(F.conv_transpose2d, (x, w, b), dtype, stride=1, padding=1)
+    _conv_family_check(F.conv_transpose2d, (x, w, b), dtype, stride=2, padding=1, output_padding=1)
+    w2 = (torch.randn(16, 6, 3, 3, generator=g) / 6.0).to(dtype)              # groups 2: 16 -> 12 channels
+    _conv_family_check(F.conv_transpose2d, (x, w2), dtype, stride=2, padding=1, output_padding=1, groups=2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_conv1d_and_conv_transpose1d(vk, dtype):
+    """1-D convolutions run as 2-D ones of height 1."""
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(4, 16, 37, generator=g).to(dtype)
+    w = (torch.randn(24, 16, 5, generator=g) / 9.0).to(dtype)
+    b = torch.randn(24, generator=g).to(dtype)
+    _conv_family_check(F.conv1d, (x, w, b), dtype, stride=1, padding=2)
+    _conv_family_check(F.conv1d, (x, w, b), dtype, stride=2, padding=1)
+    wd = (torch.randn(16, 1, 5, generator=g) / 2.0).to(dtype)                 # depthwise
+    _conv_family_check(F.conv1d, (x, wd), dtype, stride=1, padding=2, groups=16)
+    wt = (torch.randn(16, 8, 4, generator=g) / 8.0).to(dtype)
+    _conv_family_check(F.conv_transpose1d, (x, wt), dtype, stride=2, padding=1)
 
 
 @pytest.mark.parametrize("channels_last", [False, True])
@@ -613,3 +671,43 @@ def test_environment_switches_of_the_reference(vk):
     env = dict(os.environ, PYTHONPATH=str(root), TORCHVULKAN_VALIDATION="1", TORCHVULKAN_PROFILE="1", TORCHVULKAN_STRICT="1")
     p = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
     assert p.returncode == 0 and "ENV-OK" in p.stdout, p.stdout[-2000:] + p.stderr[-3000:]
+
+
+@pytest.mark.parametrize("rowwise", [False, True])
+@pytest.mark.parametrize("kinds", [("e4m3", "e4m3"), ("e4m3", "e5m2")])
+def test_scaled_mm(vk, rowwise, kinds):
+    """torch._scaled_mm on float8 operands against the emulation the reference follows (src/api/ops/matmul.cpp:706-747):
+    upcast, scale, fp32 product, bias, cast. The products of float8 values are exact in fp32 on both sides, so the
+    results differ only by the order of the fp32 additions."""
+    f8 = {"e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
+    g = torch.Generator().manual_seed(21)
+    for m, k, n in ((48, 72, 40), (33, 70, 37), (256, 512, 128)):
+        a = torch.randn(m, k, generator=g).to(f8[kinds[0]])
+        b = torch.randn(n, k, generator=g).to(f8[kinds[1]]).t()              # column-major, as torch's CUDA op wants it
+        sa = (torch.rand(m, 1, generator=g) + 0.5) if rowwise else torch.tensor(0.75)
+        sb = (torch.rand(1, n, generator=g) + 0.5) if rowwise else torch.tensor(1.5)
+        bias = torch.randn(n, generator=g).bfloat16()
+        ref = (a.float() * sa) @ (b.float() * sb)
+        for out_dtype, with_bias in ((torch.bfloat16, True), (torch.float32, False), (torch.float16, False)):
+            got = torch._scaled_mm(a.to(vk), b.to(vk), sa.to(vk), sb.to(vk), bias.to(vk) if with_bias else None, None, out_dtype)
+            assert got.dtype == out_dtype and got.shape == (m, n) and got.is_contiguous()
+            want = (ref + bias.float()) if with_bias else ref
+            tol = {torch.float32: 1e-5, torch.float16: 1e-3, torch.bfloat16: 1e-2}[out_dtype]
+            assert rel_fro(got.cpu().double().numpy(), want.double().numpy()) <= tol, (m, k, n, out_dtype)
+        # a row-major second operand is consumed through its strides as well
+        got = torch._scaled_mm(a.to(vk), b.contiguous().to(vk), sa.to(vk), sb.to(vk), None, None, torch.float32)
+        assert rel_fro(got.cpu().double().numpy(), ref.double().numpy()) <= 1e-5
+        # float8 output: divided by scale_result, cast without saturation
+        sr = torch.tensor(4.0)
+        got8 = torch._scaled_mm(a.to(vk), b.to(vk), sa.to(vk), sb.to(vk), None, sr.to(vk), torch.float8_e4m3fn)
+        want8 = (ref / sr).to(torch.float8_e4m3fn)
+        assert got8.dtype == torch.float8_e4m3fn
+        g8, w8 = got8.cpu().float(), want8.float()
+        # identical except where the fp32 sums differ in the last place right at a rounding boundary of the 3-bit mantissa
+        same = (g8 == w8) | (g8.isnan() & w8.isnan())
+        assert same.float().mean() >= 0.995
+        assert rel_fro(g8.nan_to_num(0.0).double().numpy(), w8.nan_to_num(0.0).double().numpy()) <= 2e-2
+    with pytest.raises(ValueError, match="Invalid scaling configuration"):
+        torch._scaled_mm(a.to(vk), b.to(vk), torch.ones(3).to(vk), torch.ones(1).to(vk), None, None, torch.bfloat16)
+    with pytest.raises(ValueError, match="must be fp8"):
+        torch._scaled_mm(a.float().to(vk), b.to(vk), torch.ones(()).to(vk), torch.ones(()).to(vk), None, None, torch.bfloat16)

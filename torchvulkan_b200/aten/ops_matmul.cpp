@@ -1,4 +1,4 @@
-// aten::mm / addmm / bmm / baddbmm / _addmm_activation (+ .out) for the "vulkan" device.
+// aten::mm / addmm / bmm / baddbmm / addbmm / addmv / dot / _addmm_activation / _scaled_mm (+ .out) for the "vulkan" device.
 //
 // Counterparts in the reference: mm_vulkan ... addmm_activation_vulkan and their .out wrappers
 // (src/api/ops/matmul.cpp:598-763). The checks and their messages follow ATen's CPU ops as the
@@ -185,6 +185,87 @@ at::Tensor& addmm_activation_out(const at::Tensor& input, const at::Tensor& m1, 
     return fill_out(out, (addmm_activation)(input, m1, m2, beta, alpha, use_gelu));
 }
 
+// ---- _scaled_mm (src/api/ops/matmul.cpp:706-747): the same checks and messages, then tvk_scaled_mm -------------------
+int scaled_out_kind(at::ScalarType st) {
+    switch (st) {
+        case at::kFloat: return TVK_SCALED_OUT_F32;
+        case at::kHalf: return TVK_SCALED_OUT_F16;
+        case at::kBFloat16: return TVK_SCALED_OUT_BF16;
+        case at::kFloat8_e4m3fn: return TVK_SCALED_OUT_E4M3;
+        case at::kFloat8_e5m2: return TVK_SCALED_OUT_E5M2;
+        default: return -1;
+    }
+}
+int f8_kind(at::ScalarType st) { return st == at::kFloat8_e5m2 ? TVK_F8_E5M2 : TVK_F8_E4M3; }
+
+at::Tensor& scaled_mm_out(const at::Tensor& mat1, const at::Tensor& mat2, const at::Tensor& scale_a, const at::Tensor& scale_b,
+                          const std::optional<at::Tensor>& bias, const std::optional<at::Tensor>& scale_result, std::optional<at::ScalarType> out_dtype,
+                          bool /*use_fast_accum*/, at::Tensor& out) {
+    TORCH_CHECK_VALUE(!out_dtype || *out_dtype == out.scalar_type(), "out_dtype must match output matrix type");
+    TORCH_CHECK(mat1.dim() == 2, "mat1 must be a matrix");
+    TORCH_CHECK(mat2.dim() == 2, "mat2 must be a matrix");
+    TORCH_CHECK(mat1.size(1) == mat2.size(0), "mat_a and mat_b shapes cannot be multiplied (", mat1.size(0), "x", mat1.size(1), " and ", mat2.size(0), "x",
+                mat2.size(1), ")");
+    const auto is_f8 = [](at::ScalarType st) { return st == at::kFloat8_e4m3fn || st == at::kFloat8_e5m2; };
+    TORCH_CHECK_VALUE(at::isFloat8Type(mat1.scalar_type()) && at::isFloat8Type(mat2.scalar_type()), "mat1 and mat2 must be fp8 types, got: ", mat1.scalar_type(),
+                      mat2.scalar_type());
+    if (!is_f8(mat1.scalar_type()) || !is_f8(mat2.scalar_type())) TVK_NOT_IMPLEMENTED("_scaled_mm for ", mat1.scalar_type(), " and ", mat2.scalar_type(), " (e4m3fn and e5m2 are supported)");
+    const bool tensorwise = scale_a.numel() == 1 && scale_b.numel() == 1;
+    const bool rowwise = scale_a.dim() == 2 && scale_b.dim() == 2 && scale_a.size(0) == mat1.size(0) && scale_a.size(1) == 1 && scale_b.size(0) == 1 &&
+                         scale_b.size(1) == mat2.size(1);
+    TORCH_CHECK_VALUE(tensorwise || rowwise, "Invalid scaling configuration");
+    TORCH_CHECK_VALUE(scale_a.scalar_type() == at::kFloat, "scale_a must have Float elements");
+    TORCH_CHECK_VALUE(scale_b.scalar_type() == at::kFloat, "scale_b must have Float elements");
+    TORCH_CHECK(!scale_result || (scale_result->numel() == 1 && scale_result->scalar_type() == at::kFloat), "scale_result must be a float scalar");
+    TORCH_CHECK(!bias || bias->numel() == mat2.size(1), "Bias must be size ", mat2.size(1), " but got ", bias->numel());
+    for (const at::Tensor* t : {&mat2, &scale_a, &scale_b})
+        TORCH_CHECK(t->device() == mat1.device(), "Expected all tensors to be on the same device, but found at least two devices, ", mat1.device(), " and ", t->device(), "!");
+    const int kind = scaled_out_kind(out.scalar_type());
+    if (kind < 0) TVK_NOT_IMPLEMENTED("_scaled_mm with output dtype ", out.scalar_type());
+
+    const int64_t m = mat1.size(0), k = mat1.size(1), n = mat2.size(1);
+    const bool direct = out.is_contiguous() && out.dim() == 2 && out.size(0) == m && out.size(1) == n;
+    at::Tensor dst = out;
+    if (!direct) {
+        if (out.sizes() != at::IntArrayRef({m, n})) out.resize_({m, n});
+        dst = out.is_contiguous() ? out : empty_vulkan({m, n}, out.scalar_type(), out.device());
+    }
+    if (m > 0 && n > 0) {
+        at::Tensor sa = contiguous_vulkan(scale_a), sb = contiguous_vulkan(scale_b), bs, sr;
+        tvk_scaled_mm_desc d = {};
+        d.a_kind = f8_kind(mat1.scalar_type()); d.b_kind = f8_kind(mat2.scalar_type()); d.out_kind = kind;
+        d.m = m; d.n = n; d.k = k;
+        d.a = mat1.data_ptr(); d.a_rs = mat1.stride(0); d.a_cs = mat1.stride(1);
+        d.b = mat2.data_ptr(); d.b_rs = mat2.stride(0); d.b_cs = mat2.stride(1);
+        d.out = dst.data_ptr();
+        d.scale_a = sa.data_ptr<float>(); d.sa_stride = tensorwise ? 0 : 1;
+        d.scale_b = sb.data_ptr<float>(); d.sb_stride = tensorwise ? 0 : 1;
+        if (bias && bias->defined()) {
+            bs = contiguous_vulkan(*bias);
+            if (!is_hot_float(bs.scalar_type())) TVK_NOT_IMPLEMENTED("_scaled_mm with a bias of dtype ", bs.scalar_type());
+            d.bias = bs.data_ptr(); d.bias_dtype = to_tvk_dtype(bs.scalar_type());
+        }
+        if (scale_result && scale_result->defined()) {
+            sr = contiguous_vulkan(*scale_result);
+            d.scale_result = sr.data_ptr<float>();
+        }
+        DeviceScope scope(mat1);
+        uint64_t ws_bytes = 0;
+        TVK_CALL(tvk_scaled_mm_workspace_size(&d, &ws_bytes));
+        Workspace ws(scope.device, ws_bytes);
+        TVK_CALL(tvk_scaled_mm(&d, ws.ptr, ws.bytes, scope.stream));
+    }
+    if (!dst.is_same(out)) out.copy_(dst);
+    return out;
+}
+
+at::Tensor scaled_mm(const at::Tensor& mat1, const at::Tensor& mat2, const at::Tensor& scale_a, const at::Tensor& scale_b, const std::optional<at::Tensor>& bias,
+                     const std::optional<at::Tensor>& scale_result, std::optional<at::ScalarType> out_dtype, bool use_fast_accum) {
+    // as the reference: without out_dtype the result has mat1's (float8) type
+    at::Tensor out = empty_vulkan({mat1.dim() == 2 ? mat1.size(0) : 0, mat2.dim() == 2 ? mat2.size(1) : 0}, out_dtype.value_or(mat1.scalar_type()), mat1.device());
+    return scaled_mm_out(mat1, mat2, scale_a, scale_b, bias, scale_result, out_dtype, use_fast_accum, out);
+}
+
 }  // namespace
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
@@ -205,6 +286,8 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("dot", &dot);
     m.impl("_addmm_activation", &addmm_activation);
     m.impl("_addmm_activation.out", &addmm_activation_out);
+    m.impl("_scaled_mm", &scaled_mm);
+    m.impl("_scaled_mm.out", &scaled_mm_out);
 }
 
 }  // namespace tvk_aten

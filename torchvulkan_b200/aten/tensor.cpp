@@ -97,7 +97,17 @@ namespace {
 // dst (vulkan, any strides) <- src (vulkan, same device, any strides, any supported dtype)
 void device_copy(const at::Tensor& dst, const at::Tensor& src) {
     if (dst.numel() == 0) return;
-    const int ddt = to_tvk_dtype(dst.scalar_type()), sdt = to_tvk_dtype(src.scalar_type());
+    int ddt = to_tvk_dtype(dst.scalar_type()), sdt = to_tvk_dtype(src.scalar_type());
+    if (dst.scalar_type() == src.scalar_type() && ddt < 0) {
+        // a same-type copy does not interpret the values: types the kernels have no arithmetic for (float8, int16, ...)
+        // move as integers of their width
+        switch (dst.element_size()) {
+            case 1: ddt = sdt = TVK_U8; break;
+            case 4: ddt = sdt = TVK_I32; break;
+            case 8: ddt = sdt = TVK_I64; break;
+            default: break;
+        }
+    }
     TORCH_CHECK(ddt >= 0 && sdt >= 0, "torchvulkan [NOT IMPLEMENTED]: copy between ", src.scalar_type(), " and ", dst.scalar_type());
     DeviceScope scope(dst);
     // bool <-> number conversions are not plain byte copies

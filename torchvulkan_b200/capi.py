@@ -57,6 +57,19 @@ class GemmDesc(C.Structure):
                 ("aux_op", C.c_int32), ("reserved2_", C.c_int32)]
 
 
+class ScaledMmDesc(C.Structure):
+    _fields_ = [("a_kind", C.c_int32), ("b_kind", C.c_int32), ("out_kind", C.c_int32), ("bias_dtype", C.c_int32),
+                ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64),
+                ("a", C.c_void_p), ("a_rs", C.c_int64), ("a_cs", C.c_int64),
+                ("b", C.c_void_p), ("b_rs", C.c_int64), ("b_cs", C.c_int64),
+                ("out", C.c_void_p),
+                ("scale_a", C.c_void_p), ("sa_stride", C.c_int64),
+                ("scale_b", C.c_void_p), ("sb_stride", C.c_int64),
+                ("bias", C.c_void_p), ("scale_result", C.c_void_p)]
+
+
+F8_E4M3, F8_E5M2 = 0, 1
+SCALED_OUT_F32, SCALED_OUT_F16, SCALED_OUT_BF16, SCALED_OUT_E4M3, SCALED_OUT_E5M2 = range(5)
 AUX_NONE, AUX_GELU_BACKWARD, AUX_RELU_BACKWARD = 0, 1, 2
 SCAN_SUM, SCAN_PROD, SCAN_LOGADDEXP = 0, 1, 2
 
@@ -185,6 +198,11 @@ SIGNATURES = {
     "tvk_conv2d_backward_input": (_i, [_P(Conv2dDesc), _p, _p, _p, _p, _u64, _p]),
     "tvk_conv2d_backward_weight": (_i, [_P(Conv2dDesc), _p, _p, _p, _p, _u64, _p]),
     "tvk_conv2d_backward": (_i, [_P(Conv2dDesc), _p, _p, _p, _p, _p, _p, _u64, _p]),
+    "tvk_scaled_mm_workspace_size": (_i, [_P(ScaledMmDesc), _P(_u64)]),
+    "tvk_scaled_mm": (_i, [_P(ScaledMmDesc), _p, _u64, _p]),
+    "tvk_depthwise_conv2d_forward": (_i, [_P(Conv2dDesc), _p, _p, _p, _p]),
+    "tvk_depthwise_conv2d_backward_input": (_i, [_P(Conv2dDesc), _p, _p, _p, _p]),
+    "tvk_depthwise_conv2d_backward_weight": (_i, [_P(Conv2dDesc), _p, _p, _p, _p]),
     "tvk_attention_workspace_size": (_i, [_i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _P(_u64)]),
     "tvk_attention_forward": (_i, [_i, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _d, _i, _p, _u64, _p]),
     "tvk_attention_backward": (_i, [_i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _d, _i, _p, _u64, _p]),
