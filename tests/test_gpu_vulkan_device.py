@@ -352,7 +352,7 @@ def test_conv2d_autograd(vk, dtype, stride, pad, k):
     for name, d, c in (("y", yd, yc), ("gx", xd.grad, xc.grad), ("gw", wd.grad, wc.grad), ("gb", bd.grad, bc.grad)):
         assert rel_fro(d.detach().cpu().double().numpy(), c.detach().numpy()) <= (1e-2 if dtype != torch.float32 else 1e-5), name
     with pytest.raises(RuntimeError, match="NOT IMPLEMENTED"):
-        F.conv3d(xd.unsqueeze(2), wd.unsqueeze(2))
+        F.conv_transpose3d(xd.unsqueeze(2), wd.transpose(0, 1).unsqueeze(2))
 
 
 def _conv_family_check(fn, tensors, dtype, **kw):
@@ -396,6 +396,20 @@ def test_conv_transpose2d(vk, dtype):
     _conv_family_check(F.conv_transpose2d, (x, w, b), dtype, stride=2, padding=1, output_padding=1)
     w2 = (torch.randn(16, 6, 3, 3, generator=g) / 6.0).to(dtype)              # groups 2: 16 -> 12 channels
     _conv_family_check(F.conv_transpose2d, (x, w2), dtype, stride=2, padding=1, output_padding=1, groups=2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_conv3d(vk, dtype):
+    """3-D convolution: one 2-D convolution per depth tap over the batch n * depths."""
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(2, 8, 6, 9, 7, generator=g).to(dtype)
+    w = (torch.randn(12, 8, 3, 3, 3, generator=g) / 14.0).to(dtype)
+    b = torch.randn(12, generator=g).to(dtype)
+    _conv_family_check(F.conv3d, (x, w, b), dtype, stride=1, padding=1)
+    _conv_family_check(F.conv3d, (x, w, b), dtype, stride=2, padding=1)
+    _conv_family_check(F.conv3d, (x, w, b), dtype, stride=(2, 1, 1), padding=(0, 1, 1))
+    w2 = (torch.randn(12, 4, 2, 3, 3, generator=g) / 8.0).to(dtype)
+    _conv_family_check(F.conv3d, (x, w2), dtype, stride=1, padding=(1, 1, 1), groups=2)
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])

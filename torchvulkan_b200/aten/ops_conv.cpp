@@ -11,7 +11,8 @@
 //     product and the weight-gradient product with the roles of input and output swapped);
 //   * depthwise convolutions (one input channel per group) take the direct kernels of depthwise.cu;
 //   * other grouped convolutions run group by group on channel slices.
-// 3-D convolutions and what the kernels refuse raise "[NOT IMPLEMENTED]" (the hot path never falls back to the CPU).
+//   * a 3-D convolution is one 2-D convolution per depth tap over the batch n * depths, accumulated.
+// Transposed 3-D convolutions and what the kernels refuse raise "[NOT IMPLEMENTED]" (the hot path never falls back to the CPU).
 #include "common.h"
 
 namespace tvk_aten {
@@ -205,6 +206,79 @@ at::Tensor conv_transpose2d_any(const at::Tensor& input, const at::Tensor& weigh
     return std::get<0>(conv2d_any_backward(input, like, weight, st, pd, dl, groups, true, false));
 }
 
+// ---- 3-D convolution: one 2-D convolution per depth tap -------------------------------------------------------------
+// y[:, :, do] = sum over kd of conv2d(x[:, :, do * sd - pd + kd * dd], w[:, :, kd]). For one kd the valid output depths
+// form a range and their input depths a strided slice, so each tap is ONE 2-D convolution over the batch n * depths
+// (the tensor-core kernels see a large batch), accumulated into the output slice.
+struct DepthTap {
+    int64_t do0, count, d0;      // output depths do0 .. do0 + count, reading input depths d0 + i * sd
+};
+DepthTap depth_tap(int64_t D, int64_t Do, int64_t kd, int64_t sd, int64_t pd, int64_t dd) {
+    // smallest / largest do with 0 <= do * sd - pd + kd * dd < D
+    const int64_t off = kd * dd - pd;
+    int64_t lo = off >= 0 ? 0 : (-off + sd - 1) / sd;
+    int64_t hi = (D - 1 - off) >= 0 ? (D - 1 - off) / sd : -1;
+    if (hi > Do - 1) hi = Do - 1;
+    DepthTap t{lo, hi >= lo ? hi - lo + 1 : 0, lo * sd + off};
+    return t;
+}
+// [n, c, depths, h, w] slice -> contiguous [n * depths, c, h, w]
+at::Tensor fold_depth(const at::Tensor& t5) { return contiguous_vulkan(t5.permute({0, 2, 1, 3, 4})).view({t5.size(0) * t5.size(2), t5.size(1), t5.size(3), t5.size(4)}); }
+at::Tensor unfold_depth(const at::Tensor& t4, int64_t n) { return t4.view({n, t4.size(0) / n, t4.size(1), t4.size(2), t4.size(3)}).permute({0, 2, 1, 3, 4}); }
+
+struct Geo3 {
+    std::array<int64_t, 3> st, pd, dl;
+    int64_t Do;
+};
+Geo3 geo3(const at::Tensor& input, const at::Tensor& weight, at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation) {
+    auto three = [](at::IntArrayRef v, int64_t dflt) {
+        if (v.empty()) return std::array<int64_t, 3>{dflt, dflt, dflt};
+        return v.size() == 1 ? std::array<int64_t, 3>{v[0], v[0], v[0]} : std::array<int64_t, 3>{v[0], v[1], v[2]};
+    };
+    Geo3 g{three(stride, 1), three(padding, 0), three(dilation, 1), 0};
+    g.Do = (input.size(2) + 2 * g.pd[0] - g.dl[0] * (weight.size(2) - 1) - 1) / g.st[0] + 1;
+    TORCH_CHECK(g.Do > 0, "torchvulkan [ERROR]: convolution: the filter does not fit the padded input");
+    return g;
+}
+
+at::Tensor conv3d_by_taps(const at::Tensor& input, const at::Tensor& weight, at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation,
+                          int64_t groups) {
+    const Geo3 g = geo3(input, weight, stride, padding, dilation);
+    const int64_t n = input.size(0);
+    at::Tensor y;
+    for (int64_t kd = 0; kd < weight.size(2); ++kd) {
+        const DepthTap t = depth_tap(input.size(2), g.Do, kd, g.st[0], g.pd[0], g.dl[0]);
+        if (t.count == 0) continue;
+        at::Tensor x4 = fold_depth(input.slice(2, t.d0, t.d0 + (t.count - 1) * g.st[0] + 1, g.st[0]));
+        at::Tensor y4 = conv2d_any(x4, contiguous_vulkan(weight.select(2, kd)), {g.st[1], g.st[2]}, {g.pd[1], g.pd[2]}, {g.dl[1], g.dl[2]}, groups);
+        if (!y.defined()) y = at::zeros({n, weight.size(0), g.Do, y4.size(2), y4.size(3)}, input.options());
+        y.slice(2, t.do0, t.do0 + t.count).add_(unfold_depth(y4, n));
+    }
+    TORCH_CHECK(y.defined(), "torchvulkan [ERROR]: convolution: no filter tap reaches the input");
+    return y;
+}
+
+std::tuple<at::Tensor, at::Tensor> conv3d_by_taps_backward(const at::Tensor& gy, const at::Tensor& input, const at::Tensor& weight, at::IntArrayRef stride,
+                                                            at::IntArrayRef padding, at::IntArrayRef dilation, int64_t groups, bool need_gx, bool need_gw) {
+    const Geo3 g = geo3(input, weight, stride, padding, dilation);
+    const int64_t n = input.size(0);
+    at::Tensor gx, gw;
+    if (need_gx) gx = at::zeros(input.sizes(), input.options());
+    if (need_gw) gw = at::zeros(weight.sizes(), weight.options());
+    for (int64_t kd = 0; kd < weight.size(2); ++kd) {
+        const DepthTap t = depth_tap(input.size(2), g.Do, kd, g.st[0], g.pd[0], g.dl[0]);
+        if (t.count == 0) continue;
+        at::Tensor xs = input.slice(2, t.d0, t.d0 + (t.count - 1) * g.st[0] + 1, g.st[0]);
+        at::Tensor x4 = fold_depth(xs), gy4 = fold_depth(gy.slice(2, t.do0, t.do0 + t.count));
+        at::Tensor g4x, g4w;
+        std::tie(g4x, g4w) = conv2d_any_backward(gy4, x4, contiguous_vulkan(weight.select(2, kd)), {g.st[1], g.st[2]}, {g.pd[1], g.pd[2]}, {g.dl[1], g.dl[2]}, groups,
+                                                 need_gx, need_gw);
+        if (need_gx) gx.slice(2, t.d0, t.d0 + (t.count - 1) * g.st[0] + 1, g.st[0]).add_(unfold_depth(g4x, n));
+        if (need_gw) gw.select(2, kd).copy_(g4w);
+    }
+    return {gx, gw};
+}
+
 at::Tensor squeeze_h(const at::Tensor& t) { return t.defined() ? t.squeeze(2) : t; }
 
 at::Tensor convolution_entry(const at::Tensor& input, const at::Tensor& weight, const c10::optional<at::Tensor>& bias, at::IntArrayRef stride,
@@ -216,8 +290,13 @@ at::Tensor convolution_entry(const at::Tensor& input, const at::Tensor& weight, 
         return convolution_entry(input.unsqueeze(2), weight.unsqueeze(2), bias, {s, s}, one(padding, 0, 0), one(dilation, 1, 1), transposed, one(output_padding, 0, 0), groups)
             .squeeze(2);
     }
-    TORCH_CHECK(input.dim() == 4 && weight.dim() == 4, "torchvulkan [NOT IMPLEMENTED]: convolution of ", input.dim() - 2,
-                " spatial dimensions (1-D and 2-D convolutions are supported)");
+    if (input.dim() == 5 && weight.dim() == 5) {
+        TORCH_CHECK(!transposed, "torchvulkan [NOT IMPLEMENTED]: transposed 3-D convolution");
+        at::Tensor y3 = conv3d_by_taps(input, weight, stride, padding, dilation, groups);
+        if (bias.has_value() && bias->defined()) y3.add_(bias->view({1, -1, 1, 1, 1}));
+        return y3;
+    }
+    TORCH_CHECK(input.dim() == 4 && weight.dim() == 4, "torchvulkan [NOT IMPLEMENTED]: convolution of ", input.dim() - 2, " spatial dimensions");
     const Vec2 pd = pair_of(padding, 0), dl = pair_of(dilation, 1), op = pair_of(output_padding, 0);
     const Vec2 st = effective_stride(input, weight, pair_of(stride, 1), pd, op);
     at::Tensor y;
@@ -238,8 +317,14 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> convolution_backward_entry(const 
                                       one(output_padding, 0, 0), groups, output_mask);
         return std::make_tuple(squeeze_h(std::get<0>(r)), squeeze_h(std::get<1>(r)), std::get<2>(r));
     }
-    TORCH_CHECK(input.dim() == 4 && weight.dim() == 4, "torchvulkan [NOT IMPLEMENTED]: convolution of ", input.dim() - 2,
-                " spatial dimensions (1-D and 2-D convolutions are supported)");
+    if (input.dim() == 5 && weight.dim() == 5) {
+        TORCH_CHECK(!transposed, "torchvulkan [NOT IMPLEMENTED]: transposed 3-D convolution");
+        at::Tensor gx3, gw3, gb3;
+        std::tie(gx3, gw3) = conv3d_by_taps_backward(grad_output, input, weight, stride, padding, dilation, groups, output_mask[0], output_mask[1]);
+        if (output_mask[2]) gb3 = grad_output.sum(at::IntArrayRef({0, 2, 3, 4}));
+        return std::make_tuple(gx3, gw3, gb3);
+    }
+    TORCH_CHECK(input.dim() == 4 && weight.dim() == 4, "torchvulkan [NOT IMPLEMENTED]: convolution of ", input.dim() - 2, " spatial dimensions");
     const Vec2 pd = pair_of(padding, 0), dl = pair_of(dilation, 1);
     const Vec2 st = effective_stride(input, weight, pair_of(stride, 1), pd, pair_of(output_padding, 0));
     if (!transposed && groups == 1) return conv2d_dense_backward(grad_output, input, weight, {st[0], st[1]}, padding, dilation, false, 1, output_mask);
