@@ -269,6 +269,11 @@ TVK_API int tvk_gemm_workspace_size(const tvk_gemm_desc* d, uint64_t* bytes);
 TVK_API int tvk_gemm(const tvk_gemm_desc* d, void* workspace, uint64_t workspace_bytes, void* stream);
 /* Which path tvk_gemm would take: 1 = tcgen05 tensor-core kernel, 2 = CUDA-core kernel. */
 TVK_API int tvk_gemm_path(const tvk_gemm_desc* d, int* path);
+/* How many K slices the tensor-core path would cut this product into (1 = a single launch). With more than one, the
+ * slices' fp32 partials are summed by a finishing pass that applies bias, activation, c2 and aux - there the
+ * fused forms cost no tensor-core epilogue time (the counterpart of the reference's split-K partials + at::sum,
+ * src/api/ops/conv.cpp:1034-1060, and of its autotuner's split choice, src/vulkan/autotuner.cpp:123-178). */
+TVK_API int tvk_gemm_splits(const tvk_gemm_desc* d, int* splits);
 /* _scaled_mm: out = cast((A * scale_a) @ (B * scale_b) + bias), A [m, k] and B [k, n] float8 (e4m3fn or e5m2) with
  * element strides, scales fp32 in device memory: one value each (stride 0) or one per row of A and one per column of B
  * (stride 1). Replaces scaled_mm_out_vulkan (src/api/ops/matmul.cpp:706-747), which upcasts both operands to fp32, scales

@@ -221,6 +221,33 @@ def test_fused_epilogue_two_outputs_and_activation_gradient(cuda, dtype, m, n, k
     check(h, np.maximum(ref, 0.0), dtype)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,n,k,tb", [(256, 4096, 4096, True), (128, 2048, 8192, False), (200, 4096, 4096, False)])
+def test_weight_streaming_product_runs_as_k_slices_with_fused_finishing_pass(cuda, dtype, m, n, k, tb):
+    """One or two 128-row tiles against a large weight matrix run as K slices whose finishing pass applies the whole
+    epilogue: bias + activation, the second output and the activation gradient, against the oracle's composition of
+    the separate operators."""
+    a, b = operand(m, k, dtype, 71, False), operand(k, n, dtype, 72, tb)
+    bias = cpu_randn(n, dtype, 73)
+    adev = a.to(cuda)
+    bdev = torch.empty_strided(b.shape, b.stride(), dtype=dtype, device=cuda).copy_(b)
+    z = torch.full((m, n), float("nan"), dtype=dtype, device=cuda)
+    h = torch.full((m, n), float("nan"), dtype=dtype, device=cuda)
+    d = ops().gemm_desc(adev, bdev, z, bias=bias.to(cuda), act="gelu", out2=h)
+    assert ops().gemm_splits(d) > 1
+    ops().gemm(adev, bdev, bias=bias.to(cuda), alpha=0.125, act="gelu", out=z, out2=h)
+    ops().check_device_status()
+    check(z, oracle.gemm(f64(a), f64(b), f64(bias), 0.125, 1.0, None), dtype)
+    check(h, oracle.gemm(f64(a), f64(b), f64(bias), 0.125, 1.0, "gelu"), dtype)
+    plain = ops().gemm(adev, bdev, bias=bias.to(cuda), alpha=0.125)
+    assert torch.equal(plain, z)                              # the same slices, the same sums
+    x = cpu_randn((m, n), dtype, 74)
+    out = torch.full((m, n), float("nan"), dtype=dtype, device=cuda)
+    ops().gemm(adev, bdev, alpha=0.125, out=out, aux=x.to(cuda), aux_op="gelu_backward")
+    ops().check_device_status()
+    check(out, oracle.gelu_backward(oracle.gemm(f64(a), f64(b), None, 0.125), f64(x)), dtype)
+
+
 def test_fused_epilogue_is_refused_off_the_tensor_core_path(cuda):
     from torchvulkan_b200.capi import TvkError
     a, b = cpu_randn((64, 64), torch.float32, 1).to(cuda), cpu_randn((64, 64), torch.float32, 2).to(cuda)

@@ -147,6 +147,7 @@ SIGNATURES = {
     "tvk_rng_set_state": (_i, [_i, _u64, _u64]),
     "tvk_rng_reserve": (_i, [_i, _u64, _P(_u64), _P(_u64)]),
     "tvk_gemm_workspace_size": (_i, [_P(GemmDesc), _P(_u64)]),
+    "tvk_gemm_splits": (_i, [_P(GemmDesc), _P(C.c_int)]),
     "tvk_gemm": (_i, [_P(GemmDesc), _p, _u64, _p]),
     "tvk_gemm_path": (_i, [_P(GemmDesc), _P(_i)]),
     "tvk_debug_gemm_tuning": (_i, [_i, _i, _i, _i, _i]),

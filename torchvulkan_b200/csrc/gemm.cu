@@ -46,6 +46,11 @@ struct Params {
     int act;
     int splits;          // > 1: fp32 partials [batch][split][m][n] go to `partial`
     int64_t k_chunk;     // k range per split (multiple of TK)
+    // split-K epilogue only: the activation-gradient operand of tvk_gemm_desc (C's shape and type, row pitch aux_rs)
+    const void* aux;
+    int64_t aux_rs;
+    int aux_op;
+    void* c2;            // second output (C's strides): C gets the value before the activation, c2 the activated one
 };
 
 
@@ -164,7 +169,13 @@ __global__ void __launch_bounds__(256) splitk_epilogue_vec_kernel(const float* _
         for (int e = 0; e < 4; ++e) {
             float v = p.alpha * o[e];
             if (bias) v += p.beta * to_f32(bias[gm * p.bias_rs + (gn + e) * p.bias_cs]);
-            C[gm * p.c_rs + gn + e] = from_f32<T>(apply_act(v, p.act));
+            if (p.aux_op) v = tc::aux_apply(v, to_f32(((const T*)p.aux)[gm * p.aux_rs + gn + e]), p.aux_op);
+            if (p.c2) {
+                C[gm * p.c_rs + gn + e] = from_f32<T>(v);
+                ((T*)p.c2)[gm * p.c_rs + gn + e] = from_f32<T>(apply_act(v, p.act));
+            } else {
+                C[gm * p.c_rs + gn + e] = from_f32<T>(apply_act(v, p.act));
+            }
         }
     }
 }
@@ -543,6 +554,7 @@ struct GemmTuning {
     int bn = 0, mt = 0, splits = 0, group_m = 0, debug = 0;
 };
 static GemmTuning g_tune;
+static thread_local int t_block_bn = 0, t_block_mt = 0;      // block shape for the launch that run_tc_splitk issues (0 = the cost model's)
 
 static bool fused_epilogue(const tvk_gemm_desc* d) { return d->c2 != nullptr || d->aux_op != TVK_AUX_NONE; }
 
@@ -720,6 +732,7 @@ static int run_simt(const tvk_gemm_desc* d, void* ws, uint64_t ws_bytes, cudaStr
 static int pick_mt(const tvk_gemm_desc* d) {
     if (d->dtype == TVK_F32 || d->m <= tc::BM) return 1;
     if (g_tune.mt == 1 || g_tune.mt == 2) return g_tune.mt;
+    if (t_block_mt) return t_block_mt;
     const char* e = getenv("TORCHVULKAN_GEMM_MT");   // read per call so that a test can switch it
     const int v = e ? atoi(e) : 0;
     return (v == 1 || v == 2) ? v : 0;   // 0: let the cost model decide
@@ -778,7 +791,7 @@ static int run_tc(const tvk_gemm_desc* d, void* ws, uint64_t ws_bytes, cudaStrea
         bn = tc::pick_bn(d->batch, d->m, d->n, 32, 64, 1);
     } else {
         const char* e = getenv("TORCHVULKAN_GEMM_BN");
-        const int v = g_tune.bn ? g_tune.bn : (e ? atoi(e) : 0);
+        const int v = g_tune.bn ? g_tune.bn : (t_block_bn ? t_block_bn : (e ? atoi(e) : 0));
         const int forced_bn = (v == 32 || v == 64 || v == 128 || v == 256) ? v : 0;
         const int min_bn = b_mn ? 128 / es : 32;
         const int lo = forced_bn >= min_bn ? forced_bn : min_bn, hi = forced_bn >= min_bn ? forced_bn : 256;
@@ -857,18 +870,36 @@ static int run_tc(const tvk_gemm_desc* d, void* ws, uint64_t ws_bytes, cudaStrea
 // GPU. Its K range is cut into `splits` equal slices that run as the BATCHES of one ordinary launch (slice s of A
 // and B is the same matrix shifted by s*kc along K, i.e. a batch stride), each writing an fp32 partial, and the
 // partials are summed with the epilogue by simt::splitk_epilogue_kernel.
+// One or two 128-row tiles against a large weight matrix (the forward and input-gradient products of a wide layer at a
+// small batch): every CTA streams its own columns of B over the whole of K, and what bounds the kernel is the rate at
+// which one SM pulls bytes through L2 (about 90 GB/s), not DRAM. 256-column tiles over a slice of K cut the bytes per CTA
+// (256x8192x8192: 128x128 tiles over all of K = 4 MB per CTA, 48.7 us; 128x256 tiles over half of K = 3 MB, 43.8 us
+// including the pass that sums the two fp32 partials). Returns the number of K slices, 0 when the shape is not of this kind.
+static int weight_streaming_splits(const tvk_gemm_desc* d) {
+    if (d->m > 2 * tc::BM || d->n < 2048 || d->k < 4096 || d->n % 4 != 0) return 0;
+    const int64_t base = ((d->m + tc::BM - 1) / tc::BM) * ((d->n + 255) / 256);
+    const int64_t want = (int64_t)sm_count() / base;
+    const int64_t nkb = d->k / 64;
+    int best = 0;
+    for (int sp = 2; sp <= 8 && sp <= want; sp *= 2)
+        if (nkb % sp == 0 && d->k / sp >= 1024) best = sp;
+    return best;
+}
+
 static int tc_splitk_plan(const tvk_gemm_desc* d) {
     static const bool off = getenv("TORCHVULKAN_GEMM_NO_SPLITK") != nullptr;
-    if (off || d->dtype == TVK_F32 || d->c_f32 || d->n_peer_c > 0 || fused_epilogue(d) || d->batch != 1 || d->k < 2048 || d->k % 64 != 0) return 1;
+    // (the fused forms are applied by the finishing pass of the K slices when n % 4 == 0)
+    if (off || d->dtype == TVK_F32 || d->c_f32 || d->n_peer_c > 0 || (fused_epilogue(d) && d->n % 4 != 0) || d->batch != 1 || d->k < 2048 || d->k % 64 != 0) return 1;
     static const int forced = [] {
         const char* e = getenv("TORCHVULKAN_GEMM_SPLITS");
         return e ? atoi(e) : 0;
     }();
     if (g_tune.splits >= 1 && g_tune.splits <= 64 && (d->k / 64) % g_tune.splits == 0) return g_tune.splits;
     if (forced >= 1 && forced <= 64 && (d->k / 64) % forced == 0) return forced;
+    const int64_t nkb = d->k / 64;
+    if (const int ws_splits = weight_streaming_splits(d)) return ws_splits;
     const int64_t tiles = ((d->m + tc::BM - 1) / tc::BM) * ((d->n + 127) / 128);
     if (tiles >= 100) return 1;
-    const int64_t nkb = d->k / 64;
     int best = 1;
     for (int64_t sp = 2; sp <= nkb / 4 && sp <= 64; ++sp) {
         if (nkb % sp != 0) continue;
@@ -889,8 +920,11 @@ static int run_tc_splitk(const tvk_gemm_desc* d, int splits, void* ws, uint64_t 
     part.b_bs = kc * d->b_rs;
     part.c = ws; part.c_rs = d->n; part.c_bs = d->m * d->n; part.c_f32 = 1;
     part.bias = nullptr; part.alpha = 1.f; part.beta = 0.f; part.activation = TVK_ACT_NONE;
+    part.aux = nullptr; part.aux_op = TVK_AUX_NONE; part.c2 = nullptr;
     if (!tc_eligible(&part)) return -1;                      // the caller runs the unsplit kernel
+    if (weight_streaming_splits(d) == splits) { t_block_bn = 256; t_block_mt = 1; }
     int rc = run_tc(&part, nullptr, 0, s);
+    t_block_bn = t_block_mt = 0;
     if (rc) return rc;
     simt::Params p = {};
     p.m = d->m; p.n = d->n; p.k = d->k;
@@ -898,6 +932,8 @@ static int run_tc_splitk(const tvk_gemm_desc* d, int splits, void* ws, uint64_t 
     p.bias_rs = d->bias_rs; p.bias_cs = d->bias_cs; p.bias_bs = d->bias_bs;
     p.alpha = d->alpha; p.beta = d->beta; p.act = d->activation;
     p.splits = splits;
+    p.aux = d->aux_op ? d->aux : nullptr; p.aux_rs = d->aux_rs; p.aux_op = d->aux_op;
+    p.c2 = d->c2;
     const int64_t total = d->m * d->n;
     if (d->n % 4 == 0) {
         int64_t blocks = (total / 4 + 255) / 256;
@@ -950,6 +986,24 @@ int tvk_gemm_path(const tvk_gemm_desc* d, int* path) {
     if (!path) return set_error(TVK_ERR_INVALID, "tvk_gemm_path: null output");
     *path = choose_path(d);
     if (*path == 0) return set_error(TVK_ERR_UNSUPPORTED, "tvk_gemm: operands cannot be addressed by the tensor-core path");
+    return TVK_OK;
+}
+
+int tvk_gemm_splits(const tvk_gemm_desc* d, int* splits) {
+    int rc = validate(d);
+    if (rc) return rc;
+    if (!splits) return set_error(TVK_ERR_INVALID, "tvk_gemm_splits: null output");
+    *splits = 1;
+    if (d->batch == 0 || d->m == 0 || d->n == 0 || d->k == 0) return TVK_OK;
+    if (choose_path(d) != 1) return TVK_OK;
+    if (!tc_eligible(d)) {
+        const Repack r = plan_repack(d);
+        if (!(r.a || r.b)) return TVK_OK;
+        tvk_gemm_desc e = repacked_desc(d, r, (void*)256);
+        *splits = tc_splitk_plan(&e);
+        return TVK_OK;
+    }
+    *splits = tc_splitk_plan(d);
     return TVK_OK;
 }
 

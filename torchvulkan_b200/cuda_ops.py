@@ -86,6 +86,14 @@ def gemm_desc(a, b, out, bias=None, alpha=1.0, beta=1.0, act=None, force_path=0,
     return d
 
 
+def gemm_splits(d: capi.GemmDesc) -> int:
+    """K slices the tensor-core path cuts this product into (1 = one launch; more = slices + a finishing pass in which
+    the fused forms are free)."""
+    n = C.c_int(0)
+    capi.call("tvk_gemm_splits", C.byref(d), C.byref(n))
+    return n.value
+
+
 def gemm(a, b, bias=None, alpha=1.0, beta=1.0, act=None, out=None, force_path=0, out2=None, aux=None, aux_op=None):
     batch = max(a.shape[0] if a.dim() == 3 else 1, b.shape[0] if b.dim() == 3 else 1)
     m, n = a.shape[-2], b.shape[-1]

@@ -98,10 +98,13 @@ class MLPStep:
         self._fused_fwd, self._fused_bwd = [False] * self.nl, [False] * self.nl
         for i in range(self.nl):
             plain = ops.gemm_desc(inp, self.w[i].t(), self.z[i], bias=self.b[i])        # addmm
-            if self.fuse_forward and i < self.nl - 1:
+            if (self.fuse_forward or self.fused) and i < self.nl - 1:
                 both = ops.gemm_desc(inp, self.w[i].t(), self.z[i], bias=self.b[i], act="gelu", out2=self.h[i])       # addmm + gelu
-                self._fused_fwd[i] = supported(both)
-                plain = both if self._fused_fwd[i] else plain
+                # inside the tensor-core epilogue the second store costs more than the separate gelu launch saves (measured);
+                # where the product runs as K slices, the finishing pass stores both for free
+                if supported(both) and (self.fuse_forward or ops.gemm_splits(both) > 1):
+                    self._fused_fwd[i] = True
+                    plain = both
             d.append(plain)
             inp = self.h[i] if i < self.nl - 1 else None
         for i in reversed(range(self.nl)):
