@@ -164,6 +164,9 @@ TVK_API int tvk_pointer_device(const void* ptr, int* dev);
 TVK_API int tvk_event_create(void** event);
 TVK_API int tvk_event_destroy(void* event);
 TVK_API int tvk_event_record(int dev, void* event);
+/* Work submitted to `dev`'s stream after this call runs after `event` (recorded on any device) has completed; the host does
+ * not wait (the guard's block(), src/api/guard.cpp:60-75, whose streams are not real in the reference). */
+TVK_API int tvk_event_wait(int dev, void* event);
 TVK_API int tvk_event_synchronize(void* event);
 TVK_API int tvk_event_query(void* event, int* done);
 TVK_API int tvk_event_elapsed_ms(void* start, void* end, float* ms);

@@ -209,3 +209,50 @@ def test_missing_library_fails_loudly(tmp_path, monkeypatch):
     monkeypatch.setattr(capi, "_LIB_PATH", tmp_path / "libtvk.so")
     with pytest.raises(ImportError, match="no fallback"):
         capi.lib()
+
+
+RESIZE_CHILD = textwrap.dedent(
+    """
+    import ctypes as C, sys
+    sys.path.insert(0, {root!r})
+    from torchvulkan_b200 import capi
+    lib = capi.lib()
+    keep = []
+    @capi.RAW_ALLOC_FN
+    def raw_alloc(pp, n):
+        buf = C.create_string_buffer(max(int(n), 16))     # real host bytes stand in for device memory
+        keep.append(buf)
+        pp[0] = C.addressof(buf)
+        return 0
+    @capi.RAW_FREE_FN
+    def raw_free(p):
+        return 0
+    assert lib.tvk_debug_set_raw_allocator(raw_alloc, raw_free, 2) == 0
+    import torch, torchvulkan
+    assert torchvulkan.device_count() == 2
+    st = capi.MemStats()
+    def allocated(dev):
+        assert lib.tvk_mem_get_stats(dev, C.byref(st)) == 0
+        return st.allocated_bytes
+    t = torch.empty(16, dtype=torch.uint8, device="vulkan:1")
+    assert torchvulkan.current_device() == 0 and t.device.index == 1
+    a0, a1 = allocated(0), allocated(1)
+    t.resize_(100000)                                     # grows the storage while vulkan:0 is the current device
+    assert t.numel() == 100000 and t.device.index == 1 and t.untyped_storage().device.index == 1
+    assert allocated(0) == a0, "the new block was taken from the current device instead of the storage's"
+    assert allocated(1) >= a1 + 100000 - 256
+    assert torchvulkan.current_device() == 0
+    # an event recorded on one device and waited on from the other goes through tvk_event_wait
+    ev = C.c_void_p(64)                                   # no CUDA here: any non-null handle
+    assert lib.tvk_event_wait(1, ev) == 0
+    assert lib.tvk_event_wait(5, ev) != 0 and lib.tvk_event_wait(1, None) == capi.ERR_INVALID
+    print("RESIZE-OK")
+    """
+)
+
+
+def test_resize_allocates_on_the_storage_device_with_two_fake_devices():
+    """resize_ of a vulkan:1 tensor while vulkan:0 is current must take the new block from device 1 (the hook
+    resizePrivateUse1Bytes, src/api/hook.cpp:53-83 in the reference)."""
+    out = subprocess.run([sys.executable, "-c", RESIZE_CHILD.format(root=str(ROOT))], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and "RESIZE-OK" in out.stdout, out.stdout[-2000:] + out.stderr[-4000:]

@@ -649,7 +649,7 @@ def test_hot_ops_raise_instead_of_falling_back(vk):
     with pytest.raises(RuntimeError, match="cannot be multiplied"):
         torch.ones(3, 4, device=vk) @ torch.ones(5, 6, device=vk)
     with pytest.raises((RuntimeError, NotImplementedError), match="NOT IMPLEMENTED"):
-        F.conv2d(torch.ones(1, 4, 5, 5, device=vk), torch.ones(4, 2, 3, 3, device=vk), groups=2)
+        F.conv_transpose3d(torch.ones(1, 4, 3, 5, 5, device=vk), torch.ones(4, 2, 3, 3, 3, device=vk))
 
 
 def test_environment_switches_of_the_reference(vk):

@@ -115,7 +115,12 @@ public:
         int dev = 0;
         TVK_CALL(tvk_get_device(&dev));
         c10::Device device(c10::DeviceType::PrivateUse1, (c10::DeviceIndex)dev);
-        if (nbytes == 0) return {nullptr, nullptr, &delete_block, device};
+        if (nbytes == 0) {
+            int count = 0;
+            TVK_CALL(tvk_device_count(&count));
+            TORCH_CHECK(dev >= 0 && dev < count, "torchvulkan [ERROR]: current device ", dev, " out of range (", count, " devices)");
+            return {nullptr, nullptr, &delete_block, device};
+        }
         void* p = nullptr;
         TVK_CALL(tvk_malloc(dev, nbytes, &p));
         return {p, new Block{p, dev}, &delete_block, device};
@@ -313,7 +318,11 @@ public:
         if (*event == nullptr) TVK_CALL(tvk_event_create(event));
         TVK_CALL(tvk_event_record(stream.device_index(), *event));
     }
-    void block(void*, const c10::Stream&) const override {}  // same in-order stream: already ordered
+    void block(void* event, const c10::Stream& stream) const override {
+        // each device has its own in-order stream: work submitted to `stream`'s device from here on follows the event,
+        // on whichever device it was recorded
+        if (event) TVK_CALL(tvk_event_wait(stream.device_index(), event));
+    }
     bool queryEvent(void* event) const override {
         if (!event) return true;
         int done = 1;
@@ -377,7 +386,19 @@ struct TvkHooks final : public at::PrivateUse1HooksInterface {
     void resizePrivateUse1Bytes(const c10::Storage& storage, size_t newsize) const override {
         c10::StorageImpl* impl = storage.unsafeGetStorageImpl();
         const size_t old = impl->nbytes();
-        c10::DataPtr fresh = g_allocator.allocate(newsize);
+        // the new block belongs on the storage's device, whichever device is current
+        int current = 0;
+        TVK_CALL(tvk_get_device(&current));
+        const int target = storage.device().has_index() ? (int)storage.device().index() : current;
+        if (target != current) TVK_CALL(tvk_set_device(target));
+        c10::DataPtr fresh;
+        try {
+            fresh = g_allocator.allocate(newsize);
+        } catch (...) {
+            if (target != current) tvk_set_device(current);
+            throw;
+        }
+        if (target != current) TVK_CALL(tvk_set_device(current));
         const size_t keep = std::min(old, newsize);
         if (keep) g_allocator.copy_data(fresh.get(), impl->data(), keep);
         impl->set_data_ptr_noswap(std::move(fresh));

@@ -136,6 +136,7 @@ SIGNATURES = {
     "tvk_event_destroy": (_i, [_p]),
     "tvk_event_record": (_i, [_i, _p]),
     "tvk_event_synchronize": (_i, [_p]),
+    "tvk_event_wait": (_i, [C.c_int, _p]),
     "tvk_event_query": (_i, [_p, _P(_i)]),
     "tvk_event_elapsed_ms": (_i, [_p, _p, _P(C.c_float)]),
     "tvk_graph_begin_capture": (_i, [_i]),

@@ -117,18 +117,29 @@ __global__ void pad_channels_kernel(T* __restrict__ dst, const T* __restrict__ s
     }
 }
 
-// partial fp32 [splits][taps][O][Ip] -> dw OIHW [O, I, taps] in T
+// partial fp32 [splits][taps][O][Ip] -> dw OIHW [O, I, taps] (or channels-last [O, taps, I]) in T. Threads walk the
+// partials in their own memory order (input channel fastest), so the reads of each slice are coalesced, and the loads of
+// eight slices are issued together before they are added in slice order (a dependent load-add chain over up to 64 slices,
+// with one 4-byte value used per 32-byte sector, made this kernel 11-16 us for a 64x64x3x3 filter).
 template <typename T>
 __global__ void wgrad_finalize_kernel(T* __restrict__ dw, const float* __restrict__ partial, int splits, int taps, int O, int I, int Ip,
                                       int dst_channels_last) {
-    const int64_t total = (int64_t)O * I * taps;
+    const int64_t total = (int64_t)taps * O * I, slice = (int64_t)taps * O * Ip;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
-        int64_t t, i, o;
-        if (dst_channels_last) { i = idx % I; t = (idx / I) % taps; o = idx / ((int64_t)taps * I); }   // memory order [O, T, I]
-        else { t = idx % taps; i = (idx / taps) % I; o = idx / ((int64_t)taps * I); }                  // memory order [O, I, T]
+        const int64_t i = idx % I, o = (idx / I) % O, t = idx / ((int64_t)I * O);
+        const float* src = partial + (t * O + o) * Ip + i;
         float s = 0.f;
-        for (int k = 0; k < splits; ++k) s += partial[(((int64_t)k * taps + t) * O + o) * Ip + i];
-        dw[idx] = from_f32<T>(s);
+        int k = 0;
+        for (; k + 8 <= splits; k += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = src[(int64_t)(k + u) * slice];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) s += v[u];
+        }
+        for (; k < splits; ++k) s += src[(int64_t)k * slice];
+        const int64_t dst = dst_channels_last ? ((o * taps + t) * I + i) : ((o * I + i) * taps + t);
+        dw[dst] = from_f32<T>(s);
     }
 }
 

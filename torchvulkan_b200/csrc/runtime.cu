@@ -658,6 +658,10 @@ int tvk_memcpy_d2d(int dev, void* dst, const void* src, uint64_t bytes) {
     Device* d;
     int rc = get_dev(dev, &d);
     if (rc) return rc;
+    if (g_fake_devices > 0) {       // host-only unit tests: the fake raw allocator hands out host memory
+        memmove(dst, src, (size_t)bytes);
+        return TVK_OK;
+    }
     rc = ensure_stream(d);
     if (rc) return rc;
     DeviceScope scope;
@@ -811,6 +815,21 @@ int tvk_event_record(int dev, void* event) {
     rc = scope.enter(dev);
     if (rc) return rc;
     TVK_CUDA_CHECK(cudaEventRecord((cudaEvent_t)event, d->stream));
+    return TVK_OK;
+}
+
+int tvk_event_wait(int dev, void* event) {
+    TVK_REQUIRE(event, "tvk_event_wait: null event");
+    Device* d;
+    int rc = get_dev(dev, &d);
+    if (rc) return rc;
+    if (g_fake_devices > 0) return TVK_OK;
+    rc = ensure_stream(d);
+    if (rc) return rc;
+    DeviceScope scope;
+    rc = scope.enter(dev);
+    if (rc) return rc;
+    TVK_CUDA_CHECK(cudaStreamWaitEvent(d->stream, (cudaEvent_t)event, 0));
     return TVK_OK;
 }
 
