@@ -171,16 +171,17 @@ def run_reference(args, rank: int):
 
 
 def summarize_trace(trace):
+    """tag -> [launch count, launch count x the MEDIAN launch time in ms]: the median over the repeated steps, so that one
+    slow repetition (a launch that waited for the host) does not move the figure."""
+    import statistics
+
     import torch
 
     torch.cuda.synchronize()
-    agg = {}
+    times = {}
     for tag, a, b in trace:
-        ms = a.elapsed_time(b)
-        e = agg.setdefault(tag, [0, 0.0])
-        e[0] += 1
-        e[1] += ms
-    return agg
+        times.setdefault(tag, []).append(a.elapsed_time(b))
+    return {tag: [len(v), len(v) * statistics.median(v)] for tag, v in times.items()}
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from recorded ncu captures of these kernels (bytes, summary
@@ -309,7 +310,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     line = None
     if rank == 0:
         step.trace = []
-        reps = 5
+        reps = 9
         for _ in range(reps):
             step.step(x, y)
         agg = summarize_trace(step.trace)

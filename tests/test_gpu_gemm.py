@@ -241,6 +241,15 @@ def test_weight_streaming_product_runs_as_k_slices_with_fused_finishing_pass(cud
     check(h, oracle.gemm(f64(a), f64(b), f64(bias), 0.125, 1.0, "gelu"), dtype)
     plain = ops().gemm(adev, bdev, bias=bias.to(cuda), alpha=0.125)
     assert torch.equal(plain, z)                              # the same slices, the same sums
+    # two row tiles take the CTA-pair kernel (tcgen05 cta_group::2); the single-CTA kernel gives the same bits
+    import os
+    os.environ["TORCHVULKAN_GEMM_PAIR"] = "0"
+    try:
+        single = ops().gemm(adev, bdev, bias=bias.to(cuda), alpha=0.125)
+    finally:
+        del os.environ["TORCHVULKAN_GEMM_PAIR"]
+    ops().check_device_status()
+    assert torch.equal(single, plain)
     x = cpu_randn((m, n), dtype, 74)
     out = torch.full((m, n), float("nan"), dtype=dtype, device=cuda)
     ops().gemm(adev, bdev, alpha=0.125, out=out, aux=x.to(cuda), aux_op="gelu_backward")

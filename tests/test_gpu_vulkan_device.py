@@ -185,8 +185,8 @@ def test_sdpa_causal_with_unequal_lengths_matches_aten(vk, L, S):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.float16, 3e-3)])
 def test_layer_norm_group_norm_and_scans(vk, dtype, tol):
-    """native_layer_norm / native_group_norm forward and backward, cumsum / cumprod / logcumsumexp (the rows SURVEY lists
-    next to softmax and RMSNorm; src/api/ops/norm.cpp:264-325, src/api/ops/scan.cpp:104-126) against ATen CPU in fp32."""
+    """native_layer_norm / native_group_norm forward and backward, cumsum / cumprod / logcumsumexp (the row kernels next
+    to softmax and RMSNorm; src/api/ops/norm.cpp:264-325, src/api/ops/scan.cpp:104-126) against ATen CPU in fp32."""
     torch.manual_seed(21)
     x = torch.randn(6, 17, 96).to(dtype)
     ln_c, ln_d = torch.nn.LayerNorm(96), torch.nn.LayerNorm(96).to(dtype).to(vk)

@@ -886,6 +886,18 @@ static int weight_streaming_splits(const tvk_gemm_desc* d) {
     return best;
 }
 
+// The CTA-pair kernel takes the K slices of a weight-streaming product when the output is two row tiles tall, A is
+// K-major and the slices are whole k-blocks. TORCHVULKAN_GEMM_PAIR=0 keeps the single-CTA kernel.
+static bool pair_kernel_ok(const tvk_gemm_desc* part) {
+    const char* e = getenv("TORCHVULKAN_GEMM_PAIR");      // read per call so that a test can switch it
+    if (e && atoi(e) == 0) return false;
+    if (part->dtype != TVK_F16 && part->dtype != TVK_BF16) return false;
+    if (part->m <= tc::BM || part->m > 2 * tc::BM || part->k % 64 != 0 || part->n % 4 != 0) return false;
+    if (part->a_cs != 1) return false;                              // A rows contiguous along k
+    if (!(part->b_rs == 1 || part->b_cs == 1)) return false;
+    return true;
+}
+
 static int tc_splitk_plan(const tvk_gemm_desc* d) {
     static const bool off = getenv("TORCHVULKAN_GEMM_NO_SPLITK") != nullptr;
     // (the fused forms are applied by the finishing pass of the K slices when n % 4 == 0)
@@ -922,10 +934,28 @@ static int run_tc_splitk(const tvk_gemm_desc* d, int splits, void* ws, uint64_t 
     part.bias = nullptr; part.alpha = 1.f; part.beta = 0.f; part.activation = TVK_ACT_NONE;
     part.aux = nullptr; part.aux_op = TVK_AUX_NONE; part.c2 = nullptr;
     if (!tc_eligible(&part)) return -1;                      // the caller runs the unsplit kernel
-    if (weight_streaming_splits(d) == splits) { t_block_bn = 256; t_block_mt = 1; }
-    int rc = run_tc(&part, nullptr, 0, s);
-    t_block_bn = t_block_mt = 0;
-    if (rc) return rc;
+    int rc = -2;
+    if (weight_streaming_splits(d) == splits && pair_kernel_ok(&part)) {
+        // CTA pairs: each CTA loads its own rows of A and half of a 256-column tile of B (gemm_tc_2sm.cu)
+        const bool b_mn = !(part.b_rs == 1 || part.k == 1);
+        const uint32_t fmt = d->dtype == TVK_F16 ? 0u : 1u;
+        const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+        CUtensorMap maps[3] = {};
+        rc = tc::encode_operand(&maps[2], TVK_F32, ws, part.n, part.m, part.n, splits, part.m * part.n, 32, 32);
+        if (rc) return rc;
+        rc = tc::encode_operand(&maps[0], d->dtype, part.a, part.k, part.m, part.a_rs, splits, part.a_bs, 64, 128);
+        if (rc) return rc;
+        if (!b_mn) rc = tc::encode_operand(&maps[1], d->dtype, part.b, part.k, part.n, part.b_cs, splits, part.b_bs, 64, 128);
+        else rc = tc::encode_operand(&maps[1], d->dtype, part.b, part.n, part.k, part.b_rs, splits, part.b_bs, 64, 64);
+        if (rc) return rc;
+        rc = tc::launch_pair(b_mn, maps, part.m, part.n, (int)(kc / 64), splits, idesc, (float*)ws, device_status_word(), g_tune.debug, s);
+        if (rc) return rc;
+    } else {
+        if (weight_streaming_splits(d) == splits) { t_block_bn = 256; t_block_mt = 1; }
+        rc = run_tc(&part, nullptr, 0, s);
+        t_block_bn = t_block_mt = 0;
+        if (rc) return rc;
+    }
     simt::Params p = {};
     p.m = d->m; p.n = d->n; p.k = d->k;
     p.c_rs = d->c_rs; p.c_bs = d->c_bs;

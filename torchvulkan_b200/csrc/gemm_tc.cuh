@@ -660,5 +660,9 @@ int launch_bf16_fused(int bn, int mt, const CUtensorMap* maps, const Params& p, 
 int launch_half_f32out(int bn, int mt, const CUtensorMap* maps, const Params& p, cudaStream_t s);   // f16/bf16 operands, fp32 C
 int launch_tf32(int bn, int mt, const CUtensorMap* maps, const Params& p, cudaStream_t s);          // 3xTF32
 
+// K-sliced product on CTA pairs (gemm_tc_2sm.cu): 256 x 256 tiles of fp32 partial sums, one per pair and K slice.
+struct Params2sm;
+int launch_pair(bool b_mn, const CUtensorMap* maps, int64_t m, int64_t n, int num_kb, int splits, uint32_t idesc, float* partial, int* status, int debug, cudaStream_t s);
+
 }  // namespace tc
 }  // namespace tvk
