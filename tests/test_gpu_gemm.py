@@ -257,6 +257,36 @@ def test_weight_streaming_product_runs_as_k_slices_with_fused_finishing_pass(cud
     check(out, oracle.gelu_backward(oracle.gemm(f64(a), f64(b), None, 0.125), f64(x)), dtype)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("ta,tb", LAYOUTS)
+@pytest.mark.parametrize("m,n,k", [(512, 512, 8192), (2752, 512, 4096), (328, 1376, 2048)])
+def test_few_tiles_long_k_runs_on_cta_pairs(cuda, dtype, m, n, k, ta, tb):
+    """Products with few 256 x 256 tiles and a long K (a decoder layer's weight gradients) run as K slices on CTA pairs
+    (tcgen05 cta_group::2), for all four operand layouts and ragged last tiles; checked against the oracle and, bit for
+    bit, against the single-CTA kernel on the same slices."""
+    import os
+    a, b = operand(m, k, dtype, 81, ta), operand(k, n, dtype, 82, tb)
+    adev = torch.empty_strided(a.shape, a.stride(), dtype=dtype, device=cuda).copy_(a)
+    bdev = torch.empty_strided(b.shape, b.stride(), dtype=dtype, device=cuda).copy_(b)
+    out = torch.full((m, n), float("nan"), dtype=dtype, device=cuda)
+    d = ops().gemm_desc(adev, bdev, out)
+    splits = ops().gemm_splits(d)
+    assert splits > 1
+    ops().gemm(adev, bdev, out=out, alpha=0.5)
+    ops().check_device_status()
+    check(out, oracle.gemm(f64(a), f64(b), None, 0.5), dtype)
+    os.environ["TORCHVULKAN_GEMM_PAIR"] = "0"
+    try:
+        same_slices = ops().gemm_splits(d) == splits
+        single = ops().gemm(adev, bdev, alpha=0.5)
+    finally:
+        del os.environ["TORCHVULKAN_GEMM_PAIR"]
+    ops().check_device_status()
+    check(single, oracle.gemm(f64(a), f64(b), None, 0.5), dtype)
+    if same_slices:
+        assert torch.equal(single, out)
+
+
 def test_fused_epilogue_is_refused_off_the_tensor_core_path(cuda):
     from torchvulkan_b200.capi import TvkError
     a, b = cpu_randn((64, 64), torch.float32, 1).to(cuda), cpu_randn((64, 64), torch.float32, 2).to(cuda)

@@ -886,16 +886,28 @@ static int weight_streaming_splits(const tvk_gemm_desc* d) {
     return best;
 }
 
-// The CTA-pair kernel takes the K slices of a weight-streaming product when the output is two row tiles tall, A is
-// K-major and the slices are whole k-blocks. TORCHVULKAN_GEMM_PAIR=0 keeps the single-CTA kernel.
+// The CTA-pair kernel (gemm_tc_2sm.cu) takes the K slices of a product whose output is more than one row tile tall, with
+// operands that have one unit stride each and slices of whole k-blocks. TORCHVULKAN_GEMM_PAIR=0 keeps the single-CTA kernel.
 static bool pair_kernel_ok(const tvk_gemm_desc* part) {
     const char* e = getenv("TORCHVULKAN_GEMM_PAIR");      // read per call so that a test can switch it
     if (e && atoi(e) == 0) return false;
     if (part->dtype != TVK_F16 && part->dtype != TVK_BF16) return false;
-    if (part->m <= tc::BM || part->m > 2 * tc::BM || part->k % 64 != 0 || part->n % 4 != 0) return false;
-    if (part->a_cs != 1) return false;                              // A rows contiguous along k
+    if (part->m <= tc::BM || part->k % 64 != 0 || part->n % 4 != 0) return false;
+    if (!(part->a_cs == 1 || part->a_rs == 1)) return false;
     if (!(part->b_rs == 1 || part->b_cs == 1)) return false;
     return true;
+}
+
+// K slices for the pair kernel: a product with so few 256 x 256 tiles that at least two slices of each fit the GPU's CTA
+// pairs at once (the weight gradients of a decoder layer, the wide layers of an MLP at a small batch). Such products
+// are bound by L2->SM traffic per CTA, and a pair tile pulls two thirds of the bytes of a 128 x 256 tile. 0 = not this kind.
+static int pair_splits(const tvk_gemm_desc* d) {
+    if (d->batch != 1 || d->k < 2048 || d->k % 64 != 0 || !pair_kernel_ok(d)) return 0;
+    const int64_t tiles = ((d->m + 255) / 256) * ((d->n + 255) / 256), pairs = sm_count() / 2, nkb = d->k / 64;
+    int best = 0;
+    for (int sp = 2; sp <= 8 && tiles * sp <= pairs; sp *= 2)
+        if (nkb % sp == 0 && d->k / sp >= 512) best = sp;
+    return best;
 }
 
 static int tc_splitk_plan(const tvk_gemm_desc* d) {
@@ -909,6 +921,7 @@ static int tc_splitk_plan(const tvk_gemm_desc* d) {
     if (g_tune.splits >= 1 && g_tune.splits <= 64 && (d->k / 64) % g_tune.splits == 0) return g_tune.splits;
     if (forced >= 1 && forced <= 64 && (d->k / 64) % forced == 0) return forced;
     const int64_t nkb = d->k / 64;
+    if (const int p_splits = pair_splits(d)) return p_splits;
     if (const int ws_splits = weight_streaming_splits(d)) return ws_splits;
     const int64_t tiles = ((d->m + tc::BM - 1) / tc::BM) * ((d->n + 127) / 128);
     if (tiles >= 100) return 1;
@@ -935,20 +948,22 @@ static int run_tc_splitk(const tvk_gemm_desc* d, int splits, void* ws, uint64_t 
     part.aux = nullptr; part.aux_op = TVK_AUX_NONE; part.c2 = nullptr;
     if (!tc_eligible(&part)) return -1;                      // the caller runs the unsplit kernel
     int rc = -2;
-    if (weight_streaming_splits(d) == splits && pair_kernel_ok(&part)) {
+    if ((pair_splits(d) == splits || weight_streaming_splits(d) == splits) && pair_kernel_ok(&part)) {
         // CTA pairs: each CTA loads its own rows of A and half of a 256-column tile of B (gemm_tc_2sm.cu)
-        const bool b_mn = !(part.b_rs == 1 || part.k == 1);
+        const bool a_mn = part.a_cs != 1, b_mn = part.b_rs != 1;
         const uint32_t fmt = d->dtype == TVK_F16 ? 0u : 1u;
-        const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+        const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) | ((uint32_t)(256 >> 3) << 17) |
+                               ((uint32_t)(256 >> 4) << 24);
         CUtensorMap maps[3] = {};
         rc = tc::encode_operand(&maps[2], TVK_F32, ws, part.n, part.m, part.n, splits, part.m * part.n, 32, 32);
         if (rc) return rc;
-        rc = tc::encode_operand(&maps[0], d->dtype, part.a, part.k, part.m, part.a_rs, splits, part.a_bs, 64, 128);
+        if (!a_mn) rc = tc::encode_operand(&maps[0], d->dtype, part.a, part.k, part.m, part.a_rs, splits, part.a_bs, 64, 128);
+        else rc = tc::encode_operand(&maps[0], d->dtype, part.a, part.m, part.k, part.a_cs, splits, part.a_bs, 64, 64);
         if (rc) return rc;
         if (!b_mn) rc = tc::encode_operand(&maps[1], d->dtype, part.b, part.k, part.n, part.b_cs, splits, part.b_bs, 64, 128);
         else rc = tc::encode_operand(&maps[1], d->dtype, part.b, part.n, part.k, part.b_rs, splits, part.b_bs, 64, 64);
         if (rc) return rc;
-        rc = tc::launch_pair(b_mn, maps, part.m, part.n, (int)(kc / 64), splits, idesc, (float*)ws, device_status_word(), g_tune.debug, s);
+        rc = tc::launch_pair(a_mn, b_mn, maps, part.m, part.n, (int)(kc / 64), splits, idesc, (float*)ws, device_status_word(), g_tune.debug, s);
         if (rc) return rc;
     } else {
         if (weight_streaming_splits(d) == splits) { t_block_bn = 256; t_block_mt = 1; }

@@ -662,7 +662,7 @@ int launch_tf32(int bn, int mt, const CUtensorMap* maps, const Params& p, cudaSt
 
 // K-sliced product on CTA pairs (gemm_tc_2sm.cu): 256 x 256 tiles of fp32 partial sums, one per pair and K slice.
 struct Params2sm;
-int launch_pair(bool b_mn, const CUtensorMap* maps, int64_t m, int64_t n, int num_kb, int splits, uint32_t idesc, float* partial, int* status, int debug, cudaStream_t s);
+int launch_pair(bool a_mn, bool b_mn, const CUtensorMap* maps, int64_t m, int64_t n, int num_kb, int splits, uint32_t idesc, float* partial, int* status, int debug, cudaStream_t s);
 
 }  // namespace tc
 }  // namespace tvk

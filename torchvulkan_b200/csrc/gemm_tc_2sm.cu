@@ -26,7 +26,7 @@ constexpr int k2smTmemCols = 256;
 struct Params2sm {
     int64_t m, n;
     int num_kb;              // k-blocks of 64 per K slice
-    int tiles_n;             // 256-column tiles
+    int tiles_m, tiles_n;    // 256-row and 256-column tiles
     int splits;              // K slices (the batch index of the tensor maps)
     uint32_t idesc;
     float* partial;          // [splits][m][n]
@@ -105,7 +105,7 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
 }
 
-template <bool B_MN>
+template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c,
                  const Params2sm p) {
@@ -121,7 +121,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();
     const uint32_t pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-    const uint32_t total_tiles = (uint32_t)(p.tiles_n * p.splits);
+    const uint32_t tiles_per_slice = (uint32_t)(p.tiles_m * p.tiles_n);
+    const uint32_t total_tiles = tiles_per_slice * (uint32_t)p.splits;
+    // tile t -> K slice b, row tile tm (fastest: neighbouring pairs share a tile of B), column tile tn
+    auto decode = [&](uint32_t t, int& b, int& tm, int& tn) {
+        const uint32_t bb = t / tiles_per_slice, r = t - bb * tiles_per_slice;
+        b = (int)bb;
+        tn = (int)(r / (uint32_t)p.tiles_m);
+        tm = (int)(r - (uint32_t)tn * (uint32_t)p.tiles_m);
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < k2smStages; ++s) {
@@ -158,7 +166,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             uint32_t phase = 0;
             bool ok = true;
             for (uint32_t t = pair; t < total_tiles && ok; t += npairs) {
-                const int b = (int)(t / (uint32_t)p.tiles_n), tn = (int)(t - (uint32_t)b * (uint32_t)p.tiles_n);
+                int b, tm, tn;
+                decode(t, b, tm, tn);
                 for (int kb = 0; kb < p.num_kb; ++kb) {
                     ok = mbar_wait_cluster(empty0 + 8 * stage, phase ^ 1, abort_flag, p.status, 61);
                     if (!ok) break;
@@ -166,7 +175,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     // both CTAs' copies of this stage are counted on the issuing CTA's barrier, which expects the bytes of both
                     const uint32_t bar = map_to_cta(full0 + 8 * stage, 0);
                     if (rank == 0) mbar_expect_tx(full0 + 8 * stage, 2 * k2smStage);
-                    tma_load_3d_pair(sa, &tmap_a, kb * 64, (int)rank * 128, b, bar);
+                    if (!A_MN) {
+                        tma_load_3d_pair(sa, &tmap_a, kb * 64, tm * 256 + (int)rank * 128, b, bar);
+                    } else {
+                        tma_load_3d_pair(sa, &tmap_a, tm * 256 + (int)rank * 128, kb * 64, b, bar);
+                        tma_load_3d_pair(sa + 64 * 128, &tmap_a, tm * 256 + (int)rank * 128 + 64, kb * 64, b, bar);
+                    }
                     if (!B_MN) {
                         tma_load_3d_pair(sb, &tmap_b, kb * 64, tn * 256 + (int)rank * 128, b, bar);
                     } else {
@@ -190,8 +204,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             int stage = 0;
             uint32_t phase = 0, tphase = 0;
             bool ok = true;
-            const uint32_t b_step = B_MN ? (uint32_t)(16 * 128) : 32u;
-            const uint32_t b_lbo = B_MN ? (uint32_t)(64 * 128) : 16u;
+            // per k-step advance of the descriptor start address and the distance between 64-wide column blocks (MN-major)
+            const uint32_t a_step = A_MN ? (uint32_t)(16 * 128) : 32u, b_step = B_MN ? (uint32_t)(16 * 128) : 32u;
+            const uint32_t a_lbo = A_MN ? (uint32_t)(64 * 128) : 16u, b_lbo = B_MN ? (uint32_t)(64 * 128) : 16u;
             for (uint32_t t = pair; t < total_tiles && ok; t += npairs) {
                 ok = mbar_wait_cluster(tempty, tphase ^ 1, abort_flag, p.status, 64);       // both epilogues have drained the accumulator
                 if (!ok) break;
@@ -204,7 +219,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     const uint32_t sa = smem_u32(smem + stage * k2smStage), sb = sa + k2smStageA;
 #pragma unroll
                     for (int ks = 0; ks < 4 && !(p.debug & 2); ++ks) {
-                        umma_pair(tmem_base, make_smem_desc(sa + ks * 32, 16, 1024), make_smem_desc(sb + ks * b_step, b_lbo, 1024), p.idesc, accumulate);
+                        umma_pair(tmem_base, make_smem_desc(sa + ks * a_step, a_lbo, 1024), make_smem_desc(sb + ks * b_step, b_lbo, 1024), p.idesc, accumulate);
                         accumulate = 1;
                     }
                     // the stage is free again in both CTAs
@@ -226,13 +241,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         bool ok = true;
         const uint32_t tempty_issuer = rank == 0 ? tempty : map_to_cta(tempty, 0);
         for (uint32_t t = pair; t < total_tiles && ok; t += npairs) {
-            const int b = (int)(t / (uint32_t)p.tiles_n), tn = (int)(t - (uint32_t)b * (uint32_t)p.tiles_n);
+            int b, tm, tn;
+            decode(t, b, tm, tn);
             ok = mbar_wait_cluster(tfull, tphase, abort_flag, p.status, 67);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tphase ^= 1;
             tc_fence_after();
-            const int64_t row0 = (int64_t)rank * 128 + lane_window;       // first row of this warp's 32
+            const int64_t row0 = (int64_t)tm * 256 + (int64_t)rank * 128 + lane_window;       // first row of this warp's 32
             const int64_t col0 = (int64_t)tn * 256;
             uint8_t* buf = outbuf + (warp - 2) * k2smOutBuf;
 #pragma unroll 1
@@ -279,25 +295,33 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
 }
 
-// maps[0]: A, box {64 k, 128 rows}; maps[1]: B, box {64 k, 128 rows} (K-major) or {64 columns, 64 k} (MN-major); maps[2]: the fp32
+// maps[0]: A, box {64 k, 128 rows} (K-major) or {64 rows, 64 k} (MN-major); maps[1]: B likewise over its columns; maps[2]: the fp32
 // partials [splits][m][n], box {32 columns, 32 rows}; batch = K slice
-int launch_pair(bool b_mn, const CUtensorMap* maps, int64_t m, int64_t n, int num_kb, int splits, uint32_t idesc, float* partial, int* status, int debug, cudaStream_t s) {
+int launch_pair(bool a_mn, bool b_mn, const CUtensorMap* maps, int64_t m, int64_t n, int num_kb, int splits, uint32_t idesc, float* partial, int* status, int debug,
+                cudaStream_t s) {
     Params2sm p = {};
     p.debug = debug;
-    p.m = m; p.n = n; p.num_kb = num_kb; p.tiles_n = (int)((n + 255) / 256); p.splits = splits; p.idesc = idesc; p.partial = partial; p.status = status;
-    static bool attr_done[2] = {false, false};
-    const int64_t total = (int64_t)p.tiles_n * p.splits;
+    p.m = m; p.n = n; p.num_kb = num_kb; p.tiles_m = (int)((m + 255) / 256); p.tiles_n = (int)((n + 255) / 256); p.splits = splits; p.idesc = idesc;
+    p.partial = partial; p.status = status;
+    static bool attr_done[4] = {false, false, false, false};
+    const int64_t total = (int64_t)p.tiles_m * p.tiles_n * p.splits;
     int pairs = sm_count() / 2;
     if (pairs > total) pairs = (int)total;
     if (pairs < 1) pairs = 1;
-    const void* fn = b_mn ? (const void*)gemm_pair_kernel<true> : (const void*)gemm_pair_kernel<false>;
-    if (!attr_done[b_mn ? 1 : 0]) {
-        cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, k2smSmemBytes);
+    const int which = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
+    const void* fns[4] = {(const void*)gemm_pair_kernel<false, false>, (const void*)gemm_pair_kernel<false, true>, (const void*)gemm_pair_kernel<true, false>,
+                          (const void*)gemm_pair_kernel<true, true>};
+    if (!attr_done[which]) {
+        cudaError_t e = cudaFuncSetAttribute(fns[which], cudaFuncAttributeMaxDynamicSharedMemorySize, k2smSmemBytes);
         if (e != cudaSuccess) return set_error(TVK_ERR_CUDA, "cudaFuncSetAttribute (pair gemm) failed: %s", cudaGetErrorString(e));
-        attr_done[b_mn ? 1 : 0] = true;
+        attr_done[which] = true;
     }
-    if (b_mn) gemm_pair_kernel<true><<<2 * pairs, kThreads, k2smSmemBytes, s>>>(maps[0], maps[1], maps[2], p);
-    else gemm_pair_kernel<false><<<2 * pairs, kThreads, k2smSmemBytes, s>>>(maps[0], maps[1], maps[2], p);
+    switch (which) {
+        case 0: gemm_pair_kernel<false, false><<<2 * pairs, kThreads, k2smSmemBytes, s>>>(maps[0], maps[1], maps[2], p); break;
+        case 1: gemm_pair_kernel<false, true><<<2 * pairs, kThreads, k2smSmemBytes, s>>>(maps[0], maps[1], maps[2], p); break;
+        case 2: gemm_pair_kernel<true, false><<<2 * pairs, kThreads, k2smSmemBytes, s>>>(maps[0], maps[1], maps[2], p); break;
+        default: gemm_pair_kernel<true, true><<<2 * pairs, kThreads, k2smSmemBytes, s>>>(maps[0], maps[1], maps[2], p); break;
+    }
     return launch_status("pair gemm");
 }
 
