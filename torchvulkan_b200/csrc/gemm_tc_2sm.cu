@@ -34,77 +34,6 @@ struct Params2sm {
     int debug;               // timing probes (results undefined): 1 no stores, 2 no MMAs (commits only)
 };
 
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_remote_u32(uint32_t cluster_addr) {
-    uint32_t v;
-    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
-    return v;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// A wait for an arrival made by the other CTA of the pair (a release.cluster arrive, or a tensor-core commit issued there).
-// It polls with test_wait: try_wait parks the thread for a hardware time slice, and a parked waiter was not woken
-// promptly by an arrival from the other CTA (64 k-blocks took 70 us with nothing but loads and signals in flight).
-__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok;
-}
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int site) {
-    for (uint32_t it = 0; it < (kWaitLimit << 3); ++it) {
-        if (mbar_test_wait(bar, parity)) return true;
-        if ((it & 4095) == 4095 && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    if (status && atomicCAS(status, 0, 1) == 0) {
-        status[1] = site;
-        status[2] = (int)blockIdx.x;
-        status[3] = (int)parity;
-    }
-    return false;
-}
-// A TMA tile load into this CTA's shared memory whose completion is counted on a barrier of either CTA of the pair (here
-// always the issuing CTA's): the issuer then waits on ONE barrier per stage for both halves. Not a broadcast: the bytes
-// land in the loading CTA only.
-__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* tmap, int c0, int c1, int c2, uint32_t cluster_bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
-        "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(cluster_bar)
-        : "memory");
-}
-__device__ __forceinline__ void umma_pair(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_c),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// arrives on the given barrier (a shared::cluster address: this CTA's, or the other CTA's through map_to_cta) once the
-// pair's MMAs issued so far are done
-__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
-}
-
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c,
@@ -290,6 +219,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // neither CTA leaves (and frees its barriers and tensor memory) while the other may still signal it or multiply from its shared memory
     cluster_sync_all();
     tc_fence_after();
+    if ((p.debug & 16) && threadIdx.x == 0) ((uint32_t*)p.partial)[blockIdx.x] = own_tmem;      // probe: the address each CTA's allocation returned
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(own_tmem), "r"((uint32_t)k2smTmemCols) : "memory");
     }
