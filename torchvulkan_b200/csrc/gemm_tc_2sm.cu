@@ -31,7 +31,7 @@ struct Params2sm {
     uint32_t idesc;
     float* partial;          // [splits][m][n]
     int* status;
-    int debug;               // timing probes (results undefined): 1 no stores, 2 no MMAs (commits only)
+    int debug;               // probes (results undefined): 1 no stores, 2 no MMAs (commits only), 16 every CTA writes the tensor-memory address it was given into partial[blockIdx.x]
 };
 
 template <bool A_MN, bool B_MN>
