@@ -725,3 +725,27 @@ def test_scaled_mm(vk, rowwise, kinds):
         torch._scaled_mm(a.to(vk), b.to(vk), torch.ones(3).to(vk), torch.ones(1).to(vk), None, None, torch.bfloat16)
     with pytest.raises(ValueError, match="must be fp8"):
         torch._scaled_mm(a.float().to(vk), b.to(vk), torch.ones(()).to(vk), torch.ones(()).to(vk), None, None, torch.bfloat16)
+
+
+def test_conv_bn_folding_for_inference_runs_on_the_device(vk):
+    """Evaluation-mode Conv2d + BatchNorm2d folded into one convolution by torch's own utility
+    (torch.nn.utils.fusion.fuse_conv_bn_eval): the folding arithmetic runs on the device's elementwise kernels, and the
+    folded convolution gives the unfolded pair's output."""
+    from torch.nn.utils.fusion import fuse_conv_bn_eval
+
+    torch.manual_seed(31)
+    conv, bn = torch.nn.Conv2d(16, 24, 3, padding=1), torch.nn.BatchNorm2d(24)
+    with torch.no_grad():
+        bn.running_mean.uniform_(-0.5, 0.5); bn.running_var.uniform_(0.5, 2.0); bn.weight.uniform_(0.5, 1.5); bn.bias.uniform_(-0.3, 0.3)
+    x = torch.randn(4, 16, 12, 10)
+    ref = bn.eval()(conv.eval()(x))
+    dconv, dbn = torch.nn.Conv2d(16, 24, 3, padding=1), torch.nn.BatchNorm2d(24)
+    dconv.load_state_dict(conv.state_dict()); dbn.load_state_dict(bn.state_dict())
+    dconv, dbn = dconv.to(vk).eval(), dbn.to(vk).eval()
+    with torch.no_grad():
+        fused = fuse_conv_bn_eval(dconv, dbn)
+        assert fused.weight.device.type == "vulkan"
+        out = fused(x.to(vk))
+        pair = dbn(dconv(x.to(vk)))
+    close(out, ref, 1e-4)
+    close(pair, ref, 1e-4)
