@@ -110,6 +110,10 @@ constexpr float kLog2e = 1.4426950408889634f;
 template <typename T> __device__ __forceinline__ float exp_shifted(float x, float m, float m_log2e) {
     return sizeof(T) == 2 ? ex2_approx(fmaf(x, kLog2e, -m_log2e)) : expf(x - m);
 }
+// float8 product on the tensor cores (gemm.cu), for scaled_mm.cu: see the definitions for the operand rules
+bool f8_product_ok(const void* a, int64_t a_rs, int64_t a_cs, const void* b, int64_t b_rs, int64_t b_cs, int64_t m, int64_t n, int64_t k);
+int f8_product(int a_kind, int b_kind, const void* a, int64_t a_rs, const void* b, int64_t b_cs, int64_t m, int64_t n, int64_t k, float* acc, int64_t acc_pitch,
+               cudaStream_t s);
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // ---- warp / block reductions --------------------------------------------------

@@ -448,7 +448,8 @@ static int encode_operand(CUtensorMap* map, int dtype, const void* ptr, int64_t 
     const int es = (int)dtype_size(dtype);
     CUtensorMapDataType dt = dtype == TVK_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                              : dtype == TVK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+                             : dtype == TVK_U8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8          // float8 operands travel as bytes
+                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
     cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)(batch > 0 ? batch : 1)};
     cuuint64_t bstride = (cuuint64_t)batch_stride_elems * es;
     if (batch <= 1 || bstride == 0) {
@@ -863,6 +864,54 @@ static int run_tc(const tvk_gemm_desc* d, void* ws, uint64_t ws_bytes, cudaStrea
     if (d->dtype == TVK_F16) return fused ? tc::launch_f16_fused(bn, mt, maps, p, s) : tc::launch_f16(bn, mt, maps, p, s);
     if (d->dtype == TVK_BF16) return fused ? tc::launch_bf16_fused(bn, mt, maps, p, s) : tc::launch_bf16(bn, mt, maps, p, s);
     return set_error(TVK_ERR_INVALID, "tvk_gemm: internal tile selection error");
+}
+
+// ---- float8 product (used by scaled_mm.cu) ---------------------------------------------------------------
+// acc[m][acc_pitch] (fp32) = A @ B for float8 operands read in place: A rows and B columns contiguous along k (both
+// "K-major": the layout torch._scaled_mm asks for), 16-byte aligned with pitches that are multiples of 16. kinds: 0 = e4m3,
+// 1 = e5m2 per operand. tcgen05.mma kind::f8f6f4, 128 values of K per stage.
+bool f8_product_ok(const void* a, int64_t a_rs, int64_t a_cs, const void* b, int64_t b_rs, int64_t b_cs, int64_t m, int64_t n, int64_t k) {
+    static const bool off = getenv("TORCHVULKAN_SCALED_MM_WIDEN") != nullptr;       // keep the widening path (tests compare the two)
+    if (off || m <= 0 || n <= 0 || k <= 0) return false;
+    if (!tc::tma_ok(a, m, k, a_rs, a_cs, 0, 1, 1) || a_cs != 1) return false;
+    if (!tc::tma_ok(b, k, n, b_rs, b_cs, 0, 1, 1) || b_rs != 1) return false;
+    return m <= 0x7fffffffLL && n <= 0x7fffffffLL && k <= 0x7fffffffLL;
+}
+
+int f8_product(int a_kind, int b_kind, const void* a, int64_t a_rs, const void* b, int64_t b_cs, int64_t m, int64_t n, int64_t k, float* acc, int64_t acc_pitch,
+               cudaStream_t s) {
+    tc::Params p = {};
+    p.m = m; p.n = n; p.batch = 1;
+    const int bk = 128;
+    p.num_kb = (int)((k + bk - 1) / bk);
+    p.passes = 1;
+    p.chunk_kb = 2;
+    int mt = m <= tc::BM ? 1 : 0, bn = 128;
+    // the cost model counts k-blocks of 128 bytes: a float8 k-block holds 128 values, a 16-bit one 64
+    tc::pick_block(1, m, n, k / 2 > 0 ? k / 2 : 1, 32, 256, mt == 0 ? 1 : mt, mt == 0 ? 2 : mt, &mt, &bn);
+    p.tiles_m = (int)((m + mt * tc::BM - 1) / (mt * tc::BM));
+    p.tiles_n = (int)((n + bn - 1) / bn);
+    p.total_tiles = (int64_t)p.tiles_m * p.tiles_n;
+    if (p.total_tiles >= ((int64_t)1 << 31)) return set_error(TVK_ERR_UNSUPPORTED, "torchvulkan [NOT IMPLEMENTED]: matmul with %lld output tiles", (long long)p.total_tiles);
+    p.c = acc; p.c_rs = acc_pitch; p.c_bs = 0;
+    p.alpha = 1.f; p.beta = 0.f; p.act = TVK_ACT_NONE; p.out_dtype = TVK_F32;
+    p.status = device_status_word();
+    p.group_m = 8;
+    p.idesc = (1u << 4) | ((uint32_t)a_kind << 7) | ((uint32_t)b_kind << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(tc::BM >> 4) << 24);
+    CUtensorMap maps[6] = {};
+    int rc = tc::encode_operand(&maps[0], TVK_U8, a, k, m, a_rs, 1, 0, bk, mt * tc::BM);
+    if (rc) return rc;
+    maps[1] = maps[0];
+    rc = tc::encode_operand(&maps[2], TVK_U8, b, k, n, b_cs, 1, 0, bk, bn);
+    if (rc) return rc;
+    maps[3] = maps[2];
+    const bool aligned = ((uintptr_t)acc & 15) == 0 && (acc_pitch * 4) % 16 == 0;
+    p.tma_store = (aligned && bn % 32 == 0) ? 1 : 0;
+    if (p.tma_store) {
+        rc = tc::encode_operand(&maps[4], TVK_F32, acc, n, m, acc_pitch, 1, 0, 32, 32);
+        if (rc) return rc;
+    }
+    return tc::launch_f8_f32out(bn, mt, maps, p, s);
 }
 
 // ---- split-K on the tensor-core path ------------------------------------------------------------------

@@ -385,7 +385,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
                                 for (int mt = 0; mt < MT; ++mt) {
                                     // tile mt of the block: its 128 rows (K-major) or its column blocks (MN-major) start BM*128 bytes on
                                     const uint64_t adesc = make_smem_desc(sa + mt * (BM * 128) + ks * a_step, a_lbo, a_sbo);
-                                    umma<ES == 4>(tmem_c + (uint32_t)(mt * BN), adesc, bdesc, p.idesc, accumulate);
+                                    if constexpr (ES == 1) umma_f8(tmem_c + (uint32_t)(mt * BN), adesc, bdesc, p.idesc, accumulate);
+                                    else umma<ES == 4>(tmem_c + (uint32_t)(mt * BN), adesc, bdesc, p.idesc, accumulate);
                                 }
                                 accumulate = 1;
                             }
@@ -643,10 +644,10 @@ static int launch_family(int bn, int mt, const CUtensorMap* maps, const Params& 
         return launch<32, 4, 1, OUT, FUSED>(maps, p, s);
     } else {
         switch (bn) {
-            case 256: return mt == 2 ? launch<256, 2, 2, OUT, FUSED>(maps, p, s) : launch<256, 2, 1, OUT, FUSED>(maps, p, s);
-            case 128: return mt == 2 ? launch<128, 2, 2, OUT, FUSED>(maps, p, s) : launch<128, 2, 1, OUT, FUSED>(maps, p, s);
-            case 64: return mt == 2 ? launch<64, 2, 2, OUT, FUSED>(maps, p, s) : launch<64, 2, 1, OUT, FUSED>(maps, p, s);
-            case 32: return mt == 2 ? launch<32, 2, 2, OUT, FUSED>(maps, p, s) : launch<32, 2, 1, OUT, FUSED>(maps, p, s);
+            case 256: return mt == 2 ? launch<256, ES, 2, OUT, FUSED>(maps, p, s) : launch<256, ES, 1, OUT, FUSED>(maps, p, s);
+            case 128: return mt == 2 ? launch<128, ES, 2, OUT, FUSED>(maps, p, s) : launch<128, ES, 1, OUT, FUSED>(maps, p, s);
+            case 64: return mt == 2 ? launch<64, ES, 2, OUT, FUSED>(maps, p, s) : launch<64, ES, 1, OUT, FUSED>(maps, p, s);
+            case 32: return mt == 2 ? launch<32, ES, 2, OUT, FUSED>(maps, p, s) : launch<32, ES, 1, OUT, FUSED>(maps, p, s);
         }
         return set_error(TVK_ERR_INVALID, "tvk_gemm: internal tile selection error");
     }
@@ -659,6 +660,7 @@ int launch_bf16(int bn, int mt, const CUtensorMap* maps, const Params& p, cudaSt
 int launch_bf16_fused(int bn, int mt, const CUtensorMap* maps, const Params& p, cudaStream_t s);
 int launch_half_f32out(int bn, int mt, const CUtensorMap* maps, const Params& p, cudaStream_t s);   // f16/bf16 operands, fp32 C
 int launch_tf32(int bn, int mt, const CUtensorMap* maps, const Params& p, cudaStream_t s);          // 3xTF32
+int launch_f8_f32out(int bn, int mt, const CUtensorMap* maps, const Params& p, cudaStream_t s);     // float8 operands (kind::f8f6f4), fp32 C
 
 // K-sliced product on CTA pairs (gemm_tc_2sm.cu): 256 x 256 tiles of fp32 partial sums, one per pair and K slice.
 struct Params2sm;

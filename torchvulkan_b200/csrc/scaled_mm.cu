@@ -92,6 +92,31 @@ using namespace tvk;
 
 extern "C" {
 
+static int scaled_finish(const tvk_scaled_mm_desc* d, const float* acc, int64_t acc_pitch, cudaStream_t s) {
+    const unsigned blocks = grid_for(d->m * d->n);
+#define TVK_SCALED_FINISH(TO, TB)                                                                                                                           \
+    scaled_mm_finish_kernel<TO, TB><<<blocks, 256, 0, s>>>((TO*)d->out, acc, d->m, d->n, acc_pitch, d->scale_a, d->sa_stride, d->scale_b, d->sb_stride,          \
+                                                          (const TB*)d->bias, fp8_out ? d->scale_result : nullptr, out8_kind)
+#define TVK_SCALED_FINISH_OUT(TO)                                                   \
+    do {                                                                            \
+        if (!d->bias || d->bias_dtype == TVK_F32) { TVK_SCALED_FINISH(TO, float); } \
+        else if (d->bias_dtype == TVK_F16) { TVK_SCALED_FINISH(TO, __half); }       \
+        else { TVK_SCALED_FINISH(TO, __nv_bfloat16); }                              \
+    } while (0)
+    // scale_result divides the product only when the output is float8 (matmul.cpp:736-738)
+    const bool fp8_out = d->out_kind == TVK_SCALED_OUT_E4M3 || d->out_kind == TVK_SCALED_OUT_E5M2;
+    const int out8_kind = d->out_kind == TVK_SCALED_OUT_E5M2 ? TVK_F8_E5M2 : TVK_F8_E4M3;
+    switch (d->out_kind) {
+        case TVK_SCALED_OUT_F32: TVK_SCALED_FINISH_OUT(float); break;
+        case TVK_SCALED_OUT_F16: TVK_SCALED_FINISH_OUT(__half); break;
+        case TVK_SCALED_OUT_BF16: TVK_SCALED_FINISH_OUT(__nv_bfloat16); break;
+        default: TVK_SCALED_FINISH_OUT(uint8_t); break;
+    }
+#undef TVK_SCALED_FINISH_OUT
+#undef TVK_SCALED_FINISH
+    return launch_status("scaled mm finish");
+}
+
 static int scaled_validate(const tvk_scaled_mm_desc* d, const char* who) {
     if (!d) return set_error(TVK_ERR_INVALID, "%s: null descriptor", who);
     TVK_REQUIRE(d->m >= 0 && d->n >= 0 && d->k >= 0, "%s: negative extent", who);
@@ -139,6 +164,13 @@ int tvk_scaled_mm(const tvk_scaled_mm_desc* d, void* workspace, uint64_t workspa
     __half* b16 = (__half*)((uint8_t*)workspace + p.a_bytes);
     float* acc = (float*)((uint8_t*)workspace + p.a_bytes + p.b_bytes);
     void* gws = (uint8_t*)workspace + p.total;
+    if (f8_product_ok(d->a, d->a_rs, d->a_cs, d->b, d->b_rs, d->b_cs, d->m, d->n, d->k)) {
+        // the operands are read in place by the tensor cores (tcgen05.mma kind::f8f6f4); products of float8 values are exact
+        // in the fp32 accumulator, as they are in the reference's emulation
+        rc = f8_product(d->a_kind, d->b_kind, d->a, d->a_rs, d->b, d->b_cs, d->m, d->n, d->k, acc, p.np, s);
+        if (rc) return rc;
+        return scaled_finish(d, acc, p.np, s);
+    }
     fp8_widen_kernel<<<grid_for(d->m * p.kp), 256, 0, s>>>(a16, (const uint8_t*)d->a, d->m, d->k, p.kp, d->a_rs, d->a_cs, d->a_kind);
     // B is read as its transpose: row j of the widened copy is column j of B
     fp8_widen_kernel<<<grid_for(d->n * p.kp), 256, 0, s>>>(b16, (const uint8_t*)d->b, d->n, d->k, p.kp, d->b_cs, d->b_rs, d->b_kind);
@@ -148,28 +180,7 @@ int tvk_scaled_mm(const tvk_scaled_mm_desc* d, void* workspace, uint64_t workspa
     fill_gemm(&g, d, p, a16, b16, acc);
     rc = tvk_gemm(&g, gws, workspace_bytes - p.total, stream);
     if (rc) return rc;
-    const unsigned blocks = grid_for(d->m * d->n);
-#define TVK_SCALED_FINISH(TO, TB)                                                                                                                           \
-    scaled_mm_finish_kernel<TO, TB><<<blocks, 256, 0, s>>>((TO*)d->out, acc, d->m, d->n, p.np, d->scale_a, d->sa_stride, d->scale_b, d->sb_stride,          \
-                                                          (const TB*)d->bias, fp8_out ? d->scale_result : nullptr, out8_kind)
-#define TVK_SCALED_FINISH_OUT(TO)                                                   \
-    do {                                                                            \
-        if (!d->bias || d->bias_dtype == TVK_F32) { TVK_SCALED_FINISH(TO, float); } \
-        else if (d->bias_dtype == TVK_F16) { TVK_SCALED_FINISH(TO, __half); }       \
-        else { TVK_SCALED_FINISH(TO, __nv_bfloat16); }                              \
-    } while (0)
-    // scale_result divides the product only when the output is float8 (matmul.cpp:736-738)
-    const bool fp8_out = d->out_kind == TVK_SCALED_OUT_E4M3 || d->out_kind == TVK_SCALED_OUT_E5M2;
-    const int out8_kind = d->out_kind == TVK_SCALED_OUT_E5M2 ? TVK_F8_E5M2 : TVK_F8_E4M3;
-    switch (d->out_kind) {
-        case TVK_SCALED_OUT_F32: TVK_SCALED_FINISH_OUT(float); break;
-        case TVK_SCALED_OUT_F16: TVK_SCALED_FINISH_OUT(__half); break;
-        case TVK_SCALED_OUT_BF16: TVK_SCALED_FINISH_OUT(__nv_bfloat16); break;
-        default: TVK_SCALED_FINISH_OUT(uint8_t); break;
-    }
-#undef TVK_SCALED_FINISH_OUT
-#undef TVK_SCALED_FINISH
-    return launch_status("scaled mm finish");
+    return scaled_finish(d, acc, p.np, s);
 }
 
 }  // extern "C"

@@ -89,6 +89,15 @@ __device__ __forceinline__ void umma(uint32_t tmem_c, uint64_t adesc, uint64_t b
     }
 }
 
+// float8 operands (e4m3 / e5m2 chosen per operand in the instruction descriptor), fp32 accumulation; K = 32 per instruction
+__device__ __forceinline__ void umma_f8(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_c),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
