@@ -112,8 +112,15 @@ template <typename T> __device__ __forceinline__ float exp_shifted(float x, floa
 }
 // float8 product on the tensor cores (gemm.cu), for scaled_mm.cu: see the definitions for the operand rules
 bool f8_product_ok(const void* a, int64_t a_rs, int64_t a_cs, const void* b, int64_t b_rs, int64_t b_cs, int64_t m, int64_t n, int64_t k);
-int f8_product(int a_kind, int b_kind, const void* a, int64_t a_rs, const void* b, int64_t b_cs, int64_t m, int64_t n, int64_t k, float* acc, int64_t acc_pitch,
-               cudaStream_t s);
+// What the product kernel's epilogue applies to the accumulator: out = cast(acc * row_scale[r] * col_scale[c] + bias[c]).
+// col_scale == nullptr: the plain product. bias (one value per column) has the output's dtype.
+struct F8Epilogue {
+    const float* row_scale; int64_t row_scale_stride;
+    const float* col_scale; int64_t col_scale_stride;
+    const void* bias;
+};
+int f8_product(int a_kind, int b_kind, const void* a, int64_t a_rs, const void* b, int64_t b_cs, int64_t m, int64_t n, int64_t k, void* out, int out_dtype,
+               int64_t out_pitch, const F8Epilogue* epi, cudaStream_t s);
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // ---- warp / block reductions --------------------------------------------------

@@ -878,8 +878,9 @@ bool f8_product_ok(const void* a, int64_t a_rs, int64_t a_cs, const void* b, int
     return m <= 0x7fffffffLL && n <= 0x7fffffffLL && k <= 0x7fffffffLL;
 }
 
-int f8_product(int a_kind, int b_kind, const void* a, int64_t a_rs, const void* b, int64_t b_cs, int64_t m, int64_t n, int64_t k, float* acc, int64_t acc_pitch,
-               cudaStream_t s) {
+int f8_product(int a_kind, int b_kind, const void* a, int64_t a_rs, const void* b, int64_t b_cs, int64_t m, int64_t n, int64_t k, void* out, int out_dtype,
+               int64_t out_pitch, const F8Epilogue* epi, cudaStream_t s) {
+    if (out_dtype != TVK_F32 && out_dtype != TVK_F16 && out_dtype != TVK_BF16) return set_error(TVK_ERR_INVALID, "float8 product: output dtype %d", out_dtype);
     tc::Params p = {};
     p.m = m; p.n = n; p.batch = 1;
     const int bk = 128;
@@ -893,8 +894,13 @@ int f8_product(int a_kind, int b_kind, const void* a, int64_t a_rs, const void* 
     p.tiles_n = (int)((n + bn - 1) / bn);
     p.total_tiles = (int64_t)p.tiles_m * p.tiles_n;
     if (p.total_tiles >= ((int64_t)1 << 31)) return set_error(TVK_ERR_UNSUPPORTED, "torchvulkan [NOT IMPLEMENTED]: matmul with %lld output tiles", (long long)p.total_tiles);
-    p.c = acc; p.c_rs = acc_pitch; p.c_bs = 0;
-    p.alpha = 1.f; p.beta = 0.f; p.act = TVK_ACT_NONE; p.out_dtype = TVK_F32;
+    p.c = out; p.c_rs = out_pitch; p.c_bs = 0;
+    p.alpha = 1.f; p.beta = 0.f; p.act = TVK_ACT_NONE; p.out_dtype = out_dtype;
+    if (epi) {
+        p.row_scale = epi->row_scale; p.row_scale_stride = (int)epi->row_scale_stride;
+        p.col_scale = epi->col_scale; p.col_scale_stride = (int)epi->col_scale_stride;
+        if (epi->bias) { p.bias = epi->bias; p.bias_rs = 0; p.bias_cs = 1; p.bias_bs = 0; p.beta = 1.f; }
+    }
     p.status = device_status_word();
     p.group_m = 8;
     p.idesc = (1u << 4) | ((uint32_t)a_kind << 7) | ((uint32_t)b_kind << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(tc::BM >> 4) << 24);
@@ -905,12 +911,16 @@ int f8_product(int a_kind, int b_kind, const void* a, int64_t a_rs, const void* 
     rc = tc::encode_operand(&maps[2], TVK_U8, b, k, n, b_cs, 1, 0, bk, bn);
     if (rc) return rc;
     maps[3] = maps[2];
-    const bool aligned = ((uintptr_t)acc & 15) == 0 && (acc_pitch * 4) % 16 == 0;
-    p.tma_store = (aligned && bn % 32 == 0) ? 1 : 0;
+    const int64_t es_out = out_dtype == TVK_F32 ? 4 : 2;
+    const int gcols = (int)(128 / es_out);
+    const bool aligned = ((uintptr_t)out & 15) == 0 && (out_pitch * es_out) % 16 == 0 && out_pitch * es_out < ((int64_t)1 << 40);
+    p.tma_store = (aligned && bn % gcols == 0) ? 1 : 0;
     if (p.tma_store) {
-        rc = tc::encode_operand(&maps[4], TVK_F32, acc, n, m, acc_pitch, 1, 0, 32, 32);
+        rc = tc::encode_operand(&maps[4], out_dtype, out, n, m, out_pitch, 1, 0, gcols, 32);
         if (rc) return rc;
     }
+    if (out_dtype == TVK_F16) return tc::launch_f8_f16out(bn, mt, maps, p, s);
+    if (out_dtype == TVK_BF16) return tc::launch_f8_bf16out(bn, mt, maps, p, s);
     return tc::launch_f8_f32out(bn, mt, maps, p, s);
 }
 

@@ -46,6 +46,11 @@ struct Params {
     int64_t aux_rs, aux_bs;
     int aux_op;          // TVK_AUX_*: what the epilogue does with aux
     void* peer_c[7];
+    // float8 products only (the scaled product): the accumulator of row r, column c is multiplied by
+    // row_scale[r * row_scale_stride] * col_scale[c * col_scale_stride] before alpha / bias; null col_scale = no scales
+    const float* row_scale;
+    const float* col_scale;
+    int row_scale_stride, col_scale_stride;
 };
 
 // Threads of the GEMM kernel: producer warp, MMA warp and EIGHT epilogue warps. A warp can only read the 32 tensor-memory
@@ -512,6 +517,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__
 #pragma unroll
                             for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
                             if (row_ok) {
+                                if constexpr (ES == 1) {
+                                    if (p.col_scale) {
+                                        const float rsc = __ldg(p.row_scale + row * p.row_scale_stride);
+                                        if (p.col_scale_stride == 0) {
+                                            const float sc = rsc * __ldg(p.col_scale);
+#pragma unroll
+                                            for (int j = 0; j < 32; ++j) v[j] *= sc;
+                                        } else {
+#pragma unroll
+                                            for (int j = 0; j < 32; ++j)
+                                                if (j < ncols) v[j] *= rsc * __ldg(p.col_scale + cbase + j);
+                                        }
+                                    }
+                                }
                                 if constexpr (FUSED) {
                                     epi_scale_bias_act<OUT>(v, p.alpha, p.beta, brow, p.bias_cs, cbase, ncols, TVK_ACT_NONE);
                                     if (arow) {
@@ -661,6 +680,8 @@ int launch_bf16_fused(int bn, int mt, const CUtensorMap* maps, const Params& p, 
 int launch_half_f32out(int bn, int mt, const CUtensorMap* maps, const Params& p, cudaStream_t s);   // f16/bf16 operands, fp32 C
 int launch_tf32(int bn, int mt, const CUtensorMap* maps, const Params& p, cudaStream_t s);          // 3xTF32
 int launch_f8_f32out(int bn, int mt, const CUtensorMap* maps, const Params& p, cudaStream_t s);     // float8 operands (kind::f8f6f4), fp32 C
+int launch_f8_f16out(int bn, int mt, const CUtensorMap* maps, const Params& p, cudaStream_t s);     // float8 operands, fp16 C
+int launch_f8_bf16out(int bn, int mt, const CUtensorMap* maps, const Params& p, cudaStream_t s);    // float8 operands, bf16 C
 
 // K-sliced product on CTA pairs (gemm_tc_2sm.cu): 256 x 256 tiles of fp32 partial sums, one per pair and K slice.
 struct Params2sm;

@@ -2,11 +2,15 @@
 //
 // Replaces scaled_mm_out_vulkan (src/api/ops/matmul.cpp:706-747), which follows torch's CPU emulation: both operands are
 // upcast to fp32 and scaled (one scale each, or a row of A by a column of B), multiplied in fp32, the bias added and the
-// result cast. Here the float8 values are widened to fp16, which holds every e4m3 and e5m2 value exactly, and multiplied
-// by the tcgen05 fp16 kernel with fp32 accumulation - the products are exact, as they are in the emulation - and the
-// scales, which factor out of the sum (sum_k (a_ik s_i)(b_kj t_j) = s_i t_j sum_k a_ik b_kj), the bias and the cast are
-// applied to the fp32 accumulator in one pass. Three launches of staging plus the GEMM; the widening passes read one
-// byte and write two per element.
+// result cast. Products of float8 values are exact in fp32, and the scales factor out of the sum
+// (sum_k (a_ik s_i)(b_kj t_j) = s_i t_j sum_k a_ik b_kj), so the result is acc * (s_i * t_j) + bias with acc the plain
+// product accumulated in fp32 - equal to the emulation up to the order of the fp32 additions. Three routes:
+//  - operands with k contiguous and 16-byte aligned, fp32/fp16/bf16 output: one launch of the tcgen05 kernel for 1-byte
+//    operands (kind::f8f6f4) whose epilogue applies scales, bias and cast;
+//  - the same operands with a float8 output (or a bias of another dtype than the output): that kernel leaves the fp32
+//    accumulator and one finishing pass applies scales, bias, 1/scale_result and the cast;
+//  - any other layout: both operands are widened to fp16, which holds every e4m3 and e5m2 value exactly, multiplied by
+//    the fp16 kernel with fp32 accumulation, and finished by the same pass.
 #include <cuda_fp8.h>
 
 #include "common.cuh"
@@ -27,6 +31,22 @@ __global__ void __launch_bounds__(256) fp8_widen_kernel(__half* __restrict__ out
         out[i] = c < cols ? fp8_widen(in[r * rs + c * cs], kind) : __float2half(0.f);
     }
 }
+// The same for rows that are contiguous, 8-byte aligned and a multiple of 8 long (pitch == cols): eight values per thread.
+__global__ void __launch_bounds__(256) fp8_widen8_kernel(__half* __restrict__ out, const uint8_t* __restrict__ in, int64_t rows, int64_t cols, int64_t rs, int kind) {
+    const int64_t per_row = cols / 8, total = rows * per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / per_row, c = (i - r * per_row) * 8;
+        const uint2 q = __ldg((const uint2*)(in + r * rs + c));
+        const uint32_t w[2] = {q.x, q.y};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __half lo = fp8_widen((uint8_t)(w[j >> 1] >> (16 * (j & 1))), kind), hi = fp8_widen((uint8_t)(w[j >> 1] >> (16 * (j & 1) + 8)), kind);
+            o[j] = (uint32_t)__half_as_ushort(lo) | ((uint32_t)__half_as_ushort(hi) << 16);
+        }
+        *(uint4*)(out + r * cols + c) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
 
 template <typename TO> __device__ __forceinline__ TO scaled_cast(float v, int) { return from_f32<TO>(v); }
 template <> __device__ __forceinline__ uint8_t scaled_cast<uint8_t>(float v, int kind) {
@@ -34,18 +54,27 @@ template <> __device__ __forceinline__ uint8_t scaled_cast<uint8_t>(float v, int
     return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_NOSAT, kind == TVK_F8_E5M2 ? __NV_E5M2 : __NV_E4M3);
 }
 
+// Four adjacent columns of one row per thread (the accumulator's pitch is a multiple of 4, so the 16-byte load is aligned).
 template <typename TO, typename TB>
 __global__ void __launch_bounds__(256) scaled_mm_finish_kernel(TO* __restrict__ out, const float* __restrict__ acc, int64_t m, int64_t n, int64_t acc_pitch,
                                                               const float* __restrict__ sa, int64_t sa_stride, const float* __restrict__ sb, int64_t sb_stride,
                                                               const TB* __restrict__ bias, const float* __restrict__ scale_result, int out_kind) {
-    const int64_t total = m * n;
+    const int64_t n4 = (n + 3) / 4, total = m * n4;
     const float post = scale_result ? 1.0f / scale_result[0] : 1.0f;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = i / n, c = i - r * n;
-        float v = acc[r * acc_pitch + c] * (sa[r * sa_stride] * sb[c * sb_stride]);
-        if (bias) v += to_f32(bias[c]);
-        if (scale_result) v *= post;
-        out[i] = scaled_cast<TO>(v, out_kind);
+        const int64_t r = i / n4, c0 = (i - r * n4) * 4;
+        const float4 q = *(const float4*)(acc + r * acc_pitch + c0);
+        const float a4[4] = {q.x, q.y, q.z, q.w};
+        const float rsc = sa[r * sa_stride];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t c = c0 + j;
+            if (c >= n) break;
+            float v = a4[j] * (rsc * sb[c * sb_stride]);
+            if (bias) v += to_f32(bias[c]);
+            if (scale_result) v *= post;
+            out[r * n + c] = scaled_cast<TO>(v, out_kind);
+        }
     }
 }
 
@@ -93,7 +122,7 @@ using namespace tvk;
 extern "C" {
 
 static int scaled_finish(const tvk_scaled_mm_desc* d, const float* acc, int64_t acc_pitch, cudaStream_t s) {
-    const unsigned blocks = grid_for(d->m * d->n);
+    const unsigned blocks = grid_for(d->m * ((d->n + 3) / 4));
 #define TVK_SCALED_FINISH(TO, TB)                                                                                                                           \
     scaled_mm_finish_kernel<TO, TB><<<blocks, 256, 0, s>>>((TO*)d->out, acc, d->m, d->n, acc_pitch, d->scale_a, d->sa_stride, d->scale_b, d->sb_stride,          \
                                                           (const TB*)d->bias, fp8_out ? d->scale_result : nullptr, out8_kind)
@@ -167,13 +196,26 @@ int tvk_scaled_mm(const tvk_scaled_mm_desc* d, void* workspace, uint64_t workspa
     if (f8_product_ok(d->a, d->a_rs, d->a_cs, d->b, d->b_rs, d->b_cs, d->m, d->n, d->k)) {
         // the operands are read in place by the tensor cores (tcgen05.mma kind::f8f6f4); products of float8 values are exact
         // in the fp32 accumulator, as they are in the reference's emulation
-        rc = f8_product(d->a_kind, d->b_kind, d->a, d->a_rs, d->b, d->b_cs, d->m, d->n, d->k, acc, p.np, s);
+        const int out_dtype = d->out_kind == TVK_SCALED_OUT_F32 ? TVK_F32 : d->out_kind == TVK_SCALED_OUT_F16 ? TVK_F16 : d->out_kind == TVK_SCALED_OUT_BF16 ? TVK_BF16 : -1;
+        static const bool two_pass = getenv("TORCHVULKAN_SCALED_MM_TWO_PASS") != nullptr;      // keep the separate finishing pass (tests compare the two)
+        if (out_dtype >= 0 && (!d->bias || d->bias_dtype == out_dtype) && !two_pass) {
+            // scales, bias and cast in the product kernel's epilogue: the same arithmetic as the finishing pass, acc * (sa * sb) + bias
+            const F8Epilogue e = {d->scale_a, d->sa_stride, d->scale_b, d->sb_stride, d->bias};
+            return f8_product(d->a_kind, d->b_kind, d->a, d->a_rs, d->b, d->b_cs, d->m, d->n, d->k, d->out, out_dtype, d->n, &e, s);
+        }
+        rc = f8_product(d->a_kind, d->b_kind, d->a, d->a_rs, d->b, d->b_cs, d->m, d->n, d->k, acc, TVK_F32, p.np, nullptr, s);
         if (rc) return rc;
         return scaled_finish(d, acc, p.np, s);
     }
-    fp8_widen_kernel<<<grid_for(d->m * p.kp), 256, 0, s>>>(a16, (const uint8_t*)d->a, d->m, d->k, p.kp, d->a_rs, d->a_cs, d->a_kind);
+    auto widen = [&](__half* o, const void* in, int64_t rows, int64_t rs, int64_t cs, int kind) {
+        if (cs == 1 && d->k == p.kp && rs % 8 == 0 && ((uintptr_t)in & 7) == 0)
+            fp8_widen8_kernel<<<grid_for(rows * (p.kp / 8)), 256, 0, s>>>(o, (const uint8_t*)in, rows, p.kp, rs, kind);
+        else
+            fp8_widen_kernel<<<grid_for(rows * p.kp), 256, 0, s>>>(o, (const uint8_t*)in, rows, d->k, p.kp, rs, cs, kind);
+    };
+    widen(a16, d->a, d->m, d->a_rs, d->a_cs, d->a_kind);
     // B is read as its transpose: row j of the widened copy is column j of B
-    fp8_widen_kernel<<<grid_for(d->n * p.kp), 256, 0, s>>>(b16, (const uint8_t*)d->b, d->n, d->k, p.kp, d->b_cs, d->b_rs, d->b_kind);
+    widen(b16, d->b, d->n, d->b_cs, d->b_rs, d->b_kind);
     rc = launch_status("float8 widening");
     if (rc) return rc;
     tvk_gemm_desc g;
