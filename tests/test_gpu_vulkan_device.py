@@ -695,7 +695,9 @@ def test_scaled_mm(vk, rowwise, kinds):
     results differ only by the order of the fp32 additions."""
     f8 = {"e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
     g = torch.Generator().manual_seed(21)
-    for m, k, n in ((48, 72, 40), (33, 70, 37), (256, 512, 128)):
+    # k a multiple of 16: the operands are read in place by the float8 kernel (ragged blocks, aligned and unaligned output
+    # pitches); other k: the widened route
+    for m, k, n in ((48, 72, 40), (33, 70, 37), (256, 512, 128), (200, 272, 136), (130, 144, 100), (300, 1040, 520)):
         a = torch.randn(m, k, generator=g).to(f8[kinds[0]])
         b = torch.randn(n, k, generator=g).to(f8[kinds[1]]).t()              # column-major, as torch's CUDA op wants it
         sa = (torch.rand(m, 1, generator=g) + 0.5) if rowwise else torch.tensor(0.75)
