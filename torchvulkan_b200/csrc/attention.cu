@@ -272,7 +272,7 @@ static int run_fused_forward(int dtype, void* out, float* lse, const void* q, co
     }
     const int64_t ctas = groups * p.tiles_per_group;
     TVK_REQUIRE(ctas <= 0x7fffffffLL && groups * GL <= 0x7fffffffLL, "torchvulkan [NOT IMPLEMENTED]: attention with %lld query rows", (long long)(groups * GL));
-    attn::attn_fwd_fused_kernel<<<(unsigned)ctas, tc::kThreads, attn::kFusedSmemBytes, s>>>(mq, mk, mv, p);
+    attn::attn_fwd_fused_kernel<<<(unsigned)ctas, attn::kFusedThreads, attn::kFusedSmemBytes, s>>>(mq, mk, mv, p);
     return launch_status("fused attention forward");
 }
 

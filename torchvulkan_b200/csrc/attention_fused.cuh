@@ -9,12 +9,16 @@
 // to the top-left corner (key j is visible to query l when j <= l, attention_coop.slang:53-56); all query heads of a KV group are
 // rows of one matrix (row = g*L + l).
 //
-// One CTA per 128 query rows of one (batch, kv head) group, 192 threads:
+// One CTA per 128 query rows of one (batch, kv head) group, 320 threads:
 //   warp 0   TMA: Q tile [128 x 64], K [256 x 64], V [256 x 64] (each row is one 128-byte swizzled line)
 //   warp 1   tcgen05.mma: S = Q.K^T (M=128, N<=256, K=64) into tensor-memory columns [0, 256); later O = P.V
 //            (M=128, N=64, K<=256), with V as an MN-major operand (a key's 64 values are the 128-byte row)
-//   warps 2-5 one query row per thread: two passes over the row of S in tensor memory (max, then exp and sum), P
-//            written to shared memory as the K-major swizzled A operand of the second product, then O / sum -> out.
+//   warps 2-9 the row math, two threads per query row (a warp reads the 32 tensor-memory lanes of its quarter, so two
+//            warps share a quarter and take alternate 32-column chunks): two passes over the row of S in tensor memory
+//            (max, then exp and sum; the two halves of a row meet through shared memory), P written to shared memory
+//            as the K-major swizzled A operand of the second product, then O / sum -> out. The row math is what bounds
+//            the kernel (instruction issue and tensor-memory load latency), hence eight warps and the one-instruction
+//            ex2.approx exponential on chunks that need no mask.
 // O reuses the first 64 tensor-memory columns of S (all rows have been read by then), so a CTA holds 256 columns and
 // two CTAs share an SM. With a causal mask only the key blocks some row of the tile can see are multiplied.
 #pragma once
@@ -29,7 +33,8 @@ constexpr int kFusedTmemCols = 256;                // allocated and freed with t
 constexpr int kSmemQ = 128 * 128, kSmemK = kFusedS * 128, kSmemV = kFusedS * 128, kSmemP = 4 * 128 * 128;
 // P (64 KB) is written after the first product has finished reading Q and K, so it overlays them: V | [Q K ...] = 96 KB,
 // two CTAs per SM (their phases interleave: one multiplies while the other exponentiates).
-constexpr int kFusedSmemBytes = kSmemV + kSmemP + 1024 + 256;
+constexpr int kFusedThreads = 64 + 256;            // producer warp, MMA warp, eight row-math warps
+constexpr int kFusedSmemBytes = kSmemV + kSmemP + 1024 + 256 + 2048;      // + row max and row sum of each half (2 x 2 x 128 floats)
 
 struct FusedParams {
     int L, S;                        // queries per head, keys
@@ -45,7 +50,7 @@ struct FusedParams {
     int* status;
 };
 
-__global__ void __launch_bounds__(tc::kThreads, 2)
+__global__ void __launch_bounds__(kFusedThreads, 2)
 attn_fwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                       const FusedParams p) {
     using namespace tc;
@@ -58,12 +63,14 @@ attn_fwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     uint64_t* bars = (uint64_t*)(sP + kSmemP);
     uint32_t* tmem_slot = (uint32_t*)(bars + 5);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    float* xmax = (float*)((uint8_t*)bars + 256);     // [2][128]: row max found by each half
+    float* xsum = xmax + 256;                         // [2][128]: sum of the rounded probabilities of each half
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t bar_qk = smem_u32(bars), bar_v = smem_u32(bars + 1), bar_s = smem_u32(bars + 2), bar_p = smem_u32(bars + 3),
                    bar_o = smem_u32(bars + 4);
 
     if (threadIdx.x == 0) {
-        mbar_init(bar_qk, 1); mbar_init(bar_v, 1); mbar_init(bar_s, 1); mbar_init(bar_p, 4); mbar_init(bar_o, 1);
+        mbar_init(bar_qk, 1); mbar_init(bar_v, 1); mbar_init(bar_s, 1); mbar_init(bar_p, 8); mbar_init(bar_o, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -125,6 +132,7 @@ attn_fwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         }
     } else {
         const int lane_window = (warp & 3) * 32;
+        const int half = (warp - 2) >> 2;                                  // which of the two warps of this quarter
         const int r = lane_window + lane;                                  // row of the tile
         const int64_t row = row0 + r;
         const int l = (int)(row % p.L);
@@ -133,41 +141,59 @@ attn_fwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         const uint32_t trow = tmem_base + ((uint32_t)lane_window << 16);
         bool ok = mbar_wait(bar_s, 0, abort_flag, p.status, 54);
         ok = __all_sync(0xffffffffu, ok);
+        // chunks that no row of this warp can see are skipped in both passes (their P is zero); chunks that every row sees
+        // in full need no mask
+        const int warp_nvis = __reduce_max_sync(0xffffffffu, nvis), warp_full = __reduce_min_sync(0xffffffffu, nvis);
         float m = -INFINITY, sum = 0.f;
         if (ok) {
             tc_fence_after();
-            // chunks that no row of this warp can see are skipped in both passes (their P is zero)
-            const int warp_nvis = __reduce_max_sync(0xffffffffu, nvis);
 #pragma unroll 1
-            for (int c0 = 0; c0 < kFusedS; c0 += 32) {
+            for (int c0 = half * 32; c0 < kFusedS; c0 += 64) {
                 if (c0 >= warp_nvis) break;
                 uint32_t v[32];
                 tmem_ld32(trow + (uint32_t)c0, v);
                 tmem_ld_wait();
+                if (c0 + 32 <= warp_full) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (c0 + j < nvis) m = fmaxf(m, __uint_as_float(v[j]));
+                    for (int j = 0; j < 32; ++j) m = fmaxf(m, __uint_as_float(v[j]));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (c0 + j < nvis) m = fmaxf(m, __uint_as_float(v[j]));
+                }
             }
+        }
+        xmax[half * 128 + r] = m;
+        asm volatile("bar.sync 1, 256;" ::: "memory");                     // the eight row-math warps
+        m = fmaxf(xmax[r], xmax[128 + r]);
+        if (ok) {
             const float mscaled = m * p.scale_log2e;
 #pragma unroll 1
-            for (int c0 = 0; c0 < nk; c0 += 32) {
+            for (int c0 = half * 32; c0 < nk; c0 += 64) {
                 uint32_t packed[16];
                 if (c0 < warp_nvis) {
                     uint32_t v[32];
                     tmem_ld32(trow + (uint32_t)c0, v);
                     tmem_ld_wait();
+                    const bool full = c0 + 32 <= warp_full;
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const float e0 = (c0 + 2 * j < nvis) ? exp2f(__uint_as_float(v[2 * j]) * p.scale_log2e - mscaled) : 0.f;
-                        const float e1 = (c0 + 2 * j + 1 < nvis) ? exp2f(__uint_as_float(v[2 * j + 1]) * p.scale_log2e - mscaled) : 0.f;
+                        float e0 = ex2_approx(fmaf(__uint_as_float(v[2 * j]), p.scale_log2e, -mscaled));
+                        float e1 = ex2_approx(fmaf(__uint_as_float(v[2 * j + 1]), p.scale_log2e, -mscaled));
+                        if (!full) {
+                            e0 = (c0 + 2 * j < nvis) ? e0 : 0.f;
+                            e1 = (c0 + 2 * j + 1 < nvis) ? e1 : 0.f;
+                        }
                         if (p.dtype == TVK_F16) {
                             const __half2 h = __floats2half2_rn(e0, e1);
                             packed[j] = *(const uint32_t*)&h;
-                            sum += __low2float(h) + __high2float(h);
+                            const float2 f = __half22float2(h);
+                            sum += f.x + f.y;
                         } else {
                             const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
                             packed[j] = *(const uint32_t*)&h;
-                            sum += __low2float(h) + __high2float(h);
+                            const float2 f = __bfloat1622float2(h);
+                            sum += f.x + f.y;
                         }
                     }
                 } else {
@@ -184,8 +210,11 @@ attn_fwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA
             tc_fence_before();
         }
+        xsum[half * 128 + r] = sum;
         __syncwarp();
         if (lane == 0 && ok) mbar_arrive(bar_p);
+        asm volatile("bar.sync 1, 256;" ::: "memory");                     // both halves of every row sum are written
+        sum = xsum[r] + xsum[128 + r];
         if (ok) {
             ok = mbar_wait(bar_o, 0, abort_flag, p.status, 55);
             ok = __all_sync(0xffffffffu, ok);
@@ -194,23 +223,21 @@ attn_fwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             tc_fence_after();
             const float inv = nvis > 0 ? 1.0f / sum : 0.f;
             uint16_t* orow = (uint16_t*)p.out + row * 64;
-#pragma unroll 1
-            for (int c0 = 0; c0 < 64; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld32(trow + (uint32_t)c0, v);
-                tmem_ld_wait();
-                uint32_t packed[16];
+            const int c0 = half * 32;                                      // each half stores 32 of the 64 output columns
+            uint32_t v[32];
+            tmem_ld32(trow + (uint32_t)c0, v);
+            tmem_ld_wait();
+            uint32_t packed[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float a = __uint_as_float(v[2 * j]) * inv, b = __uint_as_float(v[2 * j + 1]) * inv;
-                    if (p.dtype == TVK_F16) { const __half2 h = __floats2half2_rn(a, b); packed[j] = *(const uint32_t*)&h; }
-                    else { const __nv_bfloat162 h = __floats2bfloat162_rn(a, b); packed[j] = *(const uint32_t*)&h; }
-                }
-#pragma unroll
-                for (int j = 0; j < 16; j += 4) *(uint4*)(orow + c0 + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+            for (int j = 0; j < 16; ++j) {
+                const float a = __uint_as_float(v[2 * j]) * inv, b = __uint_as_float(v[2 * j + 1]) * inv;
+                if (p.dtype == TVK_F16) { const __half2 h = __floats2half2_rn(a, b); packed[j] = *(const uint32_t*)&h; }
+                else { const __nv_bfloat162 h = __floats2bfloat162_rn(a, b); packed[j] = *(const uint32_t*)&h; }
             }
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) *(uint4*)(orow + c0 + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
             // natural-log log-sum-exp of the scaled scores: m*scale + ln(sum)
-            p.lse[row] = nvis > 0 ? m * p.scale + logf(sum) : INFINITY;
+            if (half == 0) p.lse[row] = nvis > 0 ? m * p.scale + logf(sum) : INFINITY;
         }
     }
     __syncwarp();
