@@ -84,7 +84,14 @@ attn_fwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int group = blockIdx.x / p.tiles_per_group, tile = blockIdx.x - group * p.tiles_per_group;
+    // Under a causal mask the tiles low in a head see few keys and finish early: launch order runs from the last tile of
+    // every head to the first, so that the CTAs of the final, partial wave are the short ones.
+    int tile_id = (int)blockIdx.x;
+    if (p.causal && p.L % 128 == 0) {
+        const int tph = p.L / 128, heads = (int)gridDim.x / tph;          // tiles per head; the grid is a whole number of heads
+        tile_id = ((int)blockIdx.x % heads) * tph + (tph - 1 - (int)blockIdx.x / heads);
+    }
+    const int group = tile_id / p.tiles_per_group, tile = tile_id - group * p.tiles_per_group;
     const int64_t row0 = (int64_t)group * p.rows_per_group + (int64_t)tile * 128;     // first query row of the tile
     // keys some row of this tile can see, rounded up to whole 64-key blocks: the extent of both products
     int tile_keys = p.S;

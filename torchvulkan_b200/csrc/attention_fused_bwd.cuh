@@ -198,7 +198,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const bool vis = c0 + 2 * j + e < nvis && !dead;
-                        pr[e] = vis ? exp2f(__uint_as_float(sv[2 * j + e]) * p.scale_log2e - ls2) : 0.f;
+                        pr[e] = vis ? ex2_approx(fmaf(__uint_as_float(sv[2 * j + e]), p.scale_log2e, -ls2)) : 0.f;
                     }
                     // the forward pass multiplied V by the rounded probabilities: differentiate that function
                     if (p.dtype == TVK_F16) {
