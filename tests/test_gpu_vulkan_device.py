@@ -351,8 +351,6 @@ def test_conv2d_autograd(vk, dtype, stride, pad, k):
     yd.backward(gy.to(vk)); yc.backward(gy.double())
     for name, d, c in (("y", yd, yc), ("gx", xd.grad, xc.grad), ("gw", wd.grad, wc.grad), ("gb", bd.grad, bc.grad)):
         assert rel_fro(d.detach().cpu().double().numpy(), c.detach().numpy()) <= (1e-2 if dtype != torch.float32 else 1e-5), name
-    with pytest.raises(RuntimeError, match="NOT IMPLEMENTED"):
-        F.conv_transpose3d(xd.unsqueeze(2), wd.transpose(0, 1).unsqueeze(2))
 
 
 def _conv_family_check(fn, tensors, dtype, **kw):
@@ -396,6 +394,22 @@ def test_conv_transpose2d(vk, dtype):
     _conv_family_check(F.conv_transpose2d, (x, w, b), dtype, stride=2, padding=1, output_padding=1)
     w2 = (torch.randn(16, 6, 3, 3, generator=g) / 6.0).to(dtype)              # groups 2: 16 -> 12 channels
     _conv_family_check(F.conv_transpose2d, (x, w2), dtype, stride=2, padding=1, output_padding=1, groups=2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_conv_transpose3d(vk, dtype):
+    """Transposed 3-D convolution (slow_conv_transpose3d in the reference, src/api/ops/conv.cpp:1196-1220, 1307): one
+    transposed 2-D convolution per depth tap; gradients from the forward 3-D convolution with the roles swapped."""
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(2, 8, 4, 7, 5, generator=g).to(dtype)
+    w = (torch.randn(8, 12, 3, 3, 3, generator=g) / 14.0).to(dtype)           # [cin, cout / groups, kd, kh, kw]
+    b = torch.randn(12, generator=g).to(dtype)
+    _conv_family_check(F.conv_transpose3d, (x, w, b), dtype, stride=1, padding=1)
+    _conv_family_check(F.conv_transpose3d, (x, w, b), dtype, stride=2, padding=1, output_padding=1)
+    _conv_family_check(F.conv_transpose3d, (x, w, b), dtype, stride=(1, 2, 2), padding=(0, 1, 1), output_padding=(0, 1, 1))
+    _conv_family_check(F.conv_transpose3d, (x, w, b), dtype, stride=(2, 1, 1), padding=(1, 1, 1), output_padding=(1, 0, 0))
+    w2 = (torch.randn(8, 3, 2, 3, 3, generator=g) / 8.0).to(dtype)            # groups 2: 8 -> 6 channels
+    _conv_family_check(F.conv_transpose3d, (x, w2), dtype, stride=2, padding=(0, 1, 1), groups=2)
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
@@ -648,8 +662,6 @@ def test_hot_ops_raise_instead_of_falling_back(vk):
         a @ a
     with pytest.raises(RuntimeError, match="cannot be multiplied"):
         torch.ones(3, 4, device=vk) @ torch.ones(5, 6, device=vk)
-    with pytest.raises((RuntimeError, NotImplementedError), match="NOT IMPLEMENTED"):
-        F.conv_transpose3d(torch.ones(1, 4, 3, 5, 5, device=vk), torch.ones(4, 2, 3, 3, 3, device=vk))
 
 
 def test_environment_switches_of_the_reference(vk):

@@ -279,6 +279,35 @@ std::tuple<at::Tensor, at::Tensor> conv3d_by_taps_backward(const at::Tensor& gy,
     return {gx, gw};
 }
 
+// Transposed 3-D convolution: the input gradient of the forward 3-D convolution that maps y's shape to x's shape. For one
+// depth tap kd, input depth i of x adds conv_transpose2d(x[:, :, i], w[:, :, kd]) into output depth i * sd - pd + kd * dd:
+// the same ranges as the forward convolution's taps with the roles of the two tensors exchanged, one transposed 2-D
+// convolution over the batch n * depths per tap.
+at::Tensor conv_transpose3d_by_taps(const at::Tensor& input, const at::Tensor& weight, at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation,
+                                    at::IntArrayRef output_padding, int64_t groups) {
+    auto three = [](at::IntArrayRef v, int64_t dflt) {
+        if (v.empty()) return std::array<int64_t, 3>{dflt, dflt, dflt};
+        return v.size() == 1 ? std::array<int64_t, 3>{v[0], v[0], v[0]} : std::array<int64_t, 3>{v[0], v[1], v[2]};
+    };
+    const auto st = three(stride, 1), pd = three(padding, 0), dl = three(dilation, 1), op = three(output_padding, 0);
+    TORCH_CHECK(input.size(1) == weight.size(0), "torchvulkan [ERROR]: transposed convolution: input has ", input.size(1), " channels, weight expects ", weight.size(0));
+    const int64_t n = input.size(0), D = input.size(2);
+    const int64_t Dy = (D - 1) * st[0] - 2 * pd[0] + dl[0] * (weight.size(2) - 1) + op[0] + 1;
+    TORCH_CHECK(Dy > 0, "torchvulkan [ERROR]: transposed convolution: empty output");
+    at::Tensor y;
+    for (int64_t kd = 0; kd < weight.size(2); ++kd) {
+        // the forward convolution reads y's depths d0 + i * sd for x's depths do0 + i
+        const DepthTap t = depth_tap(Dy, D, kd, st[0], pd[0], dl[0]);
+        if (t.count == 0) continue;
+        at::Tensor x4 = fold_depth(input.slice(2, t.do0, t.do0 + t.count));
+        at::Tensor y4 = conv_transpose2d_any(x4, contiguous_vulkan(weight.select(2, kd)), {st[1], st[2]}, {pd[1], pd[2]}, {dl[1], dl[2]}, {op[1], op[2]}, groups);
+        if (!y.defined()) y = at::zeros({n, weight.size(1) * groups, Dy, y4.size(2), y4.size(3)}, input.options());
+        y.slice(2, t.d0, t.d0 + (t.count - 1) * st[0] + 1, st[0]).add_(unfold_depth(y4, n));
+    }
+    TORCH_CHECK(y.defined(), "torchvulkan [ERROR]: transposed convolution: no filter tap reaches the output");
+    return y;
+}
+
 at::Tensor squeeze_h(const at::Tensor& t) { return t.defined() ? t.squeeze(2) : t; }
 
 at::Tensor convolution_entry(const at::Tensor& input, const at::Tensor& weight, const c10::optional<at::Tensor>& bias, at::IntArrayRef stride,
@@ -291,8 +320,8 @@ at::Tensor convolution_entry(const at::Tensor& input, const at::Tensor& weight, 
             .squeeze(2);
     }
     if (input.dim() == 5 && weight.dim() == 5) {
-        TORCH_CHECK(!transposed, "torchvulkan [NOT IMPLEMENTED]: transposed 3-D convolution");
-        at::Tensor y3 = conv3d_by_taps(input, weight, stride, padding, dilation, groups);
+        at::Tensor y3 = transposed ? conv_transpose3d_by_taps(input, weight, stride, padding, dilation, output_padding, groups)
+                                   : conv3d_by_taps(input, weight, stride, padding, dilation, groups);
         if (bias.has_value() && bias->defined()) y3.add_(bias->view({1, -1, 1, 1, 1}));
         return y3;
     }
@@ -318,9 +347,14 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> convolution_backward_entry(const 
         return std::make_tuple(squeeze_h(std::get<0>(r)), squeeze_h(std::get<1>(r)), std::get<2>(r));
     }
     if (input.dim() == 5 && weight.dim() == 5) {
-        TORCH_CHECK(!transposed, "torchvulkan [NOT IMPLEMENTED]: transposed 3-D convolution");
         at::Tensor gx3, gw3, gb3;
-        std::tie(gx3, gw3) = conv3d_by_taps_backward(grad_output, input, weight, stride, padding, dilation, groups, output_mask[0], output_mask[1]);
+        if (!transposed) {
+            std::tie(gx3, gw3) = conv3d_by_taps_backward(grad_output, input, weight, stride, padding, dilation, groups, output_mask[0], output_mask[1]);
+        } else {
+            // the forward 3-D convolution behind the transposed one maps grad_output's shape to input's shape
+            if (output_mask[0]) gx3 = conv3d_by_taps(grad_output, weight, stride, padding, dilation, groups);
+            if (output_mask[1]) gw3 = std::get<1>(conv3d_by_taps_backward(input, grad_output, weight, stride, padding, dilation, groups, false, true));
+        }
         if (output_mask[2]) gb3 = grad_output.sum(at::IntArrayRef({0, 2, 3, 4}));
         return std::make_tuple(gx3, gw3, gb3);
     }
