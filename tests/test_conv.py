@@ -31,19 +31,28 @@ def test_descriptor_validation():
     assert lib.tvk_conv2d_workspace_size(C.byref(ok), 0, C.byref(n)) == 0 and n.value > 0
     assert lib.tvk_conv2d_workspace_size(C.byref(ok), 3, C.byref(n)) == 0 and n.value > 0      # both gradients in one call
     assert lib.tvk_conv2d_workspace_size(C.byref(ok), 4, C.byref(n)) == 1
-    for field, value in (("groups", 2), ("dilation_h", 2), ("stride_h", 3), ("dtype", capi.I64), ("kh", 9)):
+    for field, value in (("groups", 2), ("dtype", capi.I64)):
+        d = capi.Conv2dDesc(capi.F16, 2, 3, 8, 8, 4, 3, 3, 1, 1, 1, 1, 1, 1, 1)
+        setattr(d, field, value)
+        assert lib.tvk_conv2d_workspace_size(C.byref(d), 0, C.byref(n)) == 2, field
+        assert b"NOT IMPLEMENTED" in lib.tvk_last_error()
+    # what the implicit-GEMM kernels do not take (dilation, strides above 2 or unequal, filters of many taps) goes through
+    # unfold + GEMM like fp32
+    for field, value in (("dilation_h", 2), ("stride_h", 3), ("kh", 9)):
         d = capi.Conv2dDesc(capi.F16, 2, 3, 8, 8, 4, 3, 3, 1, 1, 1, 1, 1, 1, 1)
         setattr(d, field, value)
         if field == "kh":
             d.kw, d.h, d.w = 9, 16, 16
-        assert lib.tvk_conv2d_workspace_size(C.byref(d), 0, C.byref(n)) == 2, field
-        assert b"NOT IMPLEMENTED" in lib.tvk_last_error()
+        for mode in (0, 1, 2, 3):
+            assert lib.tvk_conv2d_workspace_size(C.byref(d), mode, C.byref(n)) == 0 and n.value > 0, (field, mode)
     d = capi.Conv2dDesc(capi.F16, 2, 3, 2, 2, 4, 3, 3, 1, 1, 0, 0, 1, 1, 1)
     assert lib.tvk_conv2d_workspace_size(C.byref(d), 0, C.byref(n)) == 1  # filter larger than the input
-    # fp32 goes through unfold + GEMM: any stride, still no groups or dilation
+    # fp32 goes through unfold + GEMM: any stride and dilation, no groups
     f = capi.Conv2dDesc(capi.F32, 2, 3, 9, 9, 4, 3, 3, 3, 3, 1, 1, 1, 1, 1)
     for mode in (0, 1, 2):
         assert lib.tvk_conv2d_workspace_size(C.byref(f), mode, C.byref(n)) == 0 and n.value > 0
+    f.dilation_w = 2
+    assert lib.tvk_conv2d_workspace_size(C.byref(f), 0, C.byref(n)) == 0 and n.value > 0
     f.groups = 3
     assert lib.tvk_conv2d_workspace_size(C.byref(f), 0, C.byref(n)) == 2 and b"NOT IMPLEMENTED" in lib.tvk_last_error()
 

@@ -396,6 +396,28 @@ def test_conv_transpose2d(vk, dtype):
     _conv_family_check(F.conv_transpose2d, (x, w2), dtype, stride=2, padding=1, output_padding=1, groups=2)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_conv2d_dilation_and_other_strides(vk, dtype):
+    """Dilation, strides above 2, unequal strides and filters of many taps (the reference's one convolution entry takes any
+    geometry, src/api/ops/conv.cpp:1088-1117): unfold + tensor-core GEMM + fold in the tensors' dtype."""
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(3, 16, 19, 17, generator=g).to(dtype)
+    w = (torch.randn(24, 16, 3, 3, generator=g) / 12.0).to(dtype)
+    b = torch.randn(24, generator=g).to(dtype)
+    _conv_family_check(F.conv2d, (x, w, b), dtype, stride=1, padding=2, dilation=2)
+    _conv_family_check(F.conv2d, (x, w, b), dtype, stride=3, padding=1)
+    _conv_family_check(F.conv2d, (x, w, b), dtype, stride=(1, 2), padding=(0, 1))
+    _conv_family_check(F.conv2d, (x, w, b), dtype, stride=(2, 1), padding=(3, 1), dilation=(3, 1))
+    _conv_family_check(F.conv2d, (x.contiguous(memory_format=torch.channels_last), w, b), dtype, stride=2, padding=2, dilation=2)
+    w9 = (torch.randn(8, 16, 9, 9, generator=g) / 36.0).to(dtype)             # 81 taps
+    _conv_family_check(F.conv2d, (x, w9), dtype, stride=1, padding=4)
+    # transposed and grouped convolutions reach the same route through the dense entry
+    wt = (torch.randn(16, 6, 3, 3, generator=g) / 12.0).to(dtype)
+    _conv_family_check(F.conv_transpose2d, (x, wt), dtype, stride=3, padding=1, output_padding=2)
+    wg = (torch.randn(24, 8, 3, 3, generator=g) / 8.0).to(dtype)
+    _conv_family_check(F.conv2d, (x, wg), dtype, stride=1, padding=2, dilation=2, groups=2)
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
 def test_conv_transpose3d(vk, dtype):
     """Transposed 3-D convolution (slow_conv_transpose3d in the reference, src/api/ops/conv.cpp:1196-1220, 1307): one

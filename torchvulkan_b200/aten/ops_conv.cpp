@@ -3,16 +3,16 @@
 // Counterparts in the reference: convolution_vulkan / convolution_backward_vulkan
 // (src/api/ops/conv.cpp:1088-1172, registered at conv.cpp:1303-1304). at::convolution routes every
 // PrivateUse1 convolution to these two ops. As there, the bias is a broadcast add after the kernel and
-// its gradient a sum over (n, h, w) (conv.cpp:1159-1170). The tensor-core kernels cover 2-D, groups 1, dilation 1,
-// stride 1 or 2 in fp16 / bf16 (any stride in fp32). Around them, as in the reference's one entry for every flavour
-// (conv.cpp:1088-1172, 1196-1294):
+// its gradient a sum over (n, h, w) (conv.cpp:1159-1170). The implicit-GEMM kernels cover 2-D, groups 1, dilation 1,
+// stride 1 or 2 in fp16 / bf16; fp32 and every other 2-D geometry go through unfold + GEMM inside the same C entry
+// points. Around them, as in the reference's one entry for every flavour (conv.cpp:1088-1172, 1196-1294):
 //   * 1-D convolutions run as 2-D ones of height 1;
 //   * a transposed convolution is the input-gradient product of the forward one (its gradients are the forward
 //     product and the weight-gradient product with the roles of input and output swapped);
 //   * depthwise convolutions (one input channel per group) take the direct kernels of depthwise.cu;
 //   * other grouped convolutions run group by group on channel slices.
-//   * a 3-D convolution is one 2-D convolution per depth tap over the batch n * depths, accumulated.
-// Transposed 3-D convolutions and what the kernels refuse raise "[NOT IMPLEMENTED]" (the hot path never falls back to the CPU).
+//   * a 3-D convolution (transposed or not) is one 2-D convolution per depth tap over the batch n * depths, accumulated.
+// What the kernels refuse raises "[NOT IMPLEMENTED]" (the hot path never falls back to the CPU).
 #include "common.h"
 
 namespace tvk_aten {
@@ -58,7 +58,8 @@ at::Tensor conv2d_dense(const at::Tensor& input, const at::Tensor& weight, const
     DeviceScope scope(x);
     uint64_t ws_bytes = 0;
     TVK_CALL(tvk_conv2d_workspace_size(&d, 0, &ws_bytes));
-    const int64_t ho = (d.h + 2 * d.pad_h - d.kh) / d.stride_h + 1, wo = (d.w + 2 * d.pad_w - d.kw) / d.stride_w + 1;
+    const int64_t ho = (d.h + 2 * d.pad_h - d.dilation_h * (d.kh - 1) - 1) / d.stride_h + 1, wo = (d.w + 2 * d.pad_w - d.dilation_w * (d.kw - 1) - 1) / d.stride_w + 1;
+    TORCH_CHECK(ho > 0 && wo > 0, "torchvulkan [ERROR]: convolution: the filter does not fit the padded input");
     at::Tensor y = empty4({d.n, d.cout, ho, wo}, x, cl);
     if (y.numel()) {
         Workspace ws(scope.device, ws_bytes);

@@ -317,26 +317,37 @@ static WgradPlan plan_wgrad(const Geo& g) {
 }  // namespace tvk
 
 namespace tvk {
-// fp32: unfold + 3xTF32 GEMM (conv_f32.cu)
-int conv2d_f32_workspace_size(const tvk_conv2d_desc* d, int mode, uint64_t* bytes);
-int conv2d_f32_forward(const tvk_conv2d_desc* d, void* y, const void* x, const void* w, void* workspace, uint64_t workspace_bytes, void* stream);
-int conv2d_f32_backward_input(const tvk_conv2d_desc* d, void* dx, const void* dy, const void* w, void* workspace, uint64_t workspace_bytes, void* stream);
-int conv2d_f32_backward_weight(const tvk_conv2d_desc* d, void* dw, const void* dy, const void* x, void* workspace, uint64_t workspace_bytes, void* stream);
+// fp32 tensors and the geometries the kernels of this file do not take: unfold + GEMM (conv_unfold.cu)
+int conv2d_unfold_workspace_size(const tvk_conv2d_desc* d, int mode, uint64_t* bytes);
+int conv2d_unfold_forward(const tvk_conv2d_desc* d, void* y, const void* x, const void* w, void* workspace, uint64_t workspace_bytes, void* stream);
+int conv2d_unfold_backward_input(const tvk_conv2d_desc* d, void* dx, const void* dy, const void* w, void* workspace, uint64_t workspace_bytes, void* stream);
+int conv2d_unfold_backward_weight(const tvk_conv2d_desc* d, void* dw, const void* dy, const void* x, void* workspace, uint64_t workspace_bytes, void* stream);
 }  // namespace tvk
 
 using namespace tvk;
 using namespace tvk::conv;
 
+// fp32 tensors, and half tensors with dilation, a stride above 2, unequal strides or a filter of more taps than the
+// implicit-GEMM kernels walk, take the unfold route
+static bool unfold_route(const tvk_conv2d_desc* d) {
+    if (!d) return false;
+    if (d->dtype == TVK_F32) return true;
+    if (d->dtype != TVK_F16 && d->dtype != TVK_BF16) return false;
+    if (d->groups != 1 || d->stride_h < 1 || d->stride_w < 1 || d->dilation_h < 1 || d->dilation_w < 1 || d->kh < 1 || d->kw < 1) return false;
+    return d->stride_h != d->stride_w || d->stride_h > 2 || d->dilation_h != 1 || d->dilation_w != 1 || d->kh * d->kw > kMaxTaps || d->kh > 64 || d->kw > 64 ||
+           d->pad_h >= 64 || d->pad_w >= 64;
+}
+
 extern "C" {
 
 int tvk_conv2d_workspace_size(const tvk_conv2d_desc* d, int mode, uint64_t* bytes) {
     if (!bytes) return set_error(TVK_ERR_INVALID, "tvk_conv2d_workspace_size: null output");
-    if (d && d->dtype == TVK_F32) {
-        if (mode != 3) return conv2d_f32_workspace_size(d, mode, bytes);
+    if (unfold_route(d)) {
+        if (mode != 3) return conv2d_unfold_workspace_size(d, mode, bytes);
         uint64_t b1 = 0, b2 = 0;      // both gradients: the two products run one after the other in the same workspace
-        int rc1 = conv2d_f32_workspace_size(d, 1, &b1);
+        int rc1 = conv2d_unfold_workspace_size(d, 1, &b1);
         if (rc1) return rc1;
-        rc1 = conv2d_f32_workspace_size(d, 2, &b2);
+        rc1 = conv2d_unfold_workspace_size(d, 2, &b2);
         if (rc1) return rc1;
         *bytes = b1 > b2 ? b1 : b2;
         return TVK_OK;
@@ -375,9 +386,9 @@ int tvk_conv2d_workspace_size(const tvk_conv2d_desc* d, int mode, uint64_t* byte
                 (unsigned long long)workspace_bytes)
 
 int tvk_conv2d_forward(const tvk_conv2d_desc* d, void* y, const void* x, const void* w, void* workspace, uint64_t workspace_bytes, void* stream) {
-    if (d && d->dtype == TVK_F32) {
+    if (unfold_route(d)) {
         TVK_REQUIRE(d->n == 0 || (y && x && w), "tvk_conv2d_forward: null pointer");
-        return conv2d_f32_forward(d, y, x, w, workspace, workspace_bytes, stream);
+        return conv2d_unfold_forward(d, y, x, w, workspace, workspace_bytes, stream);
     }
     Geo g;
     int rc = make_geo(d, &g);
@@ -428,9 +439,9 @@ int tvk_conv2d_forward(const tvk_conv2d_desc* d, void* y, const void* x, const v
 
 int tvk_conv2d_backward_input(const tvk_conv2d_desc* d, void* dx, const void* dy, const void* w, void* workspace, uint64_t workspace_bytes,
                               void* stream) {
-    if (d && d->dtype == TVK_F32) {
+    if (unfold_route(d)) {
         TVK_REQUIRE(d->n == 0 || (dx && dy && w), "tvk_conv2d_backward_input: null pointer");
-        return conv2d_f32_backward_input(d, dx, dy, w, workspace, workspace_bytes, stream);
+        return conv2d_unfold_backward_input(d, dx, dy, w, workspace, workspace_bytes, stream);
     }
     Geo g;
     int rc = make_geo(d, &g);
@@ -502,9 +513,9 @@ int tvk_conv2d_backward_input(const tvk_conv2d_desc* d, void* dx, const void* dy
 
 int tvk_conv2d_backward_weight(const tvk_conv2d_desc* d, void* dw, const void* dy, const void* x, void* workspace, uint64_t workspace_bytes,
                                void* stream) {
-    if (d && d->dtype == TVK_F32) {
+    if (unfold_route(d)) {
         TVK_REQUIRE(dw && (d->n == 0 || (dy && x)), "tvk_conv2d_backward_weight: null pointer");
-        return conv2d_f32_backward_weight(d, dw, dy, x, workspace, workspace_bytes, stream);
+        return conv2d_unfold_backward_weight(d, dw, dy, x, workspace, workspace_bytes, stream);
     }
     Geo g;
     int rc = make_geo(d, &g);
@@ -577,7 +588,7 @@ int tvk_conv2d_backward(const tvk_conv2d_desc* d, void* dx, void* dw, const void
     const void* dy_used = dy;
     uint8_t* ws = (uint8_t*)workspace;
     uint64_t left = workspace_bytes;
-    if (d->dtype != TVK_F32) {
+    if (!unfold_route(d)) {
         Geo g;
         int rc = make_geo(d, &g);
         if (rc) return rc;
