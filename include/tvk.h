@@ -562,12 +562,15 @@ TVK_API int tvk_attention_backward(int dtype, void* dq, void* dk, void* dv, cons
 /* 2-D convolution, its input gradient and its weight gradient (convolution_vulkan and
  * convolution_backward_vulkan, src/api/ops/conv.cpp:1088-1172; dispatch_conv_shader conv.cpp:661-685;
  * the three modes FORWARD / GRAD_INPUT / GRAD_WEIGHT of conv.cpp:241-245). fp16 / bf16 with fp32
- * accumulation. x, dx: contiguous NCHW [n, cin, h, w]; w, dw: contiguous OIHW [cout, cin, kh, kw];
- * y, dy: contiguous [n, cout, ho, wo] with ho = (h + 2*pad_h - kh) / stride + 1 (likewise wo).
- * Supported: stride_h == stride_w in {1, 2}, dilation 1, groups 1, kh*kw <= 64; anything else
- * returns TVK_ERR_UNSUPPORTED with a "[NOT IMPLEMENTED]" message. The bias and its gradient are
+ * accumulation, and fp32. x, dx: contiguous NCHW [n, cin, h, w]; w, dw: contiguous OIHW [cout, cin, kh, kw];
+ * y, dy: contiguous [n, cout, ho, wo] with ho = (h + 2*pad_h - dilation_h*(kh - 1) - 1) / stride_h + 1 (likewise wo).
+ * fp16 / bf16 with stride_h == stride_w in {1, 2}, dilation 1 and kh*kw <= 64 run on the implicit-GEMM tensor-core
+ * kernels; fp32 and every other stride, dilation and filter size run as unfold + GEMM + fold (the reference's own
+ * im2col route, conv.cpp:200-216). groups must be 1 (see the depthwise entry points below); other dtypes
+ * return TVK_ERR_UNSUPPORTED with a "[NOT IMPLEMENTED]" message. The bias and its gradient are
  * a broadcast add and a reduction (tvk_binary_strided, tvk_reduce) as in conv.cpp:1159-1170.
- * mode: 0 forward, 1 input gradient, 2 weight gradient; the workspace must be 256-byte aligned. */
+ * mode: 0 forward, 1 input gradient, 2 weight gradient, 3 both gradients (tvk_conv2d_backward); the workspace must
+ * be 256-byte aligned. */
 typedef struct tvk_conv2d_desc {
     int dtype;
     int64_t n, cin, h, w;
