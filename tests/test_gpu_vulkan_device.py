@@ -602,6 +602,13 @@ def test_batch_norm_evaluation_mode(vk, dtype, tol, channels_last):
     assert yd.is_contiguous(memory_format=torch.channels_last if channels_last else torch.contiguous_format)
     ref = bn.double()(x.to(dtype).double())
     assert rel_fro(yd.detach().cpu().double().numpy(), ref.detach().numpy()) <= tol
+    # gradients through a frozen layer (the statistics are constants): input, weight and bias
+    xg, xc = xd.detach().clone().requires_grad_(), x.to(dtype).double().requires_grad_()
+    gy = torch.randn(3, 24, 7, 5).to(dtype)
+    dev(xg).backward(gy.to(vk)); bn(xc).backward(gy.double())
+    btol = max(tol, 5e-3 if dtype == torch.float16 else tol)
+    for got, want in ((xg.grad, xc.grad), (dev.weight.grad, bn.weight.grad), (dev.bias.grad, bn.bias.grad)):
+        assert rel_fro(got.cpu().double().numpy(), want.numpy()) <= btol
     bn1 = torch.nn.BatchNorm1d(24).eval()
     d1 = torch.nn.BatchNorm1d(24).to(dtype).to(vk).eval()
     x1 = torch.randn(9, 24)

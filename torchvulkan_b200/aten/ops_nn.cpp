@@ -265,12 +265,33 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> native_batch_norm_legit_no_stats(
 }
 
 std::tuple<at::Tensor, at::Tensor, at::Tensor> native_batch_norm_backward(const at::Tensor& grad_out, const at::Tensor& input,
-                                                                          const c10::optional<at::Tensor>& weight, const c10::optional<at::Tensor>&,
-                                                                          const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>& save_mean,
-                                                                          const c10::optional<at::Tensor>& save_invstd, bool train, double,
+                                                                          const c10::optional<at::Tensor>& weight, const c10::optional<at::Tensor>& running_mean,
+                                                                          const c10::optional<at::Tensor>& running_var, const c10::optional<at::Tensor>& save_mean,
+                                                                          const c10::optional<at::Tensor>& save_invstd, bool train, double eps,
                                                                           std::array<bool, 3> output_mask) {
     require_float(input, "native_batch_norm_backward");
-    if (!train) TVK_NOT_IMPLEMENTED("batch_norm backward in evaluation mode");
+    if (!train) {
+        // Evaluation mode (a frozen layer inside a model that is being trained): the statistics are constants, so
+        // gx = g * w * invstd, gw = sum g * (x - mean) * invstd, gb = sum g, with invstd = rsqrt(running_var + eps).
+        // A few elementwise and reduction launches on the device; not a hot path.
+        TORCH_CHECK(running_mean.has_value() && running_mean->defined() && running_var.has_value() && running_var->defined(),
+                    "torchvulkan [ERROR]: batch_norm backward in evaluation mode needs running_mean and running_var");
+        const at::ScalarType st = input.scalar_type();
+        std::vector<int64_t> bshape(input.dim(), 1), dims;
+        bshape[1] = input.size(1);
+        for (int64_t d = 0; d < input.dim(); ++d)
+            if (d != 1) dims.push_back(d);
+        at::Tensor invstd = at::rsqrt(running_var->to(at::kFloat) + eps), mean = running_mean->to(at::kFloat);
+        at::Tensor g = grad_out.to(st);
+        at::Tensor gx, gw, gb;
+        if (output_mask[0]) {
+            at::Tensor scale = (weight.has_value() && weight->defined()) ? weight->to(at::kFloat) * invstd : invstd;
+            gx = g * scale.to(st).view(bshape);
+        }
+        if (output_mask[1]) gw = (g * ((input - mean.to(st).view(bshape)) * invstd.to(st).view(bshape))).sum(dims);
+        if (output_mask[2]) gb = g.sum(dims);
+        return {gx, gw, gb};
+    }
     TORCH_CHECK(save_mean.has_value() && save_mean->defined() && save_invstd.has_value() && save_invstd->defined(),
                 "torchvulkan [ERROR]: batch_norm backward needs the saved statistics");
     const at::ScalarType st = input.scalar_type();
