@@ -319,6 +319,11 @@ typedef enum tvk_unary_op {
     TVK_U_GELU, TVK_U_TANH, TVK_U_ABS, TVK_U_SILU, TVK_U_RECIPROCAL, TVK_U_SQUARE,
     TVK_U_SIN, TVK_U_COS,
     TVK_U_GELU_TANH,          /* gelu(approximate='tanh'), src/shaders/core/dtype.slang:738 */
+    /* the rest of the reference's unary family (src/api/ops/unary.cpp:137-260, one shader entry each) */
+    TVK_U_FLOOR, TVK_U_CEIL, TVK_U_ROUND /* half to even */, TVK_U_TRUNC, TVK_U_SIGN,
+    TVK_U_LOG2, TVK_U_LOG10, TVK_U_LOG1P, TVK_U_EXPM1, TVK_U_EXP2,
+    TVK_U_TAN, TVK_U_SINH, TVK_U_COSH, TVK_U_ASIN, TVK_U_ACOS, TVK_U_ATAN, TVK_U_ERF, TVK_U_ERFC,
+    TVK_U_HARDSIGMOID, TVK_U_HARDSWISH, TVK_U_MISH, TVK_U_LOGSIGMOID,
     TVK_U_COUNT_
 } tvk_unary_op;
 
@@ -334,6 +339,20 @@ typedef enum tvk_binary_op {
     TVK_B_GELU_TANH_BACKWARD, /* a = grad, b = x (src/shaders/core/dtype.slang:745-751)     */
     TVK_B_ADD_RELU,           /* out = relu(a + alpha*b): _add_relu, which the reference runs as add then relu
                                  (src/api/ops/binary.cpp:655-673), in one pass; NaN propagates as in relu */
+    TVK_B_FMOD,               /* C fmod: the result has the sign of a                        */
+    TVK_B_REMAINDER,          /* Python %: the result has the sign of b                      */
+    TVK_B_ATAN2,
+    TVK_B_FLOOR_DIVIDE,       /* floor(a / b) with ATen's correction for the rounding of a / b */
+    /* one tensor and two scalars (b == NULL: b_scalar and alpha are the parameters) */
+    TVK_B_CLAMP,              /* min(max(a, alpha), b_scalar), NaN stays NaN (also hardtanh) */
+    TVK_B_LEAKY_RELU,         /* a > 0 ? a : a * b_scalar                                    */
+    TVK_B_ELU,                /* a > 0 ? a : alpha * (exp(a) - 1)                            */
+    TVK_B_SOFTPLUS,           /* beta = alpha, threshold = b_scalar                          */
+    /* gradients: a = grad, b = x */
+    TVK_B_LEAKY_RELU_BACKWARD,   /* alpha = negative slope                                   */
+    TVK_B_ELU_BACKWARD,          /* alpha as in the forward, b = the input                   */
+    TVK_B_HARDSWISH_BACKWARD, TVK_B_HARDSIGMOID_BACKWARD, TVK_B_MISH_BACKWARD, TVK_B_LOGSIGMOID_BACKWARD,
+    TVK_B_SOFTPLUS_BACKWARD,     /* beta = alpha, threshold 20                               */
     TVK_B_COUNT_
 } tvk_binary_op;
 
@@ -366,6 +385,10 @@ TVK_API int tvk_binary(int op, int dtype, void* out, const void* a, const void* 
                        double alpha, int64_t n, void* stream);
 TVK_API int tvk_compare(int op, int dtype, uint8_t* out, const void* a, const void* b, double b_scalar,
                         int64_t n, void* stream);
+/* Logical and / or / xor / not on boolean tensors (one byte per element, any non-zero byte is true, results are 0 or 1):
+ * logical_and/or/xor/not of src/api/ops/compare.cpp (dispatch_compare_shader), contiguous operands. b is ignored for NOT. */
+typedef enum tvk_logical_op { TVK_L_AND = 0, TVK_L_OR, TVK_L_XOR, TVK_L_NOT, TVK_L_COUNT_ } tvk_logical_op;
+TVK_API int tvk_logical(int op, uint8_t* out, const uint8_t* a, const uint8_t* b, int64_t n, void* stream);
 TVK_API int tvk_ternary(int op, int dtype, void* out, const void* a, const void* b, const void* c,
                         double value, int64_t n, void* stream);
 /* Strided/broadcast variants over a tvk_iter. */

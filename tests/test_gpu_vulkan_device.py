@@ -728,6 +728,59 @@ def test_environment_switches_of_the_reference(vk):
     assert p.returncode == 0 and "ENV-OK" in p.stdout, p.stdout[-2000:] + p.stderr[-3000:]
 
 
+@pytest.mark.parametrize("dtype,mask_kind,causal,gqa,L,S", [
+    (torch.float32, None, True, False, 48, 48),
+    (torch.float32, None, False, False, 40, 56),
+    (torch.float16, "bool", False, False, 40, 56),
+    (torch.float16, "float", False, False, 40, 56),
+    (torch.float32, "bool", False, True, 40, 56),
+    (torch.bfloat16, "float", False, True, 24, 40),
+    (torch.float16, None, False, False, 37, 53),
+    (torch.float16, None, True, True, 37, 53),
+])
+def test_attention_with_masks_fp32_and_odd_lengths(vk, dtype, mask_kind, causal, gqa, L, S):
+    """F.scaled_dot_product_attention for the cases outside the attention kernels (an additive or boolean mask, fp32, key
+    counts that are not multiples of 8): the same overrideable operator composes them from this backend's launches
+    (the reference's fused path takes the mask as an additive bias, src/api/ops/attention.cpp:698-722). Output, the
+    gradients of q, k, v and of a floating mask against ATen CPU in float64; a query row whose mask hides every key
+    gives 0 (attention_coop.slang:164-222)."""
+    g = torch.Generator().manual_seed(17)
+    B, H, D = 2, 4, 32
+    Hk = 2 if gqa else H
+    q, k, v = (torch.randn(B, h, n, D, generator=g).to(dtype) for h, n in ((H, L), (Hk, S), (Hk, S)))
+    mask = None
+    if mask_kind == "bool":
+        mask = torch.rand(B, 1, L, S, generator=g) > 0.3
+        mask[..., 0] = True
+        mask[0, 0, 3, :] = False                                         # one row sees nothing
+    elif mask_kind == "float":
+        mask = (torch.randn(1, H, L, S, generator=g) * 0.5).to(dtype)
+    qd, kd, vd = (t.to(vk).requires_grad_() for t in (q, k, v))
+    qc, kc, vc = (t.double().requires_grad_() for t in (q, k, v))
+    md = mc = None
+    if mask is not None:
+        md = mask.to(vk)
+        mc = mask if mask.dtype == torch.bool else mask.double()
+        if mask_kind == "float":
+            md.requires_grad_(); mc.requires_grad_()
+    od = F.scaled_dot_product_attention(qd, kd, vd, attn_mask=md, is_causal=causal, enable_gqa=gqa)
+    oc = F.scaled_dot_product_attention(qc, kc, vc, attn_mask=mc, is_causal=causal, enable_gqa=gqa)
+    assert od.dtype == dtype and od.shape == oc.shape
+    gy = torch.randn(oc.shape, generator=g).to(dtype)
+    od.backward(gy.to(vk)); oc.backward(gy.double())
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    if mask_kind == "bool":
+        assert float(od[0, :, 3].detach().abs().max().cpu()) == 0.0
+        oc = oc.detach().clone(); oc[0, :, 3] = 0                        # (ATen's CPU kernel leaves NaN or 0 there, by version)
+        for t in (qc.grad, kc.grad, vc.grad):
+            t.nan_to_num_(0.0)
+    assert rel_fro(od.detach().cpu().double().numpy(), oc.detach().numpy()) <= tol
+    pairs = [(qd.grad, qc.grad), (kd.grad, kc.grad), (vd.grad, vc.grad)] + ([(md.grad, mc.grad)] if mask_kind == "float" else [])
+    for got, want in pairs:
+        assert got.shape == want.shape
+        assert rel_fro(got.cpu().double().numpy(), want.numpy()) <= tol
+
+
 @pytest.mark.parametrize("rowwise", [False, True])
 @pytest.mark.parametrize("kinds", [("e4m3", "e4m3"), ("e4m3", "e5m2")])
 def test_scaled_mm(vk, rowwise, kinds):

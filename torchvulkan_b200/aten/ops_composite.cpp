@@ -1,0 +1,257 @@
+// Operators that are a few launches of this backend's own kernels: full and per-dimension max / min, all / any, variance
+// and standard deviation, vector norms, masked_fill, tril / triu, the factory ranges, mse_loss.
+//
+// Counterparts in the reference: src/api/ops/reduce.cpp (max, min, all, any, prod ... registered at reduce.cpp:740-800),
+// src/api/ops/indexing.cpp:423 (max.dim_max), src/api/ops/shape.cpp:269 (tril.out), src/api/ops/binary.cpp (masked ops).
+// None of these is a hot path of the five benchmark configurations; they are here so that a training script's bookkeeping
+// (gradient clipping, metrics, masks, position ids) runs on the device without a host round trip. Each is written over
+// ATen calls that dispatch to the kernels of ops_eltwise.cpp / ops_reduce.cpp; reductions of 16-bit tensors accumulate in
+// fp32 inside those kernels.
+#include "common.h"
+
+#include <cmath>
+#include <limits>
+
+namespace tvk_aten {
+namespace {
+
+std::vector<int64_t> all_dims(const at::Tensor& t) {
+    std::vector<int64_t> d(t.dim());
+    for (int64_t i = 0; i < t.dim(); ++i) d[i] = i;
+    return d;
+}
+std::vector<int64_t> dims_or_all(const at::Tensor& t, at::OptionalIntArrayRef dim) {
+    if (!dim.has_value() || dim->empty()) return all_dims(t);
+    return std::vector<int64_t>(dim->begin(), dim->end());
+}
+at::Tensor& into(at::Tensor& out, const at::Tensor& value) {
+    if (out.sizes() != value.sizes()) out.resize_(value.sizes());
+    out.copy_(value);
+    return out;
+}
+
+// ---- max / min ----------------------------------------------------------------------------
+at::Tensor max_all(const at::Tensor& self) {
+    TORCH_CHECK(self.numel() > 0, "max(): Expected reduction dim to be specified for input.numel() == 0. Specify the reduction dim with the 'dim' argument.");
+    return self.dim() == 0 ? self.clone() : at::amax(self, all_dims(self), false);
+}
+at::Tensor min_all(const at::Tensor& self) {
+    TORCH_CHECK(self.numel() > 0, "min(): Expected reduction dim to be specified for input.numel() == 0. Specify the reduction dim with the 'dim' argument.");
+    return self.dim() == 0 ? self.clone() : at::amin(self, all_dims(self), false);
+}
+at::Tensor& max_unary_out(const at::Tensor& self, at::Tensor& out) { return into(out, max_all(self)); }
+at::Tensor& min_unary_out(const at::Tensor& self, at::Tensor& out) { return into(out, min_all(self)); }
+// values by amax / amin, indices by argmax / argmin (the first extremum, NaN first: the rule of arg_reduce.slang:49-65)
+std::tuple<at::Tensor, at::Tensor> max_dim(const at::Tensor& self, int64_t dim, bool keepdim) {
+    return {at::amax(self, {dim}, keepdim), at::argmax(self, dim, keepdim)};
+}
+std::tuple<at::Tensor, at::Tensor> min_dim(const at::Tensor& self, int64_t dim, bool keepdim) {
+    return {at::amin(self, {dim}, keepdim), at::argmin(self, dim, keepdim)};
+}
+std::tuple<at::Tensor&, at::Tensor&> max_dim_out(const at::Tensor& self, int64_t dim, bool keepdim, at::Tensor& values, at::Tensor& indices) {
+    into(values, at::amax(self, {dim}, keepdim));
+    into(indices, at::argmax(self, dim, keepdim));
+    return {values, indices};
+}
+std::tuple<at::Tensor&, at::Tensor&> min_dim_out(const at::Tensor& self, int64_t dim, bool keepdim, at::Tensor& values, at::Tensor& indices) {
+    into(values, at::amin(self, {dim}, keepdim));
+    into(indices, at::argmin(self, dim, keepdim));
+    return {values, indices};
+}
+
+// ---- all / any ----------------------------------------------------------------------------
+// the truth values as 0 / 1 floats, reduced by amin (all) or amax (any)
+at::Tensor truth01(const at::Tensor& self) { return (self.scalar_type() == at::kBool ? self : at::ne(self, 0)).to(at::kFloat); }
+at::Tensor all_any(const at::Tensor& self, std::vector<int64_t> dims, bool keepdim, bool is_all) {
+    if (self.numel() == 0 || self.dim() == 0) {
+        // the empty conjunction is true, the empty disjunction false; a 0-dim tensor is its own truth value
+        if (self.dim() == 0 && self.numel()) return at::ne(self, 0);
+        std::vector<int64_t> shape;
+        for (int64_t i = 0; i < self.dim(); ++i) {
+            const bool reduced = std::find_if(dims.begin(), dims.end(), [&](int64_t d) { return (d < 0 ? d + self.dim() : d) == i; }) != dims.end();
+            if (!reduced) shape.push_back(self.size(i));
+            else if (keepdim) shape.push_back(1);
+        }
+        at::Tensor r = at::empty(shape, self.options().dtype(at::kBool));
+        r.fill_(is_all);
+        return r;
+    }
+    at::Tensor f = truth01(self);
+    return at::gt(is_all ? at::amin(f, dims, keepdim) : at::amax(f, dims, keepdim), 0.5);
+}
+at::Tensor all_full(const at::Tensor& self) { return all_any(self, all_dims(self), false, true); }
+at::Tensor any_full(const at::Tensor& self) { return all_any(self, all_dims(self), false, false); }
+at::Tensor all_dim(const at::Tensor& self, int64_t dim, bool keepdim) { return all_any(self, {dim}, keepdim, true); }
+at::Tensor any_dim(const at::Tensor& self, int64_t dim, bool keepdim) { return all_any(self, {dim}, keepdim, false); }
+at::Tensor all_dims_fn(const at::Tensor& self, at::OptionalIntArrayRef dim, bool keepdim) { return all_any(self, dims_or_all(self, dim), keepdim, true); }
+at::Tensor any_dims_fn(const at::Tensor& self, at::OptionalIntArrayRef dim, bool keepdim) { return all_any(self, dims_or_all(self, dim), keepdim, false); }
+at::Tensor& all_all_out(const at::Tensor& self, at::Tensor& out) { return into(out, all_full(self)); }
+at::Tensor& any_all_out(const at::Tensor& self, at::Tensor& out) { return into(out, any_full(self)); }
+at::Tensor& all_out(const at::Tensor& self, int64_t dim, bool keepdim, at::Tensor& out) { return into(out, all_dim(self, dim, keepdim)); }
+at::Tensor& any_out(const at::Tensor& self, int64_t dim, bool keepdim, at::Tensor& out) { return into(out, any_dim(self, dim, keepdim)); }
+at::Tensor& all_dims_out(const at::Tensor& self, at::OptionalIntArrayRef dim, bool keepdim, at::Tensor& out) { return into(out, all_dims_fn(self, dim, keepdim)); }
+at::Tensor& any_dims_out(const at::Tensor& self, at::OptionalIntArrayRef dim, bool keepdim, at::Tensor& out) { return into(out, any_dims_fn(self, dim, keepdim)); }
+
+// ---- variance, standard deviation, vector norm --------------------------------------------------
+// two passes in fp32: the mean, then the sum of squared deviations divided by n - correction
+std::tuple<at::Tensor, at::Tensor> var_mean_impl(const at::Tensor& self, at::OptionalIntArrayRef dim, const c10::optional<at::Scalar>& correction, bool keepdim) {
+    TORCH_CHECK(is_hot_float(self.scalar_type()), "torchvulkan [NOT IMPLEMENTED]: var / std of ", self.scalar_type());
+    const std::vector<int64_t> dims = dims_or_all(self, dim);
+    at::Tensor x = self.to(at::kFloat);
+    int64_t n = 1;
+    for (int64_t d : dims) n *= self.size(d < 0 ? d + self.dim() : d);
+    at::Tensor mean = self.dim() == 0 ? x : at::mean(x, dims, true);
+    at::Tensor dev = x - mean;
+    at::Tensor ss = self.dim() == 0 ? dev * dev : at::sum(dev * dev, dims, true);
+    const double denom = (double)n - (correction.has_value() ? correction->toDouble() : 1.0);
+    at::Tensor var = ss * (denom > 0.0 ? 1.0 / denom : std::numeric_limits<double>::quiet_NaN());
+    if (!keepdim && self.dim() > 0) {
+        std::vector<int64_t> sorted(dims);
+        for (auto& d : sorted) d = d < 0 ? d + self.dim() : d;
+        std::sort(sorted.rbegin(), sorted.rend());
+        for (int64_t d : sorted) { var = var.squeeze(d); mean = mean.squeeze(d); }
+    }
+    return {var.to(self.scalar_type()), mean.to(self.scalar_type())};
+}
+at::Tensor var_correction(const at::Tensor& self, at::OptionalIntArrayRef dim, const c10::optional<at::Scalar>& correction, bool keepdim) {
+    return std::get<0>(var_mean_impl(self, dim, correction, keepdim));
+}
+at::Tensor std_correction(const at::Tensor& self, at::OptionalIntArrayRef dim, const c10::optional<at::Scalar>& correction, bool keepdim) {
+    return at::sqrt(std::get<0>(var_mean_impl(self, dim, correction, keepdim)));
+}
+std::tuple<at::Tensor, at::Tensor> var_mean_correction(const at::Tensor& self, at::OptionalIntArrayRef dim, const c10::optional<at::Scalar>& correction, bool keepdim) {
+    return var_mean_impl(self, dim, correction, keepdim);
+}
+std::tuple<at::Tensor, at::Tensor> std_mean_correction(const at::Tensor& self, at::OptionalIntArrayRef dim, const c10::optional<at::Scalar>& correction, bool keepdim) {
+    auto vm = var_mean_impl(self, dim, correction, keepdim);
+    return {at::sqrt(std::get<0>(vm)), std::get<1>(vm)};
+}
+
+at::Tensor vector_norm(const at::Tensor& self, const at::Scalar& ord_s, at::OptionalIntArrayRef dim, bool keepdim, c10::optional<at::ScalarType> dtype) {
+    const at::ScalarType out_st = dtype.value_or(self.scalar_type());
+    TORCH_CHECK(is_hot_float(self.scalar_type()) && is_hot_float(out_st), "torchvulkan [NOT IMPLEMENTED]: vector norm of ", self.scalar_type());
+    const double ord = ord_s.toDouble();
+    at::Tensor x = self.to(at::kFloat);
+    if (self.dim() == 0) x = x.reshape({1});
+    const std::vector<int64_t> dims = self.dim() == 0 ? std::vector<int64_t>{0} : dims_or_all(self, dim);
+    const bool keep = keepdim && self.dim() > 0;
+    at::Tensor r;
+    if (ord == 2.0) r = at::sqrt(at::sum(x * x, dims, keep));
+    else if (ord == 1.0) r = at::sum(at::abs(x), dims, keep);
+    else if (std::isinf(ord)) r = ord > 0 ? at::amax(at::abs(x), dims, keep) : at::amin(at::abs(x), dims, keep);
+    else if (ord == 0.0) r = at::sum(at::ne(x, 0).to(at::kFloat), dims, keep);
+    else r = at::pow(at::sum(at::pow(at::abs(x), ord), dims, keep), 1.0 / ord);
+    if (self.dim() == 0) r = r.reshape({});
+    return r.to(out_st);
+}
+at::Tensor& vector_norm_out(const at::Tensor& self, const at::Scalar& ord, at::OptionalIntArrayRef dim, bool keepdim, c10::optional<at::ScalarType> dtype, at::Tensor& out) {
+    return into(out, vector_norm(self, ord, dim, keepdim, dtype));
+}
+
+// ---- masks ---------------------------------------------------------------------------------
+at::Tensor& masked_fill_scalar_(at::Tensor& self, const at::Tensor& mask, const at::Scalar& value) {
+    TORCH_CHECK(mask.scalar_type() == at::kBool, "masked_fill_ only supports boolean masks, but got mask with dtype ", mask.scalar_type());
+    at::Tensor v = at::empty({}, self.options());
+    v.fill_(value);
+    self.copy_(at::where(mask, v, self));
+    return self;
+}
+at::Tensor& masked_fill_tensor_(at::Tensor& self, const at::Tensor& mask, const at::Tensor& value) {
+    TORCH_CHECK(mask.scalar_type() == at::kBool, "masked_fill_ only supports boolean masks, but got mask with dtype ", mask.scalar_type());
+    TORCH_CHECK(value.dim() == 0, "masked_fill_ only supports a 0-dimensional value tensor, but got tensor with ", value.dim(), " dimension(s).");
+    self.copy_(at::where(mask, value.to(self.options()), self));
+    return self;
+}
+
+// lower / upper triangle of the last two dimensions: the band mask is built on the host (rows x cols booleans) and applied
+// with one where launch
+at::Tensor tri_impl(const at::Tensor& self, int64_t diagonal, bool lower) {
+    TORCH_CHECK(self.dim() >= 2, lower ? "tril" : "triu", ": input tensor must have at least 2 dimensions");
+    const int64_t rows = self.size(-2), cols = self.size(-1);
+    at::Tensor band = at::ones({rows, cols}, at::TensorOptions().dtype(at::kBool).device(at::kCPU));
+    band = lower ? band.tril(diagonal) : band.triu(diagonal);
+    at::Tensor zero = at::empty({}, self.options());
+    zero.fill_(0);
+    return at::where(band.to(self.device()), self, zero);
+}
+at::Tensor tril(const at::Tensor& self, int64_t diagonal) { return tri_impl(self, diagonal, true); }
+at::Tensor triu(const at::Tensor& self, int64_t diagonal) { return tri_impl(self, diagonal, false); }
+at::Tensor& tril_(at::Tensor& self, int64_t diagonal) { self.copy_(tri_impl(self, diagonal, true)); return self; }
+at::Tensor& triu_(at::Tensor& self, int64_t diagonal) { self.copy_(tri_impl(self, diagonal, false)); return self; }
+at::Tensor& tril_out(const at::Tensor& self, int64_t diagonal, at::Tensor& out) { return into(out, tri_impl(self, diagonal, true)); }
+at::Tensor& triu_out(const at::Tensor& self, int64_t diagonal, at::Tensor& out) { return into(out, tri_impl(self, diagonal, false)); }
+
+// ---- ranges: computed on the host (they are index vectors, a few KB) and copied to the device ---------------------
+at::Tensor& arange_out(const at::Scalar& start, const at::Scalar& end, const at::Scalar& step, at::Tensor& out) {
+    at::Tensor host = at::arange(start, end, step, out.options().device(at::kCPU));
+    return into(out, host);
+}
+at::Tensor& linspace_out(const at::Scalar& start, const at::Scalar& end, int64_t steps, at::Tensor& out) {
+    at::Tensor host = at::linspace(start, end, steps, out.options().device(at::kCPU));
+    return into(out, host);
+}
+at::Tensor& eye_m_out(int64_t n, int64_t m, at::Tensor& out) {
+    at::Tensor host = at::eye(n, m, out.options().device(at::kCPU));
+    return into(out, host);
+}
+at::Tensor& eye_out(int64_t n, at::Tensor& out) { return eye_m_out(n, n, out); }
+
+// ---- mse_loss ------------------------------------------------------------------------------
+at::Tensor mse_loss(const at::Tensor& self, const at::Tensor& target, int64_t reduction) {
+    at::Tensor d = self - target;
+    at::Tensor sq = d * d;
+    if (reduction == at::Reduction::Mean) return sq.numel() ? at::mean(sq, all_dims(sq), false) : sq.sum() / 0.0;
+    if (reduction == at::Reduction::Sum) return at::sum(sq, all_dims(sq), false);
+    return sq;
+}
+at::Tensor mse_loss_backward(const at::Tensor& grad, const at::Tensor& self, const at::Tensor& target, int64_t reduction) {
+    const double norm = reduction == at::Reduction::Mean ? 2.0 / (double)std::max<int64_t>(self.numel(), 1) : 2.0;
+    return (self - target) * grad * norm;
+}
+
+}  // namespace
+
+TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+    m.impl("max", &max_all);
+    m.impl("min", &min_all);
+    m.impl("max.unary_out", &max_unary_out);
+    m.impl("min.unary_out", &min_unary_out);
+    m.impl("max.dim", &max_dim);
+    m.impl("min.dim", &min_dim);
+    m.impl("max.dim_max", &max_dim_out);
+    m.impl("min.dim_min", &min_dim_out);
+    m.impl("all", &all_full);
+    m.impl("any", &any_full);
+    m.impl("all.dim", &all_dim);
+    m.impl("any.dim", &any_dim);
+    m.impl("all.dims", &all_dims_fn);
+    m.impl("any.dims", &any_dims_fn);
+    m.impl("all.all_out", &all_all_out);
+    m.impl("any.all_out", &any_all_out);
+    m.impl("all.out", &all_out);
+    m.impl("any.out", &any_out);
+    m.impl("all.dims_out", &all_dims_out);
+    m.impl("any.dims_out", &any_dims_out);
+    m.impl("var.correction", &var_correction);
+    m.impl("std.correction", &std_correction);
+    m.impl("var_mean.correction", &var_mean_correction);
+    m.impl("std_mean.correction", &std_mean_correction);
+    m.impl("linalg_vector_norm", &vector_norm);
+    m.impl("linalg_vector_norm.out", &vector_norm_out);
+    m.impl("masked_fill_.Scalar", &masked_fill_scalar_);
+    m.impl("masked_fill_.Tensor", &masked_fill_tensor_);
+    m.impl("tril", &tril);
+    m.impl("triu", &triu);
+    m.impl("tril_", &tril_);
+    m.impl("triu_", &triu_);
+    m.impl("tril.out", &tril_out);
+    m.impl("triu.out", &triu_out);
+    m.impl("arange.start_out", &arange_out);
+    m.impl("linspace.out", &linspace_out);
+    m.impl("eye.m_out", &eye_m_out);
+    m.impl("eye.out", &eye_out);
+    m.impl("mse_loss", &mse_loss);
+    m.impl("mse_loss_backward", &mse_loss_backward);
+}
+
+}  // namespace tvk_aten

@@ -8,6 +8,8 @@
 // strided/broadcast kernel. Unsupported dtypes raise; nothing falls back to the CPU.
 #include "common.h"
 
+#include <limits>
+
 namespace tvk_aten {
 namespace {
 
@@ -185,7 +187,8 @@ at::Tensor& threshold_backward_out(const at::Tensor& grad, const at::Tensor& sel
 at::Tensor compare_impl(int op, const at::Tensor& a_in, const at::Tensor& b_in, at::Tensor out, const char* name) {
     const at::Tensor& anchor = is_vulkan(a_in) ? a_in : b_in;
     const at::ScalarType st = at::result_type(a_in, b_in);
-    if (!is_hot_float(st)) TVK_NOT_IMPLEMENTED(name, " for dtype ", st, " on the vulkan device");
+    const bool is_int = st == at::kLong || st == at::kInt || st == at::kBool || st == at::kByte;     // compared exactly, as 64-bit integers
+    if (!is_hot_float(st) && !is_int) TVK_NOT_IMPLEMENTED(name, " for dtype ", st, " on the vulkan device");
     const int dt = to_tvk_dtype(st);
     DeviceScope scope(anchor);
     if (is_vulkan(a_in) && is_cpu_scalar(b_in) && a_in.is_contiguous()) {
@@ -214,6 +217,152 @@ template <int OP> at::Tensor cmp_tensor(const at::Tensor& a, const at::Tensor& b
 template <int OP> at::Tensor& cmp_tensor_out(const at::Tensor& a, const at::Tensor& b, at::Tensor& out) { compare_impl(OP, a, b, out, "comparison"); return out; }
 template <int OP> at::Tensor cmp_scalar(const at::Tensor& a, const at::Scalar& b) { return compare_impl(OP, a, scalar_tensor_like(b, a), {}, "comparison"); }
 template <int OP> at::Tensor& cmp_scalar_out(const at::Tensor& a, const at::Scalar& b, at::Tensor& out) { compare_impl(OP, a, scalar_tensor_like(b, a), out, "comparison"); return out; }
+
+// ---- one tensor and two scalar parameters (clamp, hardtanh, leaky_relu, elu, softplus) ----------------------------
+// The kernels are the binary family's scalar-operand form (b == NULL): b_scalar and alpha carry the parameters.
+at::Tensor scalar_binary(int op, const at::Tensor& self, double bs, double alpha, at::Tensor out, const char* name) {
+    require_float(self, name);
+    at::Tensor a = self.is_non_overlapping_and_dense() ? self : contiguous_vulkan(self);
+    const bool direct = out.defined() && out.scalar_type() == a.scalar_type() && same_dense_layout(a, out);
+    at::Tensor target = direct ? out : alloc_like(a, a.scalar_type());
+    if (a.numel()) {
+        DeviceScope scope(a);
+        TVK_CALL(tvk_binary(op, to_tvk_dtype(a.scalar_type()), target.data_ptr(), a.data_ptr(), nullptr, bs, alpha, a.numel(), scope.stream));
+    }
+    if (out.defined() && !direct) {
+        if (out.sizes() != a.sizes()) out.resize_(a.sizes());
+        out.copy_(target);
+        return out;
+    }
+    return target;
+}
+at::Tensor clamp_impl(const at::Tensor& self, const c10::optional<at::Scalar>& lo, const c10::optional<at::Scalar>& hi, at::Tensor out) {
+    TORCH_CHECK(lo.has_value() || hi.has_value(), "torch.clamp: At least one of 'min' or 'max' must not be None");
+    return scalar_binary(TVK_B_CLAMP, self, hi.has_value() ? hi->toDouble() : std::numeric_limits<double>::infinity(),
+                         lo.has_value() ? lo->toDouble() : -std::numeric_limits<double>::infinity(), out, "clamp");
+}
+at::Tensor clamp(const at::Tensor& self, const c10::optional<at::Scalar>& lo, const c10::optional<at::Scalar>& hi) { return clamp_impl(self, lo, hi, {}); }
+at::Tensor& clamp_(at::Tensor& self, const c10::optional<at::Scalar>& lo, const c10::optional<at::Scalar>& hi) { clamp_impl(self, lo, hi, self); return self; }
+at::Tensor& clamp_out(const at::Tensor& self, const c10::optional<at::Scalar>& lo, const c10::optional<at::Scalar>& hi, at::Tensor& out) { clamp_impl(self, lo, hi, out); return out; }
+at::Tensor clamp_min(const at::Tensor& self, const at::Scalar& lo) { return clamp_impl(self, lo, c10::nullopt, {}); }
+at::Tensor& clamp_min_(at::Tensor& self, const at::Scalar& lo) { clamp_impl(self, lo, c10::nullopt, self); return self; }
+at::Tensor& clamp_min_out(const at::Tensor& self, const at::Scalar& lo, at::Tensor& out) { clamp_impl(self, lo, c10::nullopt, out); return out; }
+at::Tensor clamp_max(const at::Tensor& self, const at::Scalar& hi) { return clamp_impl(self, c10::nullopt, hi, {}); }
+at::Tensor& clamp_max_(at::Tensor& self, const at::Scalar& hi) { clamp_impl(self, c10::nullopt, hi, self); return self; }
+at::Tensor& clamp_max_out(const at::Tensor& self, const at::Scalar& hi, at::Tensor& out) { clamp_impl(self, c10::nullopt, hi, out); return out; }
+at::Tensor hardtanh(const at::Tensor& self, const at::Scalar& lo, const at::Scalar& hi) { return clamp_impl(self, lo, hi, {}); }
+at::Tensor& hardtanh_(at::Tensor& self, const at::Scalar& lo, const at::Scalar& hi) { clamp_impl(self, lo, hi, self); return self; }
+at::Tensor& hardtanh_out(const at::Tensor& self, const at::Scalar& lo, const at::Scalar& hi, at::Tensor& out) { clamp_impl(self, lo, hi, out); return out; }
+// grad where lo < x < hi, else 0 (hardtanh_backward of ATen)
+at::Tensor hardtanh_backward(const at::Tensor& grad, const at::Tensor& self, const at::Scalar& lo, const at::Scalar& hi) {
+    return at::where(at::logical_and(at::gt(self, lo), at::lt(self, hi)), grad, at::zeros({}, grad.options()));
+}
+at::Tensor leaky_relu(const at::Tensor& self, const at::Scalar& slope) { return scalar_binary(TVK_B_LEAKY_RELU, self, slope.toDouble(), 1.0, {}, "leaky_relu"); }
+at::Tensor& leaky_relu_(at::Tensor& self, const at::Scalar& slope) { scalar_binary(TVK_B_LEAKY_RELU, self, slope.toDouble(), 1.0, self, "leaky_relu_"); return self; }
+at::Tensor& leaky_relu_out(const at::Tensor& self, const at::Scalar& slope, at::Tensor& out) { scalar_binary(TVK_B_LEAKY_RELU, self, slope.toDouble(), 1.0, out, "leaky_relu.out"); return out; }
+at::Tensor leaky_relu_backward(const at::Tensor& grad, const at::Tensor& self, const at::Scalar& slope, bool self_is_result) {
+    // with a positive slope the sign of the result is the sign of the input, so the same test serves both
+    TORCH_CHECK(!self_is_result || slope.toDouble() > 0.0, "In-place leakyReLu backward calculation is triggered with a negative slope which is not supported.");
+    return binary_impl(TVK_B_LEAKY_RELU_BACKWARD, grad, self, slope.toDouble(), {}, "leaky_relu_backward");
+}
+void elu_check(const at::Scalar& scale, const at::Scalar& input_scale) {
+    if (scale.toDouble() != 1.0 || input_scale.toDouble() != 1.0) TVK_NOT_IMPLEMENTED("elu with scale or input_scale other than 1 (selu, celu)");
+}
+at::Tensor elu(const at::Tensor& self, const at::Scalar& alpha, const at::Scalar& scale, const at::Scalar& input_scale) {
+    elu_check(scale, input_scale);
+    return scalar_binary(TVK_B_ELU, self, 0.0, alpha.toDouble(), {}, "elu");
+}
+at::Tensor& elu_(at::Tensor& self, const at::Scalar& alpha, const at::Scalar& scale, const at::Scalar& input_scale) {
+    elu_check(scale, input_scale);
+    scalar_binary(TVK_B_ELU, self, 0.0, alpha.toDouble(), self, "elu_");
+    return self;
+}
+at::Tensor& elu_out(const at::Tensor& self, const at::Scalar& alpha, const at::Scalar& scale, const at::Scalar& input_scale, at::Tensor& out) {
+    elu_check(scale, input_scale);
+    scalar_binary(TVK_B_ELU, self, 0.0, alpha.toDouble(), out, "elu.out");
+    return out;
+}
+at::Tensor elu_backward(const at::Tensor& grad, const at::Scalar& alpha, const at::Scalar& scale, const at::Scalar& input_scale, bool is_result,
+                        const at::Tensor& self_or_result) {
+    elu_check(scale, input_scale);
+    // from the result y = alpha * (exp(x) - 1) for x <= 0: dy/dx = y + alpha
+    if (is_result) return at::where(at::gt(self_or_result, 0), grad, grad * (self_or_result + alpha));
+    return binary_impl(TVK_B_ELU_BACKWARD, grad, self_or_result, alpha.toDouble(), {}, "elu_backward");
+}
+at::Tensor softplus(const at::Tensor& self, const at::Scalar& beta, const at::Scalar& threshold) {
+    return scalar_binary(TVK_B_SOFTPLUS, self, threshold.toDouble(), beta.toDouble(), {}, "softplus");
+}
+at::Tensor& softplus_out(const at::Tensor& self, const at::Scalar& beta, const at::Scalar& threshold, at::Tensor& out) {
+    scalar_binary(TVK_B_SOFTPLUS, self, threshold.toDouble(), beta.toDouble(), out, "softplus.out");
+    return out;
+}
+at::Tensor softplus_backward(const at::Tensor& grad, const at::Tensor& self, const at::Scalar& beta, const at::Scalar& threshold) {
+    if (threshold.toDouble() != 20.0) TVK_NOT_IMPLEMENTED("softplus backward with a threshold other than 20");
+    return binary_impl(TVK_B_SOFTPLUS_BACKWARD, grad, self, beta.toDouble(), {}, "softplus_backward");
+}
+template <int OP> at::Tensor grad_x_fn(const at::Tensor& grad, const at::Tensor& self) { return binary_impl(OP, grad, self, 1.0, {}, "activation backward"); }
+std::tuple<at::Tensor, at::Tensor> log_sigmoid_forward(const at::Tensor& self) {
+    return {unary_fn<TVK_U_LOGSIGMOID>(self), at::empty({0}, self.options())};      // (the buffer is a CPU-kernel detail; unused here)
+}
+at::Tensor log_sigmoid_backward(const at::Tensor& grad, const at::Tensor& self, const at::Tensor&) {
+    return binary_impl(TVK_B_LOGSIGMOID_BACKWARD, grad, self, 1.0, {}, "log_sigmoid_backward");
+}
+
+// ---- logical ops on boolean tensors ------------------------------------------------------
+// any dtype in (x != 0 is true), Bool out; the operands are broadcast and made contiguous first (masks are small next to
+// the tensors they select from)
+at::Tensor as_bool(const at::Tensor& t) {
+    if (t.scalar_type() == at::kBool) return t;
+    return at::ne(t, 0);
+}
+at::Tensor logical_impl(int op, const at::Tensor& a_in, const at::Tensor* b_in, at::Tensor out) {
+    const at::Tensor& anchor = (b_in && !is_vulkan(a_in)) ? *b_in : a_in;
+    auto bring = [&](const at::Tensor& t) { return is_vulkan(t) ? as_bool(t) : t.to(at::kBool).to(anchor.device()); };
+    at::Tensor a = bring(a_in), b;
+    std::vector<int64_t> shape(a.sizes().begin(), a.sizes().end());
+    if (b_in) {
+        b = bring(*b_in);
+        shape = at::infer_size(a.sizes(), b.sizes());
+        b = contiguous_vulkan(b.expand(shape));
+    }
+    a = contiguous_vulkan(a.expand(shape));
+    at::Tensor target = (out.defined() && out.scalar_type() == at::kBool && out.is_contiguous() && out.sizes() == at::IntArrayRef(shape)) ? out
+                                                                                                                                       : empty_vulkan(shape, at::kBool, anchor.device());
+    if (target.numel()) {
+        DeviceScope scope(anchor);
+        TVK_CALL(tvk_logical(op, (uint8_t*)target.data_ptr(), (const uint8_t*)a.data_ptr(), b_in ? (const uint8_t*)b.data_ptr() : nullptr, target.numel(), scope.stream));
+    }
+    if (out.defined() && !target.is_same(out)) {
+        if (out.sizes() != at::IntArrayRef(shape)) out.resize_(shape);
+        out.copy_(target);
+        return out;
+    }
+    return target;
+}
+template <int OP> at::Tensor logical_fn(const at::Tensor& a, const at::Tensor& b) { return logical_impl(OP, a, &b, {}); }
+template <int OP> at::Tensor& logical_out(const at::Tensor& a, const at::Tensor& b, at::Tensor& out) { logical_impl(OP, a, &b, out); return out; }
+template <int OP> at::Tensor& logical_fn_(at::Tensor& a, const at::Tensor& b) { logical_impl(OP, a, &b, a); return a; }
+at::Tensor logical_not(const at::Tensor& a) { return logical_impl(TVK_L_NOT, a, nullptr, {}); }
+at::Tensor& logical_not_out(const at::Tensor& a, at::Tensor& out) { logical_impl(TVK_L_NOT, a, nullptr, out); return out; }
+// bitwise ops: on Bool tensors they are the logical ops (masks); integer tensors are not handled
+void require_bool(const at::Tensor& a, const char* name) {
+    if (a.scalar_type() != at::kBool) TVK_NOT_IMPLEMENTED(name, " for dtype ", a.scalar_type(), " (Bool masks are supported)");
+}
+template <int OP> at::Tensor bitwise_fn(const at::Tensor& a, const at::Tensor& b) { require_bool(a, "bitwise op"); require_bool(b, "bitwise op"); return logical_impl(OP, a, &b, {}); }
+template <int OP> at::Tensor& bitwise_out(const at::Tensor& a, const at::Tensor& b, at::Tensor& out) { require_bool(a, "bitwise op"); require_bool(b, "bitwise op"); logical_impl(OP, a, &b, out); return out; }
+at::Tensor bitwise_not(const at::Tensor& a) { require_bool(a, "bitwise_not"); return logical_impl(TVK_L_NOT, a, nullptr, {}); }
+at::Tensor& bitwise_not_out(const at::Tensor& a, at::Tensor& out) { require_bool(a, "bitwise_not"); logical_impl(TVK_L_NOT, a, nullptr, out); return out; }
+
+// the product of two masks is their conjunction
+at::Tensor mul_tensor(const at::Tensor& a, const at::Tensor& b) {
+    if (a.scalar_type() == at::kBool && b.scalar_type() == at::kBool) return logical_impl(TVK_L_AND, a, &b, {});
+    return binary_impl(TVK_B_MUL, a, b, 1.0, {}, "binary op", true);
+}
+
+// isnan / isposinf / isneginf as comparisons
+at::Tensor isnan(const at::Tensor& self) { return compare_impl(TVK_C_NE, self, self, {}, "isnan"); }
+at::Tensor& isposinf_out(const at::Tensor& self, at::Tensor& out) { compare_impl(TVK_C_EQ, self, scalar_tensor_like(std::numeric_limits<double>::infinity(), self), out, "isposinf"); return out; }
+at::Tensor& isneginf_out(const at::Tensor& self, at::Tensor& out) { compare_impl(TVK_C_EQ, self, scalar_tensor_like(-std::numeric_limits<double>::infinity(), self), out, "isneginf"); return out; }
 
 // ---- ternary ----------------------------------------------------------------------------
 at::Tensor ternary_impl(int op, const at::Tensor& a_in, const at::Tensor& b_in, const at::Tensor* c_in, double value, at::Tensor out, const char* name) {
@@ -335,7 +484,7 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("sub.Tensor", &sub);
     m.impl("sub_.Tensor", &sub_);
     m.impl("sub.out", &sub_out);
-    m.impl("mul.Tensor", &bin_fn<TVK_B_MUL, true>);
+    m.impl("mul.Tensor", &mul_tensor);
     m.impl("mul_.Tensor", &bin_fn_<TVK_B_MUL, true>);
     m.impl("mul.out", &bin_out<TVK_B_MUL, true>);
     m.impl("div.Tensor", &bin_fn<TVK_B_DIV, false>);
@@ -359,6 +508,90 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("sigmoid_backward.grad_input", &bin_out<TVK_B_SIGMOID_BACKWARD, false>);
     m.impl("tanh_backward", &bin_fn<TVK_B_TANH_BACKWARD, false>);
     m.impl("tanh_backward.grad_input", &bin_out<TVK_B_TANH_BACKWARD, false>);
+
+    REG_UNARY(m, "floor", TVK_U_FLOOR);
+    REG_UNARY(m, "ceil", TVK_U_CEIL);
+    REG_UNARY(m, "round", TVK_U_ROUND);
+    REG_UNARY(m, "trunc", TVK_U_TRUNC);
+    REG_UNARY(m, "sign", TVK_U_SIGN);
+    REG_UNARY(m, "log2", TVK_U_LOG2);
+    REG_UNARY(m, "log10", TVK_U_LOG10);
+    REG_UNARY(m, "log1p", TVK_U_LOG1P);
+    REG_UNARY(m, "expm1", TVK_U_EXPM1);
+    REG_UNARY(m, "exp2", TVK_U_EXP2);
+    REG_UNARY(m, "tan", TVK_U_TAN);
+    REG_UNARY(m, "sinh", TVK_U_SINH);
+    REG_UNARY(m, "cosh", TVK_U_COSH);
+    REG_UNARY(m, "asin", TVK_U_ASIN);
+    REG_UNARY(m, "acos", TVK_U_ACOS);
+    REG_UNARY(m, "atan", TVK_U_ATAN);
+    REG_UNARY(m, "erf", TVK_U_ERF);
+    REG_UNARY(m, "erfc", TVK_U_ERFC);
+    REG_UNARY(m, "hardsigmoid", TVK_U_HARDSIGMOID);
+    REG_UNARY(m, "hardswish", TVK_U_HARDSWISH);
+    REG_UNARY(m, "mish", TVK_U_MISH);
+    m.impl("fmod.Tensor", &bin_fn<TVK_B_FMOD, false>);
+    m.impl("fmod_.Tensor", &bin_fn_<TVK_B_FMOD, false>);
+    m.impl("fmod.Tensor_out", &bin_out<TVK_B_FMOD, false>);
+    m.impl("remainder.Tensor", &bin_fn<TVK_B_REMAINDER, false>);
+    m.impl("remainder_.Tensor", &bin_fn_<TVK_B_REMAINDER, false>);
+    m.impl("remainder.Tensor_out", &bin_out<TVK_B_REMAINDER, false>);
+    m.impl("atan2", &bin_fn<TVK_B_ATAN2, false>);
+    m.impl("atan2_", &bin_fn_<TVK_B_ATAN2, false>);
+    m.impl("atan2.out", &bin_out<TVK_B_ATAN2, false>);
+    m.impl("floor_divide", &bin_fn<TVK_B_FLOOR_DIVIDE, false>);
+    m.impl("floor_divide_.Tensor", &bin_fn_<TVK_B_FLOOR_DIVIDE, false>);
+    m.impl("floor_divide.out", &bin_out<TVK_B_FLOOR_DIVIDE, false>);
+    m.impl("clamp", &clamp);
+    m.impl("clamp_", &clamp_);
+    m.impl("clamp.out", &clamp_out);
+    m.impl("clamp_min", &clamp_min);
+    m.impl("clamp_min_", &clamp_min_);
+    m.impl("clamp_min.out", &clamp_min_out);
+    m.impl("clamp_max", &clamp_max);
+    m.impl("clamp_max_", &clamp_max_);
+    m.impl("clamp_max.out", &clamp_max_out);
+    m.impl("hardtanh", &hardtanh);
+    m.impl("hardtanh_", &hardtanh_);
+    m.impl("hardtanh.out", &hardtanh_out);
+    m.impl("hardtanh_backward", &hardtanh_backward);
+    m.impl("leaky_relu", &leaky_relu);
+    m.impl("leaky_relu_", &leaky_relu_);
+    m.impl("leaky_relu.out", &leaky_relu_out);
+    m.impl("leaky_relu_backward", &leaky_relu_backward);
+    m.impl("elu", &elu);
+    m.impl("elu_", &elu_);
+    m.impl("elu.out", &elu_out);
+    m.impl("elu_backward", &elu_backward);
+    m.impl("softplus", &softplus);
+    m.impl("softplus.out", &softplus_out);
+    m.impl("softplus_backward", &softplus_backward);
+    m.impl("hardswish_backward", &grad_x_fn<TVK_B_HARDSWISH_BACKWARD>);
+    m.impl("hardsigmoid_backward", &grad_x_fn<TVK_B_HARDSIGMOID_BACKWARD>);
+    m.impl("mish_backward", &grad_x_fn<TVK_B_MISH_BACKWARD>);
+    m.impl("log_sigmoid_forward", &log_sigmoid_forward);
+    m.impl("log_sigmoid_backward", &log_sigmoid_backward);
+    m.impl("logical_and", &logical_fn<TVK_L_AND>);
+    m.impl("logical_and_", &logical_fn_<TVK_L_AND>);
+    m.impl("logical_and.out", &logical_out<TVK_L_AND>);
+    m.impl("logical_or", &logical_fn<TVK_L_OR>);
+    m.impl("logical_or_", &logical_fn_<TVK_L_OR>);
+    m.impl("logical_or.out", &logical_out<TVK_L_OR>);
+    m.impl("logical_xor", &logical_fn<TVK_L_XOR>);
+    m.impl("logical_xor.out", &logical_out<TVK_L_XOR>);
+    m.impl("logical_not", &logical_not);
+    m.impl("logical_not.out", &logical_not_out);
+    m.impl("bitwise_and.Tensor", &bitwise_fn<TVK_L_AND>);
+    m.impl("bitwise_and.Tensor_out", &bitwise_out<TVK_L_AND>);
+    m.impl("bitwise_or.Tensor", &bitwise_fn<TVK_L_OR>);
+    m.impl("bitwise_or.Tensor_out", &bitwise_out<TVK_L_OR>);
+    m.impl("bitwise_xor.Tensor", &bitwise_fn<TVK_L_XOR>);
+    m.impl("bitwise_xor.Tensor_out", &bitwise_out<TVK_L_XOR>);
+    m.impl("bitwise_not", &bitwise_not);
+    m.impl("bitwise_not.out", &bitwise_not_out);
+    m.impl("isnan", &isnan);
+    m.impl("isposinf.out", &isposinf_out);
+    m.impl("isneginf.out", &isneginf_out);
 
 #define REG_CMP(name, OP)                                   \
     m.impl(name ".Tensor", &cmp_tensor<OP>);                \

@@ -53,8 +53,35 @@ at::Tensor reduce_dims(int op, const at::Tensor& self, at::OptionalIntArrayRef d
     at::ScalarType out_st = dtype.value_or(in_st);
     at::Tensor x = self;
     if (c10::isIntegralType(in_st, true) && (op == TVK_R_SUM)) {
-        // integer sums promote to int64 in ATen; this path computes them in fp32 only when asked for a float result
-        TORCH_CHECK(dtype.has_value() && is_hot_float(*dtype), "torchvulkan [NOT IMPLEMENTED]: ", name, " of integer tensors without a floating dtype");
+        if (!(dtype.has_value() && is_hot_float(*dtype))) {
+            // Integer (and boolean) sums promote to int64 in ATen and must be exact: the reduced dimensions are moved last and
+            // folded into one, scanned by the 64-bit cumulative sum, and the last column is the result. Counts and index
+            // bookkeeping, not a hot path.
+            TORCH_CHECK(!dtype.has_value() || c10::isIntegralType(*dtype, false), "torchvulkan [NOT IMPLEMENTED]: ", name, " of ", in_st, " into ", *dtype);
+            const int64_t nd = self.dim();
+            std::vector<bool> red(nd, false);
+            if (!dims.has_value() || dims->empty()) std::fill(red.begin(), red.end(), true);
+            else for (int64_t d : *dims) red[at::maybe_wrap_dim(d, nd)] = true;
+            std::vector<int64_t> perm, kept_shape, keep_shape;
+            int64_t count = 1;
+            for (int64_t d = 0; d < nd; ++d) {
+                keep_shape.push_back(red[d] ? 1 : self.size(d));
+                if (!red[d]) { perm.push_back(d); kept_shape.push_back(self.size(d)); }
+            }
+            for (int64_t d = 0; d < nd; ++d)
+                if (red[d]) { perm.push_back(d); count *= self.size(d); }
+            at::Tensor result;
+            if (nd == 0) result = self.to(at::kLong);
+            else if (count == 0) result = at::zeros(kept_shape, self.options().dtype(at::kLong));
+            else {
+                std::vector<int64_t> folded(kept_shape);
+                folded.push_back(count);
+                at::Tensor y = contiguous_vulkan(self.to(at::kLong).permute(perm)).reshape(folded);
+                result = at::cumsum(y, -1).select(-1, count - 1);
+            }
+            result = result.to(dtype.value_or(at::kLong));
+            return (keepdim && nd > 0) ? result.reshape(keep_shape) : result;
+        }
         x = self.to(*dtype);
         in_st = *dtype;
     }

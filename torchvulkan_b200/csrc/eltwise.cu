@@ -29,6 +29,28 @@ template <int OP> __device__ __forceinline__ float unary_apply(float x) {
     else if constexpr (OP == TVK_U_SQUARE) return x * x;
     else if constexpr (OP == TVK_U_SIN) return sinf(x);
     else if constexpr (OP == TVK_U_COS) return cosf(x);
+    else if constexpr (OP == TVK_U_FLOOR) return floorf(x);
+    else if constexpr (OP == TVK_U_CEIL) return ceilf(x);
+    else if constexpr (OP == TVK_U_ROUND) return rintf(x);
+    else if constexpr (OP == TVK_U_TRUNC) return truncf(x);
+    else if constexpr (OP == TVK_U_SIGN) return (float)((x > 0.f) - (x < 0.f));
+    else if constexpr (OP == TVK_U_LOG2) return log2f(x);
+    else if constexpr (OP == TVK_U_LOG10) return log10f(x);
+    else if constexpr (OP == TVK_U_LOG1P) return log1pf(x);
+    else if constexpr (OP == TVK_U_EXPM1) return expm1f(x);
+    else if constexpr (OP == TVK_U_EXP2) return exp2f(x);
+    else if constexpr (OP == TVK_U_TAN) return tanf(x);
+    else if constexpr (OP == TVK_U_SINH) return sinhf(x);
+    else if constexpr (OP == TVK_U_COSH) return coshf(x);
+    else if constexpr (OP == TVK_U_ASIN) return asinf(x);
+    else if constexpr (OP == TVK_U_ACOS) return acosf(x);
+    else if constexpr (OP == TVK_U_ATAN) return atanf(x);
+    else if constexpr (OP == TVK_U_ERF) return erff(x);
+    else if constexpr (OP == TVK_U_ERFC) return erfcf(x);
+    else if constexpr (OP == TVK_U_HARDSIGMOID) return fminf(fmaxf(x + 3.0f, 0.0f), 6.0f) / 6.0f;
+    else if constexpr (OP == TVK_U_HARDSWISH) return x * fminf(fmaxf(x + 3.0f, 0.0f), 6.0f) / 6.0f;
+    else if constexpr (OP == TVK_U_MISH) return x * tanhf(x > 20.0f ? x : log1pf(expf(x)));
+    else if constexpr (OP == TVK_U_LOGSIGMOID) return fminf(x, 0.0f) - log1pf(expf(-fabsf(x)));
     else return x;
 }
 
@@ -56,10 +78,55 @@ template <int OP> __device__ __forceinline__ float binary_apply(float a, float b
         return a * s * (1.0f + b * (1.0f - s));
     } else if constexpr (OP == TVK_B_SIGMOID_BACKWARD) return a * (1.0f - b) * b;
     else if constexpr (OP == TVK_B_TANH_BACKWARD) return a * (1.0f - b * b);
-    else return a;
+    else if constexpr (OP == TVK_B_FMOD) return fmodf(a, b);
+    else if constexpr (OP == TVK_B_REMAINDER) {
+        float r = fmodf(a, b);
+        if (r != 0.0f && ((r < 0.0f) != (b < 0.0f))) r += b;
+        return r;
+    } else if constexpr (OP == TVK_B_ATAN2) return atan2f(a, b);
+    else if constexpr (OP == TVK_B_FLOOR_DIVIDE) {
+        if (b == 0.0f) return a / b;
+        const float mod = fmodf(a, b);
+        float div = (a - mod) / b;
+        if (mod != 0.0f && ((b < 0.0f) != (mod < 0.0f))) div -= 1.0f;
+        if (div == 0.0f) return copysignf(0.0f, a / b);
+        float fl = floorf(div);
+        if (div - fl > 0.5f) fl += 1.0f;
+        return fl;
+    } else if constexpr (OP == TVK_B_CLAMP) return (a != a) ? a : fminf(fmaxf(a, alpha), b);
+    else if constexpr (OP == TVK_B_LEAKY_RELU) return a > 0.0f ? a : a * b;
+    else if constexpr (OP == TVK_B_ELU) return a > 0.0f ? a : alpha * expm1f(a);
+    else if constexpr (OP == TVK_B_SOFTPLUS) return (a * alpha > b) ? a : log1pf(expf(a * alpha)) / alpha;
+    else if constexpr (OP == TVK_B_LEAKY_RELU_BACKWARD) return b > 0.0f ? a : a * alpha;
+    else if constexpr (OP == TVK_B_ELU_BACKWARD) return b > 0.0f ? a : a * alpha * expf(b);
+    else if constexpr (OP == TVK_B_HARDSWISH_BACKWARD) return b < -3.0f ? 0.0f : (b <= 3.0f ? a * (b / 3.0f + 0.5f) : a);
+    else if constexpr (OP == TVK_B_HARDSIGMOID_BACKWARD) return (b > -3.0f && b < 3.0f) ? a * (1.0f / 6.0f) : 0.0f;
+    else if constexpr (OP == TVK_B_MISH_BACKWARD) {
+        const float sp = b > 20.0f ? b : log1pf(expf(b)), t = tanhf(sp), sg = 1.0f / (1.0f + expf(-b));
+        return a * (t + b * sg * (1.0f - t * t));
+    } else if constexpr (OP == TVK_B_LOGSIGMOID_BACKWARD) return a / (1.0f + expf(b));
+    else if constexpr (OP == TVK_B_SOFTPLUS_BACKWARD) {
+        const float z = expf(b * alpha);
+        return (b * alpha > 20.0f) ? a : a * z / (z + 1.0f);
+    } else return a;
 }
 
-template <int OP> __device__ __forceinline__ bool compare_apply(float a, float b) {
+template <typename T> struct CmpVal { using type = float; static __device__ __forceinline__ float get(T v) { return to_f32(v); } };
+template <> struct CmpVal<int64_t> { using type = int64_t; static __device__ __forceinline__ int64_t get(int64_t v) { return v; } };
+template <> struct CmpVal<int32_t> { using type = int64_t; static __device__ __forceinline__ int64_t get(int32_t v) { return v; } };
+template <> struct CmpVal<uint8_t> { using type = int64_t; static __device__ __forceinline__ int64_t get(uint8_t v) { return v; } };
+#define TVK_DISPATCH_CMP(dtype, T, ...)                                                        \
+    switch (dtype) {                                                                           \
+        case TVK_F32: { using T = float; __VA_ARGS__; break; }                                 \
+        case TVK_F16: { using T = __half; __VA_ARGS__; break; }                                \
+        case TVK_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; }                        \
+        case TVK_I64: { using T = int64_t; __VA_ARGS__; break; }                               \
+        case TVK_I32: { using T = int32_t; __VA_ARGS__; break; }                               \
+        case TVK_U8: { using T = uint8_t; __VA_ARGS__; break; }                                \
+        default: return ::tvk::set_error(TVK_ERR_UNSUPPORTED, "torchvulkan [NOT IMPLEMENTED]: comparison of dtype %d", (int)(dtype)); \
+    }
+
+template <int OP, typename V> __device__ __forceinline__ bool compare_apply(V a, V b) {
     if constexpr (OP == TVK_C_EQ) return a == b;
     else if constexpr (OP == TVK_C_NE) return a != b;
     else if constexpr (OP == TVK_C_LT) return a < b;
@@ -250,10 +317,18 @@ template <int OP> static int binary_op(int dtype, void* out, const void* a, cons
 
 // ---- compare (output u8) and where (u8 condition) ----------------------------------
 template <typename T, int OP>
-__global__ void compare_kernel(uint8_t* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b, float bs, int64_t n) {
+__global__ void compare_kernel(uint8_t* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b, typename CmpVal<T>::type bs, int64_t n) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
-        out[i] = compare_apply<OP>(to_f32(a[i]), b ? to_f32(b[i]) : bs) ? 1 : 0;
+        out[i] = compare_apply<OP>(CmpVal<T>::get(a[i]), b ? CmpVal<T>::get(b[i]) : bs) ? 1 : 0;
+}
+// and / or / xor / not on boolean bytes (any non-zero byte is true; the result is 0 or 1)
+__global__ void logical_kernel(uint8_t* __restrict__ out, const uint8_t* __restrict__ a, const uint8_t* __restrict__ b, int op, int64_t n) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const bool x = a[i] != 0, y = b ? b[i] != 0 : false;
+        out[i] = op == TVK_L_AND ? (x && y) : op == TVK_L_OR ? (x || y) : op == TVK_L_XOR ? (x != y) : !x;
+    }
 }
 template <typename T>
 __global__ void where_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b, const uint8_t* __restrict__ c, int64_t n) {
@@ -526,7 +601,7 @@ __global__ void strided_compare_kernel(uint8_t* out, const T* a, const T* b, Ite
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < it.total; i += stride) {
         int64_t off[3];
         iter_offsets<3>(it, i, off);
-        out[off[0]] = compare_apply<OP>(to_f32(a[off[1]]), to_f32(b[off[2]])) ? 1 : 0;
+        out[off[0]] = compare_apply<OP>(CmpVal<T>::get(a[off[1]]), CmpVal<T>::get(b[off[2]])) ? 1 : 0;
     }
 }
 template <typename T>
@@ -575,6 +650,9 @@ template <typename F> static int dispatch_unary_op(int op, F&& f) {
         C(TVK_U_NEG) C(TVK_U_EXP) C(TVK_U_LOG) C(TVK_U_SQRT) C(TVK_U_RSQRT) C(TVK_U_SIGMOID) C(TVK_U_RELU)
         C(TVK_U_GELU) C(TVK_U_TANH) C(TVK_U_ABS) C(TVK_U_SILU) C(TVK_U_RECIPROCAL) C(TVK_U_SQUARE) C(TVK_U_SIN) C(TVK_U_COS)
         C(TVK_U_GELU_TANH)
+        C(TVK_U_FLOOR) C(TVK_U_CEIL) C(TVK_U_ROUND) C(TVK_U_TRUNC) C(TVK_U_SIGN) C(TVK_U_LOG2) C(TVK_U_LOG10) C(TVK_U_LOG1P) C(TVK_U_EXPM1) C(TVK_U_EXP2)
+        C(TVK_U_TAN) C(TVK_U_SINH) C(TVK_U_COSH) C(TVK_U_ASIN) C(TVK_U_ACOS) C(TVK_U_ATAN) C(TVK_U_ERF) C(TVK_U_ERFC)
+        C(TVK_U_HARDSIGMOID) C(TVK_U_HARDSWISH) C(TVK_U_MISH) C(TVK_U_LOGSIGMOID)
 #undef C
         default: return set_error(TVK_ERR_INVALID, "unknown unary op %d", op);
     }
@@ -585,6 +663,9 @@ template <typename F> static int dispatch_binary_op(int op, F&& f) {
         C(TVK_B_ADD) C(TVK_B_SUB) C(TVK_B_MUL) C(TVK_B_DIV) C(TVK_B_MAXIMUM) C(TVK_B_MINIMUM) C(TVK_B_POW)
         C(TVK_B_GELU_BACKWARD) C(TVK_B_THRESHOLD_BACKWARD) C(TVK_B_SILU_BACKWARD) C(TVK_B_SIGMOID_BACKWARD) C(TVK_B_TANH_BACKWARD)
         C(TVK_B_GELU_TANH_BACKWARD) C(TVK_B_ADD_RELU)
+        C(TVK_B_FMOD) C(TVK_B_REMAINDER) C(TVK_B_ATAN2) C(TVK_B_FLOOR_DIVIDE) C(TVK_B_CLAMP) C(TVK_B_LEAKY_RELU) C(TVK_B_ELU) C(TVK_B_SOFTPLUS)
+        C(TVK_B_LEAKY_RELU_BACKWARD) C(TVK_B_ELU_BACKWARD) C(TVK_B_HARDSWISH_BACKWARD) C(TVK_B_HARDSIGMOID_BACKWARD) C(TVK_B_MISH_BACKWARD)
+        C(TVK_B_LOGSIGMOID_BACKWARD) C(TVK_B_SOFTPLUS_BACKWARD)
 #undef C
         default: return set_error(TVK_ERR_INVALID, "unknown binary op %d", op);
     }
@@ -652,9 +733,17 @@ int tvk_compare(int op, int dtype, uint8_t* out, const void* a, const void* b, d
     cudaStream_t s = (cudaStream_t)stream;
     return dispatch_compare_op(op, [&](auto opc) {
         constexpr int OP = decltype(opc)::value;
-        TVK_DISPATCH_FLOAT(dtype, T, (compare_kernel<T, OP><<<scalar_grid(n), 256, 0, s>>>(out, (const T*)a, (const T*)b, (float)b_scalar, n)));
+        TVK_DISPATCH_CMP(dtype, T, (compare_kernel<T, OP><<<scalar_grid(n), 256, 0, s>>>(out, (const T*)a, (const T*)b, (typename CmpVal<T>::type)b_scalar, n)));
         return launch_status("compare");
     });
+}
+
+int tvk_logical(int op, uint8_t* out, const uint8_t* a, const uint8_t* b, int64_t n, void* stream) {
+    if (n == 0) return TVK_OK;
+    TVK_REQUIRE(op >= 0 && op < TVK_L_COUNT_, "tvk_logical: unknown op %d", op);
+    TVK_REQUIRE(out && a && (b || op == TVK_L_NOT) && n > 0, "tvk_logical: null pointer or negative size");
+    logical_kernel<<<scalar_grid(n), 256, 0, (cudaStream_t)stream>>>(out, a, op == TVK_L_NOT ? nullptr : b, op, n);
+    return launch_status("logical op");
 }
 
 int tvk_ternary(int op, int dtype, void* out, const void* a, const void* b, const void* c, double value, int64_t n,
@@ -743,7 +832,7 @@ int tvk_compare_strided(int op, int dtype, uint8_t* out, const void* a, const vo
     cudaStream_t s = (cudaStream_t)stream;
     return dispatch_compare_op(op, [&](auto opc) {
         constexpr int OP = decltype(opc)::value;
-        TVK_DISPATCH_FLOAT(dtype, T, (strided_compare_kernel<T, OP><<<scalar_grid(ia.total), 256, 0, s>>>(out, (const T*)a, (const T*)b, ia)));
+        TVK_DISPATCH_CMP(dtype, T, (strided_compare_kernel<T, OP><<<scalar_grid(ia.total), 256, 0, s>>>(out, (const T*)a, (const T*)b, ia)));
         return launch_status("strided compare");
     });
 }
