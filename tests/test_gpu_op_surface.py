@@ -242,3 +242,51 @@ def test_mse_and_bce_losses(vk, reduction):
     _close(bd, bc, 1e-5)
     bd.backward(gy.to(vk)); bc.backward(gy)
     _close(xd2.grad, xc2.grad, 1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_gather_family_with_gradients(vk, dtype):
+    """index_select, gather, x[idx] and their adjoints (index_add, scatter_add, accumulate-put) on the row-gather kernel and
+    its deterministic backward; flip, roll, one_hot, prod, equal."""
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(7, 9, 5, generator=g).to(dtype)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+
+    def both(fn, *idx):
+        xd, xc = x.to(vk).requires_grad_(), x.double().requires_grad_()
+        yd, yc = fn(xd, *[i.to(vk) for i in idx]), fn(xc, *idx)
+        _close(yd.double(), yc, tol)
+        gy = torch.randn(yc.shape, generator=g).to(dtype)
+        yd.backward(gy.to(vk)); yc.backward(gy.double())
+        _close(xd.grad.double(), xc.grad, tol)
+
+    i1 = torch.tensor([3, 0, 3, 6, 1])
+    for dim in (0, 1, 2, -1):
+        both(lambda t, i, dim=dim: t.index_select(dim, i), i1 % x.size(dim))
+    both(lambda t, i: t[i], i1)                                              # rows by an index vector (repeats add up in the gradient)
+    both(lambda t, i: t[i], torch.tensor([[0, 2], [6, -1]]))                 # an index matrix, a negative index
+    both(lambda t, i: t[:, i], torch.tensor([8, 8, 1]))
+    both(lambda t, i: t[..., i], torch.tensor([4, 0]))
+    for dim in (0, 1, 2):
+        idx = torch.randint(0, x.size(dim), (7, 9, 5), generator=g)
+        both(lambda t, i, dim=dim: t.gather(dim, i), idx)
+    both(lambda t, i: t.gather(1, i), torch.randint(0, 9, (4, 3, 5), generator=g))      # an index smaller than the input
+    both(lambda t, i: t.log_softmax(-1).gather(-1, i), torch.randint(0, 5, (7, 9, 1), generator=g))   # picking token log-probabilities
+    both(lambda t: t.flip(0))
+    both(lambda t: t.flip((1, 2)))
+    both(lambda t: t.roll(2, 1))
+    both(lambda t: t.roll((-1, 3), (0, 2)))
+    both(lambda t: t.roll(4))
+    xd = x.to(vk)
+    _close(torch.zeros(7, 9, 5, dtype=dtype).to(vk).scatter_add(1, torch.zeros(7, 2, 5, dtype=torch.long).to(vk), xd[:, :2]),
+           torch.zeros(7, 9, 5, dtype=dtype).scatter_add(1, torch.zeros(7, 2, 5, dtype=torch.long), x[:, :2]), tol)
+    _close(xd.index_add(1, torch.tensor([0, 0, 4]).to(vk), xd[:, :3], alpha=0.5), x.index_add(1, torch.tensor([0, 0, 4]), x[:, :3], alpha=0.5), tol)
+    labels = torch.tensor([[1, 3, 0], [2, 2, 4]])
+    _close(F.one_hot(labels.to(vk), 5), F.one_hot(labels, 5), 0)
+    _close(xd.scatter(2, torch.randint(0, 5, (7, 9, 2), generator=torch.Generator().manual_seed(1)).to(vk), -2.0),
+           x.scatter(2, torch.randint(0, 5, (7, 9, 2), generator=torch.Generator().manual_seed(1)), -2.0), 0)
+    small = (torch.rand(4, 6, generator=g) + 0.5).to(dtype)
+    _close(small.to(vk).prod(), small.float().prod().to(dtype), tol)
+    _close(small.to(vk).prod(1), small.float().prod(1).to(dtype), tol)
+    _close(small.to(vk).prod(0, keepdim=True), small.float().prod(0, keepdim=True).to(dtype), tol)
+    assert torch.equal(xd, xd.clone()) and not torch.equal(xd, xd + 1) and not torch.equal(xd, xd[:3])
