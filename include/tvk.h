@@ -193,6 +193,15 @@ TVK_API int tvk_rng_set_seed(int dev, uint64_t seed);
 TVK_API int tvk_rng_get_state(int dev, uint64_t* seed, uint64_t* offset);
 TVK_API int tvk_rng_set_state(int dev, uint64_t seed, uint64_t offset);
 TVK_API int tvk_rng_reserve(int dev, uint64_t count, uint64_t* seed, uint64_t* offset);
+/* Random fills and dropout on a (seed, offset) pair reserved with tvk_rng_reserve (the reference's random family,
+ * src/api/ops/random.cpp, and native_dropout_vulkan, src/api/ops/dropout.cpp:10-90). Philox4x32-10, four elements per
+ * 128-bit block: a call over n elements consumes (n + 3) / 4 offsets. kind 0: uniform in [a, b); 1: normal(mean a,
+ * std b); 2: Bernoulli(p = a) as 0 / 1 (dtype may be TVK_U8 for a mask). The streams are this library's own: the same
+ * seed gives the same numbers here, not the reference's. tvk_dropout: out = keep ? in / keep_prob : 0, mask = keep. */
+TVK_API int tvk_random_fill(int kind, int dtype, void* out, int64_t n, double a, double b, uint64_t seed, uint64_t offset,
+                            void* stream);
+TVK_API int tvk_dropout(int dtype, void* out, uint8_t* mask, const void* in, int64_t n, double keep_prob, uint64_t seed,
+                        uint64_t offset, void* stream);
 
 /* ------------------------------------------------------------------------- *
  * Dense contraction.
@@ -621,6 +630,23 @@ TVK_API int tvk_conv2d_backward_weight(const tvk_conv2d_desc* desc, void* dw, co
  * tvk_conv2d_workspace_size. The results are bit-identical to the two separate calls. */
 TVK_API int tvk_conv2d_backward(const tvk_conv2d_desc* desc, void* dx, void* dw, const void* dy, const void* x, const void* w,
                                 void* workspace, uint64_t workspace_bytes, void* stream);
+
+/* 2-D max and average pooling on NCHW planes (src/api/ops/pool.cpp: max_pool2d_with_indices, avg_pool2d and their
+ * backward entries). planes = n * c; x, dx: [planes, h, w]; y, dy, indices: [planes, ho, wo], ho / wo given by the caller
+ * (floor or ceil mode). Max pooling: a NaN in the window wins, ties keep the first element, indices[...] = h * w_in + w
+ * inside the plane; average pooling: the divisor is divisor_override when > 0, else the window's size clipped to the
+ * padded plane (count_include_pad != 0) or to the plane. The backward calls are gathers: deterministic, no atomics. */
+typedef struct tvk_pool2d_desc {
+    int dtype;
+    int64_t planes, h, w, ho, wo;
+    int64_t kh, kw, stride_h, stride_w, pad_h, pad_w, dilation_h, dilation_w;
+    int32_t count_include_pad;
+    int64_t divisor_override;
+} tvk_pool2d_desc;
+TVK_API int tvk_max_pool2d_forward(const tvk_pool2d_desc* desc, void* y, int64_t* indices, const void* x, void* stream);
+TVK_API int tvk_max_pool2d_backward(const tvk_pool2d_desc* desc, void* dx, const void* dy, const int64_t* indices, void* stream);
+TVK_API int tvk_avg_pool2d_forward(const tvk_pool2d_desc* desc, void* y, const void* x, void* stream);
+TVK_API int tvk_avg_pool2d_backward(const tvk_pool2d_desc* desc, void* dx, const void* dy, void* stream);
 
 /* Depthwise 2-D convolution: groups == cin, cout a multiple of cin (one input channel per group). The reference sends
  * these through the same grouped convolution as everything else (convolution_vulkan with groups > 1,

@@ -290,3 +290,99 @@ def test_gather_family_with_gradients(vk, dtype):
     _close(small.to(vk).prod(1), small.float().prod(1).to(dtype), tol)
     _close(small.to(vk).prod(0, keepdim=True), small.float().prod(0, keepdim=True).to(dtype), tol)
     assert torch.equal(xd, xd.clone()) and not torch.equal(xd, xd + 1) and not torch.equal(xd, xd[:3])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("kw", [
+    dict(kernel_size=2), dict(kernel_size=3, stride=2, padding=1), dict(kernel_size=(3, 2), stride=(2, 1), padding=(1, 0)),
+    dict(kernel_size=3, stride=2, padding=1, ceil_mode=True), dict(kernel_size=3, stride=1, padding=1, dilation=2),
+])
+def test_max_pool2d(vk, dtype, kw):
+    """max_pool2d with indices and its gradient against ATen CPU: same values, same argmax positions (first maximum in
+    row-major order), the gradient routed to exactly those positions."""
+    g = torch.Generator().manual_seed(13)
+    x = torch.randn(3, 5, 13, 11, generator=g).to(dtype)
+    xd, xc = x.to(vk).requires_grad_(), x.float().requires_grad_()
+    (yd, idd), (yc, idc) = F.max_pool2d(xd, return_indices=True, **kw), F.max_pool2d(xc, return_indices=True, **kw)
+    _close(yd.float(), yc, 0)
+    _close(idd, idc, 0)
+    gy = torch.randn(yc.shape, generator=g).to(dtype)
+    yd.backward(gy.to(vk)); yc.backward(gy.float())
+    _close(xd.grad.float(), xc.grad, 1e-6 if dtype == torch.float32 else 2e-3)
+    # 3-D input, and a channels-last input
+    _close(F.max_pool2d(x[0].to(vk), **kw).float(), F.max_pool2d(x[0].float(), **kw), 0)
+    _close(F.max_pool2d(x.to(vk).contiguous(memory_format=torch.channels_last), **kw).float(), F.max_pool2d(x.float(), **kw), 0)
+    xn = x.clone(); xn[0, 0, 4, 4] = float("nan")
+    _close(F.max_pool2d(xn.to(vk), **kw).float(), F.max_pool2d(xn.float(), **kw), 0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("kw", [
+    dict(kernel_size=2), dict(kernel_size=3, stride=2, padding=1), dict(kernel_size=3, stride=2, padding=1, count_include_pad=False),
+    dict(kernel_size=(3, 2), stride=(2, 1), padding=(1, 1), ceil_mode=True), dict(kernel_size=3, stride=2, padding=1, ceil_mode=True, count_include_pad=False),
+    dict(kernel_size=2, divisor_override=3),
+])
+def test_avg_pool2d(vk, dtype, kw):
+    g = torch.Generator().manual_seed(14)
+    x = torch.randn(2, 6, 12, 9, generator=g).to(dtype)
+    xd, xc = x.to(vk).requires_grad_(), x.double().requires_grad_()
+    yd, yc = F.avg_pool2d(xd, **kw), F.avg_pool2d(xc, **kw)
+    tol = 1e-6 if dtype == torch.float32 else 1e-2
+    _close(yd.double(), yc, tol)
+    gy = torch.randn(yc.shape, generator=g).to(dtype)
+    yd.backward(gy.to(vk)); yc.backward(gy.double())
+    _close(xd.grad.double(), xc.grad, tol)
+
+
+def test_random_fills_and_dropout(vk):
+    """uniform / normal / Bernoulli fills and dropout (src/api/ops/random.cpp, dropout.cpp): the distributions' moments
+    within a few standard errors, reproducible under a seed, advancing between calls; dropout's mask, scale and gradient."""
+    import torchvulkan
+
+    n = 1 << 20
+    torchvulkan.manual_seed(1234)
+    u = torch.rand(n, device=vk).cpu()
+    assert 0.0 <= float(u.min()) and float(u.max()) < 1.0
+    assert abs(float(u.mean()) - 0.5) < 2e-3 and abs(float(u.var()) - 1 / 12) < 2e-3
+    z = torch.randn(n, device=vk).cpu()
+    assert abs(float(z.mean())) < 5e-3 and abs(float(z.std()) - 1.0) < 5e-3
+    assert abs(float((z.abs() < 1.0).float().mean()) - 0.6827) < 3e-3 and float(z.abs().max()) > 4.0
+    assert abs(float(torch.corrcoef(torch.stack([z[:-1], z[1:]]))[0, 1])) < 5e-3
+    w = torch.empty(300, 700, device=vk).uniform_(-2.0, 3.0).cpu()
+    assert -2.0 <= float(w.min()) and float(w.max()) < 3.0 and abs(float(w.mean()) - 0.5) < 2e-2
+    nrm = torch.empty(n, device=vk).normal_(3.0, 0.5).cpu()
+    assert abs(float(nrm.mean()) - 3.0) < 3e-3 and abs(float(nrm.std()) - 0.5) < 3e-3
+    h = torch.randn(n, device=vk, dtype=torch.float16).cpu().float()
+    assert abs(float(h.mean())) < 5e-3 and abs(float(h.std()) - 1.0) < 5e-3
+    b = torch.empty(n, device=vk).bernoulli_(0.3).cpu()
+    assert set(b.unique().tolist()) == {0.0, 1.0} and abs(float(b.mean()) - 0.3) < 2e-3
+    # the same seed replays the stream; the stream advances between calls; an odd length is filled to its end
+    torchvulkan.manual_seed(7)
+    a1, a2 = torch.randn(1001, device=vk).cpu(), torch.randn(1001, device=vk).cpu()
+    torchvulkan.manual_seed(7)
+    b1 = torch.randn(1001, device=vk).cpu()
+    assert torch.equal(a1, b1) and not torch.equal(a1, a2) and bool(a1.isfinite().all())
+    torch.manual_seed(7)                                                    # torch.manual_seed seeds every device's generator
+    assert torch.equal(torch.randn(1001, device=vk).cpu(), a1)
+    # nn.init and a strided target
+    lin = torch.nn.Linear(64, 32).to(vk)
+    torch.nn.init.kaiming_uniform_(lin.weight); torch.nn.init.normal_(lin.bias, std=0.02)
+    assert float(lin.weight.detach().cpu().abs().max()) > 0 and abs(float(lin.bias.detach().cpu().std()) - 0.02) < 0.01
+    t = torch.zeros(64, 64, device=vk)
+    t.t()[:, :3].normal_()
+    assert float(t.cpu()[:3].abs().sum()) > 0 and float(t.cpu()[3:].abs().sum()) == 0
+    # dropout
+    x = torch.randn(512, 1024)
+    xd = x.to(vk).requires_grad_()
+    y = F.dropout(xd, 0.25, training=True)
+    yc = y.detach().cpu()
+    kept = yc != 0
+    assert abs(float(kept.float().mean()) - 0.75) < 3e-3
+    assert torch.allclose(yc[kept], x[kept] / 0.75, rtol=1e-6, atol=1e-7)
+    y.backward(torch.ones_like(y))
+    assert torch.allclose(xd.grad.cpu(), kept.float() / 0.75, rtol=1e-6, atol=0)
+    assert torch.equal(F.dropout(xd, 0.25, training=False).detach().cpu(), x)
+    drop = torch.nn.Dropout(0.5)
+    yh = drop(x.half().to(vk)).cpu()
+    assert abs(float((yh != 0).float().mean()) - 0.5) < 3e-3 and torch.equal(yh[yh != 0], (x.half() * 2)[yh != 0])
+    assert float(F.dropout(xd, 1.0, training=True).detach().abs().sum().cpu()) == 0.0

@@ -1,0 +1,79 @@
+// Random fills and dropout on the "vulkan" device.
+//
+// Counterparts in the reference: uniform_ / normal_ / bernoulli_ (src/api/ops/random.cpp), native_dropout and its backward
+// (src/api/ops/dropout.cpp:10-120). Every launch reserves its offsets from the device's generator state
+// (tvk_rng_reserve; torch.manual_seed and torchvulkan.manual_seed reach tvk_rng_set_seed through the generator), so the
+// same seed replays the same stream. torch.randn / rand / rand_like / dropout / nn.init.* are composites over these.
+// A generator object passed by the caller shares the state of its device.
+#include "common.h"
+
+namespace tvk_aten {
+namespace {
+
+enum { kUniform = 0, kNormal = 1, kBernoulli = 2 };
+
+at::Tensor& random_fill_(at::Tensor& self, int kind, double a, double b, const char* name) {
+    const at::ScalarType st = self.scalar_type();
+    const bool mask = st == at::kBool || st == at::kByte;
+    if (!is_hot_float(st) && !(mask && kind == kBernoulli)) TVK_NOT_IMPLEMENTED(name, " for dtype ", st, " on the vulkan device");
+    if (self.numel() == 0) return self;
+    at::Tensor target = self.is_non_overlapping_and_dense() ? self : empty_vulkan(self.sizes(), st, self.device());
+    DeviceScope scope(self);
+    uint64_t seed = 0, offset = 0;
+    TVK_CALL(tvk_rng_reserve(scope.device, (uint64_t)((target.numel() + 3) / 4), &seed, &offset));
+    TVK_CALL(tvk_random_fill(kind, to_tvk_dtype(st), target.data_ptr(), target.numel(), a, b, seed, offset, scope.stream));
+    if (!target.is_same(self)) self.copy_(target);
+    return self;
+}
+at::Tensor& uniform_(at::Tensor& self, double from, double to, c10::optional<at::Generator>) {
+    TORCH_CHECK(from <= to, "uniform_ expects to return a [from, to) range, but found from=", from, " > to=", to);
+    return random_fill_(self, kUniform, from, to, "uniform_");
+}
+at::Tensor& normal_(at::Tensor& self, double mean, double std, c10::optional<at::Generator>) {
+    TORCH_CHECK(std >= 0.0, "normal expects std >= 0.0, but found std ", std);
+    return random_fill_(self, kNormal, mean, std, "normal_");
+}
+at::Tensor& bernoulli_float_(at::Tensor& self, double p, c10::optional<at::Generator>) {
+    TORCH_CHECK(p >= 0.0 && p <= 1.0, "bernoulli_ expects p to be in [0, 1], but got p=", p);
+    return random_fill_(self, kBernoulli, p, 0.0, "bernoulli_");
+}
+at::Tensor bernoulli_p(const at::Tensor& self, double p, c10::optional<at::Generator> gen) {
+    at::Tensor out = at::empty_like(self);
+    return bernoulli_float_(out, p, gen);
+}
+
+std::tuple<at::Tensor, at::Tensor> native_dropout(const at::Tensor& input, double p, c10::optional<bool> train) {
+    if (input.numel() == 0) return {input, at::empty_like(input, input.options().dtype(at::kBool))};
+    if (train.has_value() && !*train) {
+        at::Tensor ones = at::empty_like(input, input.options().dtype(at::kBool));
+        ones.fill_(true);
+        return {input.clone(), ones};
+    }
+    TORCH_CHECK(p >= 0.0 && p <= 1.0, "dropout probability has to be between 0 and 1, but got ", p);
+    if (!is_hot_float(input.scalar_type())) TVK_NOT_IMPLEMENTED("dropout for dtype ", input.scalar_type(), " on the vulkan device");
+    // elementwise: any dense layout runs as it is, and the outputs keep it
+    at::Tensor src = input.is_non_overlapping_and_dense() ? input : contiguous_vulkan(input);
+    at::Tensor out = at::empty_strided(src.sizes(), src.strides(), src.options());
+    at::Tensor mask = at::empty_strided(src.sizes(), src.strides(), src.options().dtype(at::kBool));
+    DeviceScope scope(src);
+    uint64_t seed = 0, offset = 0;
+    TVK_CALL(tvk_rng_reserve(scope.device, (uint64_t)((src.numel() + 3) / 4), &seed, &offset));
+    TVK_CALL(tvk_dropout(to_tvk_dtype(src.scalar_type()), out.data_ptr(), (uint8_t*)mask.data_ptr(), src.data_ptr(), src.numel(), 1.0 - p, seed, offset, scope.stream));
+    return {out, mask};
+}
+at::Tensor native_dropout_backward(const at::Tensor& grad, const at::Tensor& mask, double scale) {
+    return grad * mask.to(grad.scalar_type()) * scale;
+}
+
+}  // namespace
+
+TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+    m.impl("uniform_", &uniform_);
+    m.impl("normal_", &normal_);
+    m.impl("bernoulli_.float", &bernoulli_float_);
+    m.impl("bernoulli.p", &bernoulli_p);
+    m.impl("native_dropout", &native_dropout);
+    m.impl("native_dropout_backward", &native_dropout_backward);
+}
+
+}  // namespace tvk_aten
