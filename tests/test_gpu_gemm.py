@@ -134,7 +134,6 @@ def test_tc_block_choice_large_product(cuda):
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("m,n,k,ta,tb", [(256, 10, 8192, False, True),      # classifier head: split-K on the tensor cores
-                                         (256, 8192, 10, False, False),     # its input gradient: A's 20-byte row pitch is repacked
                                          (10, 8192, 256, True, False),      # its weight gradient: A^T is repacked
                                          (12, 4096, 250, True, True),       # both operands repacked
                                          (300, 7, 4096, False, True)])
@@ -151,6 +150,39 @@ def test_skinny_shapes_take_the_tensor_core_path(cuda, dtype, m, n, k, ta, tb):
     ops().gemm(adev, bdev, bias=bias.to(cuda), alpha=0.5, beta=2.0, act="relu", out=out)
     ops().check_device_status()
     check(out, oracle.gemm(f64(a), f64(b), f64(bias), 0.5, 2.0, "relu"), dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("m,n,k,ta", [(256, 8192, 10, False),      # the input gradient of a classifier head
+                                      (256, 8192, 10, True), (1, 512, 1, False), (5, 1032, 16, False), (300, 4096, 7, True), (9, 520, 3, False)])
+def test_small_k_products_run_on_the_output_bound_kernel(cuda, dtype, m, n, k, ta):
+    """k <= 16 against a wide B with contiguous rows: no contraction to speak of, the product is bound by writing C. One
+    CUDA-core launch applies alpha, bias, the activation and the activation-gradient operand (the mm + gelu_backward
+    pair of a classifier head's input gradient) in registers."""
+    a, b = operand(m, k, dtype, 91, ta), operand(k, n, dtype, 92, False)
+    bias = cpu_randn(n, dtype, 93)
+    adev = torch.empty_strided(a.shape, a.stride(), dtype=dtype, device=cuda).copy_(a)
+    bdev = b.to(cuda)
+    out = torch.full((m, n), float("nan"), dtype=dtype, device=cuda)
+    assert ops().gemm_path(adev, bdev, out) == 2
+    ops().gemm(adev, bdev, bias=bias.to(cuda), alpha=0.5, beta=2.0, act="relu", out=out)
+    ops().check_device_status()
+    check(out, oracle.gemm(f64(a), f64(b), f64(bias), 0.5, 2.0, "relu"), dtype)
+    x = cpu_randn((m, n), dtype, 94)
+    for aux_op, back in (("gelu_backward", oracle.gelu_backward), ("relu_backward", lambda g, t: np.where(t > 0, g, 0.0))):
+        out = torch.full((m, n), float("nan"), dtype=dtype, device=cuda)
+        if dtype == torch.float32:
+            continue                                     # the activation-gradient operand is a half-type feature of the product
+        assert ops().gemm_path(adev, bdev, out, aux=x.to(cuda), aux_op=aux_op) == 2
+        ops().gemm(adev, bdev, alpha=0.25, out=out, aux=x.to(cuda), aux_op=aux_op)
+        ops().check_device_status()
+        check(out, back(oracle.gemm(f64(a), f64(b), None, 0.25), f64(x)), dtype)
+    # a column-major B is not this kernel's case
+    bt = operand(k, n, dtype, 92, True)
+    btdev = torch.empty_strided(bt.shape, bt.stride(), dtype=dtype, device=cuda).copy_(bt)
+    out = torch.full((m, n), float("nan"), dtype=dtype, device=cuda)
+    ops().gemm(adev, btdev, out=out)
+    check(out, oracle.gemm(f64(a), f64(bt), None, 1.0), dtype)
 
 
 def test_skinny_n_batched(cuda):

@@ -344,6 +344,69 @@ static int plan_splits(int64_t batch, int64_t m, int64_t n, int64_t k, int64_t* 
     return (int)splits;
 }
 
+// k <= 16, B rows contiguous along n (the input gradient of a classifier head: dY [m, 10] @ W [10, n]; a rank-k update):
+// there is no contraction to speak of, the product is bound by writing C (and reading aux). A thread owns one 16-byte
+// packet of columns for kSmallKRows rows: it walks the k rows of B once (each packet of B is used for all its rows), the
+// m x k factors of A sit in shared memory and are read as broadcasts. alpha, bias, the activation and the
+// activation-gradient operand (aux) are applied in registers: C = act((alpha * A @ B + beta * bias) * act'(aux)).
+constexpr int kSmallKRows = 4, kSmallKMax = 16;
+template <typename T>
+__global__ void __launch_bounds__(256) small_k_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C, const T* __restrict__ bias, Params p) {
+    constexpr int N = Vec16<T>::N;
+    constexpr int R = kSmallKRows;
+    __shared__ float As[R][kSmallKMax];
+    const int64_t row0 = (int64_t)blockIdx.y * R;
+    const int64_t col = ((int64_t)blockIdx.x * 256 + threadIdx.x) * N;
+    const bool live = col < p.n;
+    // every load this thread needs is issued before anything waits on one: the k packets of B, then the aux packets
+    Vec16<T> vb[kSmallKMax], aux[R];
+#pragma unroll
+    for (int kk = 0; kk < kSmallKMax; ++kk)
+        if (live && kk < p.k) vb[kk] = load16(B + kk * p.b_rs + col);
+    if (p.aux_op && live) {
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+            if (row0 + r < p.m) aux[r] = load16_stream((const T*)p.aux + (row0 + r) * p.aux_rs + col);
+    }
+    if (threadIdx.x < R * kSmallKMax) {
+        const int r = threadIdx.x / kSmallKMax, kk = threadIdx.x % kSmallKMax;
+        As[r][kk] = (row0 + r < p.m && kk < p.k) ? to_f32(A[(row0 + r) * p.a_rs + kk * p.a_cs]) : 0.f;
+    }
+    __syncthreads();
+    if (!live) return;
+    float acc[R][N];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int e = 0; e < N; ++e) acc[r][e] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < kSmallKMax; ++kk) {
+        if (kk < p.k) {
+#pragma unroll
+            for (int e = 0; e < N; ++e) {
+                const float fb = to_f32(vb[kk].v[e]);
+#pragma unroll
+                for (int r = 0; r < R; ++r) acc[r][e] = fmaf(As[r][kk], fb, acc[r][e]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int64_t row = row0 + r;
+        if (row < p.m) {
+            Vec16<T> out;
+#pragma unroll
+            for (int e = 0; e < N; ++e) {
+                float v = p.alpha * acc[r][e];
+                if (bias) v += p.beta * to_f32(bias[row * p.bias_rs + (col + e) * p.bias_cs]);
+                if (p.aux_op) v = tc::aux_apply(v, to_f32(aux[r].v[e]), p.aux_op);
+                out.v[e] = from_f32<T>(apply_act(v, p.act));
+            }
+            store16(C + row * p.c_rs + col, out);
+        }
+    }
+}
+
 }  // namespace simt
 
 // =====================================================================================
@@ -633,7 +696,10 @@ static Repack plan_repack(const tvk_gemm_desc* d) {
     return r;
 }
 
+static bool small_k_ok(const tvk_gemm_desc* d);
+
 static int choose_path(const tvk_gemm_desc* d) {
+    if (small_k_ok(d)) return 2;                                          // output-bound: a CUDA-core kernel that also takes aux
     if (d->c_f32 && d->dtype != TVK_F32) return tc_eligible(d) ? 1 : 0;   // mixed output exists on the tensor-core path only
     if (d->n_peer_c > 0) return tc_eligible(d) ? 1 : 0;                   // so do the pushed peer copies
     if (fused_epilogue(d)) {                                              // the fused epilogues exist on the tensor-core path only
@@ -653,6 +719,29 @@ static int choose_path(const tvk_gemm_desc* d) {
     // Very skinny outputs leave the 128-row MMA mostly idle: only where the launch still fills the GPU
     if ((d->m < 32 || d->n < 32) && !skinny_tc_worthwhile(d)) return 2;
     return 1;
+}
+
+// the small-k kernel: k of at most 16, one batch, B and C (and aux) rows contiguous and addressable in 16-byte packets
+static bool small_k_ok(const tvk_gemm_desc* d) {
+    const int64_t es = (int64_t)dtype_size(d->dtype), N = 16 / es;
+    if (d->k < 1 || d->k > simt::kSmallKMax || d->batch != 1 || d->n < 512 || d->n % N != 0 || d->m < 1) return false;
+    if (d->c2 || d->c_f32 || d->n_peer_c > 0 || d->force_path == 1) return false;
+    if (d->b_cs != 1 || !aligned16(d->b) || (d->b_rs * es) % 16 != 0 || !aligned16(d->c) || (d->c_rs * es) % 16 != 0) return false;
+    if (d->aux_op != TVK_AUX_NONE && (!d->aux || !aligned16(d->aux) || (d->aux_rs * es) % 16 != 0)) return false;
+    return (d->m + simt::kSmallKRows - 1) / simt::kSmallKRows <= 65535;
+}
+static int run_small_k(const tvk_gemm_desc* d, cudaStream_t s) {
+    simt::Params p = {};
+    p.m = d->m; p.n = d->n; p.k = d->k;
+    p.a_rs = d->a_rs; p.a_cs = d->a_cs; p.b_rs = d->b_rs; p.b_cs = d->b_cs;
+    p.c_rs = d->c_rs;
+    p.bias_rs = d->bias_rs; p.bias_cs = d->bias_cs;
+    p.alpha = d->alpha; p.beta = d->beta; p.act = d->activation;
+    p.aux = d->aux_op ? d->aux : nullptr; p.aux_rs = d->aux_rs; p.aux_op = d->aux_op;
+    const int64_t N = 16 / (int64_t)dtype_size(d->dtype);
+    dim3 grid((unsigned)((d->n / N + 255) / 256), (unsigned)((d->m + simt::kSmallKRows - 1) / simt::kSmallKRows));
+    TVK_DISPATCH_FLOAT(d->dtype, T, (simt::small_k_kernel<T><<<grid, 256, 0, s>>>((const T*)d->a, (const T*)d->b, (T*)d->c, (const T*)d->bias, p)));
+    return launch_status("small-k gemm");
 }
 
 static bool skinny_n_ok(const tvk_gemm_desc* d) {
@@ -1161,6 +1250,7 @@ int tvk_gemm(const tvk_gemm_desc* d, void* workspace, uint64_t workspace_bytes, 
     if (rc) return rc;
     if (d->batch == 0 || d->m == 0 || d->n == 0) return TVK_OK;
     cudaStream_t s = (cudaStream_t)stream;
+    if (small_k_ok(d)) return run_small_k(d, s);
     const int path = (d->k == 0) ? 2 : choose_path(d);
     if (path == 0) return set_error(TVK_ERR_UNSUPPORTED, "tvk_gemm: operands cannot be addressed by the tensor-core path");
     if (path == 2) return run_simt(d, workspace, workspace_bytes, s);

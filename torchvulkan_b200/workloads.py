@@ -112,7 +112,8 @@ class MLPStep:
             d.append(ops.gemm_desc(self.gz[i].t(), act_in, self.gw[i]))                  # wgrad = gz^T @ in
             if i > 0:
                 plain = ops.gemm_desc(self.gz[i], self.w[i], self.gh[i - 1])             # dgrad = gz @ W
-                if self.fused and self.sizes[i + 1] >= 1024:
+                # (a product over a classifier's few outputs takes the output-bound small-k kernel, which applies aux in registers)
+                if self.fused and (self.sizes[i + 1] >= 1024 or self.sizes[i + 1] <= 16):
                     both = ops.gemm_desc(self.gz[i], self.w[i], self.gz[i - 1], aux=self.z[i - 1], aux_op="gelu_backward")   # mm + gelu_backward
                     self._fused_bwd[i] = supported(both)
                     plain = both if self._fused_bwd[i] else plain
