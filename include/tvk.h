@@ -193,15 +193,21 @@ TVK_API int tvk_rng_set_seed(int dev, uint64_t seed);
 TVK_API int tvk_rng_get_state(int dev, uint64_t* seed, uint64_t* offset);
 TVK_API int tvk_rng_set_state(int dev, uint64_t seed, uint64_t offset);
 TVK_API int tvk_rng_reserve(int dev, uint64_t count, uint64_t* seed, uint64_t* offset);
+/* The same for a launch that may be recorded into a graph: outside a capture *device_state is NULL and (seed, offset) are
+ * the reserved values; during tvk_graph_begin_capture .. tvk_graph_end_capture *device_state points at two words of device
+ * memory (seed, base offset) that every tvk_graph_launch refreshes from the generator before the graph runs, and *offset
+ * is relative to that base - so each replay draws new numbers and advances the generator by what the graph consumes. */
+TVK_API int tvk_rng_reserve_state(int dev, uint64_t count, uint64_t* seed, uint64_t* offset, const uint64_t** device_state);
 /* Random fills and dropout on a (seed, offset) pair reserved with tvk_rng_reserve (the reference's random family,
  * src/api/ops/random.cpp, and native_dropout_vulkan, src/api/ops/dropout.cpp:10-90). Philox4x32-10, four elements per
  * 128-bit block: a call over n elements consumes (n + 3) / 4 offsets. kind 0: uniform in [a, b); 1: normal(mean a,
  * std b); 2: Bernoulli(p = a) as 0 / 1 (dtype may be TVK_U8 for a mask). The streams are this library's own: the same
- * seed gives the same numbers here, not the reference's. tvk_dropout: out = keep ? in / keep_prob : 0, mask = keep. */
+ * seed gives the same numbers here, not the reference's. tvk_dropout: out = keep ? in / keep_prob : 0, mask = keep.
+ * device_state: NULL, or the pointer tvk_rng_reserve_state returned (the kernel then reads seed and base offset there). */
 TVK_API int tvk_random_fill(int kind, int dtype, void* out, int64_t n, double a, double b, uint64_t seed, uint64_t offset,
-                            void* stream);
+                            const uint64_t* device_state, void* stream);
 TVK_API int tvk_dropout(int dtype, void* out, uint8_t* mask, const void* in, int64_t n, double keep_prob, uint64_t seed,
-                        uint64_t offset, void* stream);
+                        uint64_t offset, const uint64_t* device_state, void* stream);
 
 /* ------------------------------------------------------------------------- *
  * Dense contraction.

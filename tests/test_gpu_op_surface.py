@@ -386,3 +386,43 @@ def test_random_fills_and_dropout(vk):
     yh = drop(x.half().to(vk)).cpu()
     assert abs(float((yh != 0).float().mean()) - 0.5) < 3e-3 and torch.equal(yh[yh != 0], (x.half() * 2)[yh != 0])
     assert float(F.dropout(xd, 1.0, training=True).detach().abs().sum().cpu()) == 0.0
+
+
+def test_random_launches_inside_a_graph_draw_new_numbers_on_every_replay(vk):
+    """Dropout and random fills recorded into torchvulkan.Graph read the generator state from device memory that every
+    launch of the graph refreshes: replays differ from each other, advance the generator, and repeat under the same seed."""
+    import torchvulkan
+
+    x = torch.ones(256, 512, device=vk)
+    y, noise = torch.empty_like(x), torch.empty(1000, device=vk)
+
+    def work():
+        y.copy_(F.dropout(x, 0.5, training=True))
+        noise.normal_()
+
+    for _ in range(2):
+        work()
+    g = torchvulkan.Graph()
+    with g.capture():
+        work()
+
+    def replays(seed, n=3):
+        torchvulkan.manual_seed(seed)
+        out = []
+        for _ in range(n):
+            g.replay()
+            out.append((y.cpu().clone(), noise.cpu().clone()))
+        return out
+
+    a, b, c = replays(5), replays(5), replays(6)
+    for i in range(3):
+        assert torch.equal(a[i][0], b[i][0]) and torch.equal(a[i][1], b[i][1])           # the same seed replays the same sequence
+        assert not torch.equal(a[i][0], c[i][0])
+        assert abs(float((a[i][0] != 0).float().mean()) - 0.5) < 0.01 and abs(float(a[i][1].std()) - 1.0) < 0.1
+    assert not torch.equal(a[0][0], a[1][0]) and not torch.equal(a[1][0], a[2][0]) and not torch.equal(a[0][1], a[1][1])
+    # an eager launch after the replays continues the stream instead of repeating a replay's numbers
+    torchvulkan.manual_seed(5)
+    g.replay()
+    eager = torch.empty(1000, device=vk).normal_().cpu()
+    assert not torch.equal(eager, a[0][1]) and not torch.equal(eager, a[1][1])
+    g.reset()

@@ -20,8 +20,9 @@ at::Tensor& random_fill_(at::Tensor& self, int kind, double a, double b, const c
     at::Tensor target = self.is_non_overlapping_and_dense() ? self : empty_vulkan(self.sizes(), st, self.device());
     DeviceScope scope(self);
     uint64_t seed = 0, offset = 0;
-    TVK_CALL(tvk_rng_reserve(scope.device, (uint64_t)((target.numel() + 3) / 4), &seed, &offset));
-    TVK_CALL(tvk_random_fill(kind, to_tvk_dtype(st), target.data_ptr(), target.numel(), a, b, seed, offset, scope.stream));
+    const uint64_t* state = nullptr;      // non-null inside a graph capture: the replay's generator state lives on the device
+    TVK_CALL(tvk_rng_reserve_state(scope.device, (uint64_t)((target.numel() + 3) / 4), &seed, &offset, &state));
+    TVK_CALL(tvk_random_fill(kind, to_tvk_dtype(st), target.data_ptr(), target.numel(), a, b, seed, offset, state, scope.stream));
     if (!target.is_same(self)) self.copy_(target);
     return self;
 }
@@ -57,8 +58,10 @@ std::tuple<at::Tensor, at::Tensor> native_dropout(const at::Tensor& input, doubl
     at::Tensor mask = at::empty_strided(src.sizes(), src.strides(), src.options().dtype(at::kBool));
     DeviceScope scope(src);
     uint64_t seed = 0, offset = 0;
-    TVK_CALL(tvk_rng_reserve(scope.device, (uint64_t)((src.numel() + 3) / 4), &seed, &offset));
-    TVK_CALL(tvk_dropout(to_tvk_dtype(src.scalar_type()), out.data_ptr(), (uint8_t*)mask.data_ptr(), src.data_ptr(), src.numel(), 1.0 - p, seed, offset, scope.stream));
+    const uint64_t* state = nullptr;
+    TVK_CALL(tvk_rng_reserve_state(scope.device, (uint64_t)((src.numel() + 3) / 4), &seed, &offset, &state));
+    TVK_CALL(tvk_dropout(to_tvk_dtype(src.scalar_type()), out.data_ptr(), (uint8_t*)mask.data_ptr(), src.data_ptr(), src.numel(), 1.0 - p, seed, offset, state,
+                         scope.stream));
     return {out, mask};
 }
 at::Tensor native_dropout_backward(const at::Tensor& grad, const at::Tensor& mask, double scale) {

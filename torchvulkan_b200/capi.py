@@ -155,8 +155,9 @@ SIGNATURES = {
     "tvk_max_pool2d_backward": (_i, [_p, _p, _p, _p, _p]),
     "tvk_avg_pool2d_forward": (_i, [_p, _p, _p, _p]),
     "tvk_avg_pool2d_backward": (_i, [_p, _p, _p, _p]),
-    "tvk_random_fill": (_i, [_i, _i, _p, _i64, _d, _d, _u64, _u64, _p]),
-    "tvk_dropout": (_i, [_i, _p, _p, _p, _i64, _d, _u64, _u64, _p]),
+    "tvk_random_fill": (_i, [_i, _i, _p, _i64, _d, _d, _u64, _u64, _p, _p]),
+    "tvk_dropout": (_i, [_i, _p, _p, _p, _i64, _d, _u64, _u64, _p, _p]),
+    "tvk_rng_reserve_state": (_i, [_i, _u64, _P(_u64), _P(_u64), _P(_p)]),
     "tvk_gemm_workspace_size": (_i, [_P(GemmDesc), _P(_u64)]),
     "tvk_gemm_splits": (_i, [_P(GemmDesc), _P(C.c_int)]),
     "tvk_gemm": (_i, [_P(GemmDesc), _p, _u64, _p]),

@@ -41,7 +41,9 @@ template <> __device__ __forceinline__ uint8_t rnd_store<uint8_t>(float v) { ret
 
 // kind 0: uniform in [a, b); 1: normal(mean a, std b) by Box-Muller (two words per pair of values); 2: Bernoulli(p = a)
 template <typename T>
-__global__ void __launch_bounds__(256) random_fill_kernel(T* __restrict__ out, int64_t n, int kind, float a, float b, uint64_t seed, uint64_t offset) {
+__global__ void __launch_bounds__(256) random_fill_kernel(T* __restrict__ out, int64_t n, int kind, float a, float b, uint64_t seed, uint64_t offset,
+                                                          const uint64_t* __restrict__ state) {
+    if (state) { seed = state[0]; offset += state[1]; }        // a captured launch: the generator state of this replay
     const Philox gen(seed);
     const int64_t blocks = (n + 3) / 4;
     for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < blocks; q += (int64_t)gridDim.x * blockDim.x) {
@@ -73,7 +75,8 @@ __global__ void __launch_bounds__(256) random_fill_kernel(T* __restrict__ out, i
 // out = keep ? in * scale : 0, mask = keep, keep ~ Bernoulli(keep_prob)
 template <typename T>
 __global__ void __launch_bounds__(256) dropout_kernel(T* __restrict__ out, uint8_t* __restrict__ mask, const T* __restrict__ in, int64_t n, float keep_prob,
-                                                      float scale, uint64_t seed, uint64_t offset) {
+                                                      float scale, uint64_t seed, uint64_t offset, const uint64_t* __restrict__ state) {
+    if (state) { seed = state[0]; offset += state[1]; }
     const Philox gen(seed);
     const int64_t blocks = (n + 3) / 4;
     for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < blocks; q += (int64_t)gridDim.x * blockDim.x) {
@@ -104,7 +107,8 @@ using namespace tvk;
 
 extern "C" {
 
-int tvk_random_fill(int kind, int dtype, void* out, int64_t n, double a, double b, uint64_t seed, uint64_t offset, void* stream) {
+int tvk_random_fill(int kind, int dtype, void* out, int64_t n, double a, double b, uint64_t seed, uint64_t offset, const uint64_t* device_state,
+                    void* stream) {
     if (n == 0) return TVK_OK;
     TVK_REQUIRE(out && n > 0, "tvk_random_fill: null output or negative size");
     TVK_REQUIRE(kind >= 0 && kind <= 2, "tvk_random_fill: unknown distribution %d", kind);
@@ -113,20 +117,21 @@ int tvk_random_fill(int kind, int dtype, void* out, int64_t n, double a, double 
     TVK_REQUIRE(kind != 2 || (a >= 0.0 && a <= 1.0), "tvk_random_fill: Bernoulli needs 0 <= p <= 1");
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == TVK_U8) {
-        random_fill_kernel<uint8_t><<<random_grid(n), 256, 0, s>>>((uint8_t*)out, n, kind, (float)a, (float)b, seed, offset);
+        random_fill_kernel<uint8_t><<<random_grid(n), 256, 0, s>>>((uint8_t*)out, n, kind, (float)a, (float)b, seed, offset, device_state);
     } else {
-        TVK_DISPATCH_FLOAT(dtype, T, (random_fill_kernel<T><<<random_grid(n), 256, 0, s>>>((T*)out, n, kind, (float)a, (float)b, seed, offset)));
+        TVK_DISPATCH_FLOAT(dtype, T, (random_fill_kernel<T><<<random_grid(n), 256, 0, s>>>((T*)out, n, kind, (float)a, (float)b, seed, offset, device_state)));
     }
     return launch_status("random fill");
 }
 
-int tvk_dropout(int dtype, void* out, uint8_t* mask, const void* in, int64_t n, double keep_prob, uint64_t seed, uint64_t offset, void* stream) {
+int tvk_dropout(int dtype, void* out, uint8_t* mask, const void* in, int64_t n, double keep_prob, uint64_t seed, uint64_t offset,
+                const uint64_t* device_state, void* stream) {
     if (n == 0) return TVK_OK;
     TVK_REQUIRE(out && mask && in && n > 0, "tvk_dropout: null pointer or negative size");
     TVK_REQUIRE(keep_prob >= 0.0 && keep_prob <= 1.0, "tvk_dropout: keep probability %f is not in [0, 1]", keep_prob);
     const float scale = keep_prob > 0.0 ? (float)(1.0 / keep_prob) : 0.f;
     cudaStream_t s = (cudaStream_t)stream;
-    TVK_DISPATCH_FLOAT(dtype, T, (dropout_kernel<T><<<random_grid(n), 256, 0, s>>>((T*)out, mask, (const T*)in, n, (float)keep_prob, scale, seed, offset)));
+    TVK_DISPATCH_FLOAT(dtype, T, (dropout_kernel<T><<<random_grid(n), 256, 0, s>>>((T*)out, mask, (const T*)in, n, (float)keep_prob, scale, seed, offset, device_state)));
     return launch_status("dropout");
 }
 

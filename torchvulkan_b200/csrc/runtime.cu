@@ -252,6 +252,12 @@ struct RngState {
     std::mutex mu;
     uint64_t seed = 67280421310721ull;  // torch's default seed constant
     uint64_t offset = 0;
+    // While a graph is being captured the random launches take their (seed, base offset) from these two words of device
+    // memory plus an offset relative to the start of the capture; every launch of the graph first writes the generator's
+    // current seed and offset there and advances the offset by what the graph consumes, so a replay draws new numbers.
+    uint64_t* dev_state = nullptr;
+    bool capturing = false;
+    uint64_t capture_used = 0;
 };
 
 struct Device {
@@ -858,7 +864,13 @@ struct GraphHandle {
     cudaGraphExec_t exec = nullptr;
     GraphPool* pool = nullptr;
     int device = 0;
+    uint64_t rng_used = 0;       // generator offsets one launch of the graph consumes
 };
+
+__global__ void set_rng_state_kernel(uint64_t* state, uint64_t seed, uint64_t offset) {
+    state[0] = seed;
+    state[1] = offset;
+}
 
 int tvk_graph_begin_capture(int dev) {
     Device* d;
@@ -868,10 +880,30 @@ int tvk_graph_begin_capture(int dev) {
     if (rc) return rc;
     rc = d->alloc.begin_capture();
     if (rc) return rc;
+    {
+        std::lock_guard<std::mutex> lock(d->rng.mu);
+        d->rng.capturing = true;
+        d->rng.capture_used = 0;
+    }
     if (g_fake_devices > 0) return TVK_OK;
+    if (!d->rng.dev_state) {
+        DeviceScope scope;
+        rc = scope.enter(dev);
+        if (rc == TVK_OK && cudaMalloc((void**)&d->rng.dev_state, 2 * sizeof(uint64_t)) != cudaSuccess) {
+            cudaGetLastError();
+            d->rng.dev_state = nullptr;
+            rc = set_error(TVK_ERR_OOM, "tvk_graph_begin_capture: no device memory for the generator state");
+        }
+        if (rc) {
+            d->rng.capturing = false;
+            d->alloc.release_pool(d->alloc.end_capture());
+            return rc;
+        }
+    }
     // Relaxed: a cache miss of the allocator may still call cudaMalloc, from this thread or from autograd's
     cudaError_t e = cudaStreamBeginCapture(d->stream, cudaStreamCaptureModeRelaxed);
     if (e != cudaSuccess) {
+        d->rng.capturing = false;
         d->alloc.release_pool(d->alloc.end_capture());
         return set_error(TVK_ERR_CUDA, "cudaStreamBeginCapture failed: %s", cudaGetErrorString(e));
     }
@@ -891,6 +923,12 @@ int tvk_graph_end_capture(int dev, void** graph) {
     GraphHandle* h = new GraphHandle();
     h->pool = pool;
     h->device = dev;
+    {
+        std::lock_guard<std::mutex> lock(d->rng.mu);
+        h->rng_used = d->rng.capture_used;
+        d->rng.capturing = false;
+        d->rng.capture_used = 0;
+    }
     if (g_fake_devices > 0) {
         *graph = h;
         return TVK_OK;
@@ -926,6 +964,16 @@ int tvk_graph_launch(int dev, void* graph) {
     GraphHandle* h = (GraphHandle*)graph;
     if (h->device != dev) return set_error(TVK_ERR_INVALID, "tvk_graph_launch: the graph was captured on device %d, not %d", h->device, dev);
     if (g_fake_devices > 0) return TVK_OK;
+    if (h->rng_used > 0 && d->rng.dev_state) {
+        uint64_t seed, base;
+        {
+            std::lock_guard<std::mutex> lock(d->rng.mu);
+            seed = d->rng.seed;
+            base = d->rng.offset;
+            d->rng.offset += h->rng_used;
+        }
+        set_rng_state_kernel<<<1, 1, 0, d->stream>>>(d->rng.dev_state, seed, base);
+    }
     TVK_CUDA_CHECK(cudaGraphLaunch(h->exec, d->stream));
     return TVK_OK;
 }
@@ -978,6 +1026,25 @@ int tvk_rng_set_state(int dev, uint64_t seed, uint64_t offset) {
     std::lock_guard<std::mutex> lock(d->rng.mu);
     d->rng.seed = seed;
     d->rng.offset = offset;
+    return TVK_OK;
+}
+
+int tvk_rng_reserve_state(int dev, uint64_t count, uint64_t* seed, uint64_t* offset, const uint64_t** device_state) {
+    Device* d;
+    int rc = get_dev(dev, &d);
+    if (rc) return rc;
+    if (!device_state) return set_error(TVK_ERR_INVALID, "tvk_rng_reserve_state: null output");
+    std::lock_guard<std::mutex> lock(d->rng.mu);
+    if (seed) *seed = d->rng.seed;
+    if (d->rng.capturing && d->rng.dev_state) {
+        *device_state = d->rng.dev_state;
+        if (offset) *offset = d->rng.capture_used;          // relative to what the graph's launch writes into device_state
+        d->rng.capture_used += count;
+        return TVK_OK;
+    }
+    *device_state = nullptr;
+    if (offset) *offset = d->rng.offset;
+    d->rng.offset += count;
     return TVK_OK;
 }
 
