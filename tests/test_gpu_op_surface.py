@@ -426,3 +426,41 @@ def test_random_launches_inside_a_graph_draw_new_numbers_on_every_replay(vk):
     eager = torch.empty(1000, device=vk).normal_().cpu()
     assert not torch.equal(eager, a[0][1]) and not torch.equal(eager, a[1][1])
     g.reset()
+
+
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+def test_smooth_l1_huber_and_kl_div(vk, reduction):
+    g = torch.Generator().manual_seed(15)
+    x, t = torch.randn(14, 11, generator=g) * 2, torch.randn(14, 11, generator=g)
+    for fn in (lambda a, b: F.smooth_l1_loss(a, b, reduction=reduction, beta=0.7), lambda a, b: F.smooth_l1_loss(a, b, reduction=reduction, beta=0.0),
+               lambda a, b: F.huber_loss(a, b, reduction=reduction, delta=1.3)):
+        xd, xc = x.to(vk).requires_grad_(), x.clone().requires_grad_()
+        ld, lc = fn(xd, t.to(vk)), fn(xc, t)
+        _close(ld, lc, 1e-5)
+        gy = torch.randn(lc.shape, generator=g)
+        ld.backward(gy.to(vk)); lc.backward(gy)
+        _close(xd.grad, xc.grad, 1e-5)
+    if reduction != "none":
+        kr = "batchmean" if reduction == "mean" else reduction
+        p, q = x.log_softmax(1), t.softmax(1)
+        q[0, :3] = 0
+        _close(F.kl_div(p.to(vk), q.to(vk), reduction=kr), F.kl_div(p, q, reduction=kr), 1e-5)
+    a = torch.tensor([0.0, 0.0, 2.0, 1.5, 0.0]); b = torch.tensor([0.0, float("nan"), 3.0, 0.0, 5.0])
+    _close(torch.xlogy(a.to(vk), b.to(vk)), torch.xlogy(a, b), 1e-6)
+
+
+def test_masked_select_and_printing_a_device_tensor(vk):
+    g = torch.Generator().manual_seed(16)
+    x = torch.randn(7, 9, generator=g)
+    m = torch.rand(7, 9, generator=g) > 0.6
+    _close(x.to(vk).masked_select(m.to(vk)), x.masked_select(m), 0)
+    _close(x.to(vk).masked_select(m[:1].to(vk)), x.masked_select(m[:1]), 0)            # a broadcast mask
+    assert x.to(vk).masked_select(torch.zeros(7, 9, dtype=torch.bool).to(vk)).numel() == 0
+    # repr of floating, half, integer, boolean and gradient-carrying tensors (the formatter runs its statistics on the device)
+    for t in (x, x.half(), (x * 1e4), torch.arange(6), m, torch.tensor(3.5), torch.tensor([float("nan"), float("inf"), 1.0])):
+        s = repr(t.to(vk))
+        assert "vulkan" in s and s.startswith("tensor(")
+    xr = x.to(vk).requires_grad_()
+    assert "requires_grad=True" in repr(xr) and "grad_fn" in repr((xr * 2).sum())
+    squeeze = lambda t: "".join(repr(t).split()).replace(",device='vulkan:0'", "")   # noqa: E731  (the suffix may wrap onto its own line)
+    assert squeeze(x.to(vk)) == squeeze(x)

@@ -54,6 +54,19 @@ def _load_backend():
     torch.Tensor.vulkan = _to_vulkan
     torch.Tensor.is_vulkan = property(lambda self: self.device.type == "vulkan")
     torch.utils.generate_methods_for_privateuse1_backend(for_tensor=False)
+    # The tensor formatter gathers its statistics (min / max of the finite values) on the tensor's device in float64;
+    # this device computes in fp32, fp16 and bf16, so printing uses float32 there, as the reference does for devices
+    # without fp64 (torchvulkan/__init__.py:208-215).
+    import torch._tensor_str as _ts
+
+    _totype = _ts.tensor_totype
+
+    def _vulkan_tensor_totype(t):
+        if t.device.type == "vulkan":
+            return t.to(dtype=torch.float)
+        return _totype(t)
+
+    _ts.tensor_totype = _vulkan_tensor_totype
     _install_pickling(torch)
     return _C
 

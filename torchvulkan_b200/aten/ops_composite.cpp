@@ -209,9 +209,51 @@ at::Tensor mse_loss_backward(const at::Tensor& grad, const at::Tensor& self, con
     return (self - target) * grad * norm;
 }
 
+// ---- smooth-L1 / Huber losses, xlogy (kl_div, binary_cross_entropy) ---------------------------------
+at::Tensor reduce_loss(const at::Tensor& v, int64_t reduction) {
+    if (reduction == at::Reduction::Mean) return v.numel() ? at::mean(v, all_dims(v), false) : v.sum() / 0.0;
+    if (reduction == at::Reduction::Sum) return at::sum(v, all_dims(v), false);
+    return v;
+}
+double loss_norm(const at::Tensor& self, int64_t reduction) { return reduction == at::Reduction::Mean ? 1.0 / (double)std::max<int64_t>(self.numel(), 1) : 1.0; }
+// |d| < beta ? 0.5 d^2 / beta : |d| - 0.5 beta   (beta == 0: the L1 loss)
+at::Tensor smooth_l1_loss(const at::Tensor& self, const at::Tensor& target, int64_t reduction, double beta) {
+    TORCH_CHECK(beta >= 0, "smooth_l1_loss does not support negative values for beta.");
+    at::Tensor d = at::abs(self - target);
+    if (beta == 0) return reduce_loss(d, reduction);
+    return reduce_loss(at::where(at::lt(d, beta), d * d * (0.5 / beta), d - 0.5 * beta), reduction);
+}
+at::Tensor smooth_l1_loss_backward(const at::Tensor& grad, const at::Tensor& self, const at::Tensor& target, int64_t reduction, double beta) {
+    at::Tensor d = self - target;
+    at::Tensor slope = beta == 0 ? at::sign(d) : at::clamp(d * (1.0 / beta), -1.0, 1.0);
+    return slope * grad * loss_norm(self, reduction);
+}
+// |d| <= delta ? 0.5 d^2 : delta (|d| - 0.5 delta)
+at::Tensor huber_loss(const at::Tensor& self, const at::Tensor& target, int64_t reduction, double delta) {
+    TORCH_CHECK(delta > 0, "huber_loss does not support non-positive values for delta.");
+    at::Tensor d = at::abs(self - target);
+    return reduce_loss(at::where(at::le(d, delta), d * d * 0.5, (d - 0.5 * delta) * delta), reduction);
+}
+at::Tensor huber_loss_backward(const at::Tensor& grad, const at::Tensor& self, const at::Tensor& target, int64_t reduction, double delta) {
+    return at::clamp(self - target, -delta, delta) * grad * loss_norm(self, reduction);
+}
+// x * log(y), 0 where x == 0 (whatever y), NaN where y is NaN
+at::Tensor vk_xlogy(const at::Tensor& x, const at::Tensor& y) {
+    at::Tensor zero = at::zeros({}, y.options());
+    at::Tensor r = at::where(at::eq(x, 0), zero, x * at::log(y));
+    return at::where(at::isnan(y), y, r);
+}
+at::Tensor& xlogy_out(const at::Tensor& x, const at::Tensor& y, at::Tensor& out) { return into(out, vk_xlogy(x, y)); }
+
 }  // namespace
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+    m.impl("smooth_l1_loss", &smooth_l1_loss);
+    m.impl("smooth_l1_loss_backward", &smooth_l1_loss_backward);
+    m.impl("huber_loss", &huber_loss);
+    m.impl("huber_loss_backward", &huber_loss_backward);
+    m.impl("xlogy.Tensor", &vk_xlogy);
+    m.impl("xlogy.OutTensor", &xlogy_out);
     m.impl("max", &max_all);
     m.impl("min", &min_all);
     m.impl("max.unary_out", &max_unary_out);

@@ -514,6 +514,7 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     REG_UNARY(m, "round", TVK_U_ROUND);
     REG_UNARY(m, "trunc", TVK_U_TRUNC);
     REG_UNARY(m, "sign", TVK_U_SIGN);
+    REG_UNARY(m, "sgn", TVK_U_SIGN);           // real tensors: sgn is sign (the gradient of abs)
     REG_UNARY(m, "log2", TVK_U_LOG2);
     REG_UNARY(m, "log10", TVK_U_LOG10);
     REG_UNARY(m, "log1p", TVK_U_LOG1P);

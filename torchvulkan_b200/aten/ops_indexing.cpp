@@ -217,6 +217,25 @@ at::Tensor& vk_index_put_impl_(at::Tensor& self, const c10::List<c10::optional<a
     return self;
 }
 
+// ---- masked_select ------------------------------------------------------------------------------
+// The elements of self where mask is true, in row-major order. The output's length depends on the data, so the count is
+// read back (one synchronisation, as on any backend); the selection itself stays on the device: a stable sort of the
+// negated mask lists the selected positions first and in order, and those rows are gathered. (Printing a floating tensor
+// goes through this: torch's formatter selects the finite non-zero values.)
+at::Tensor vk_masked_select(const at::Tensor& self, const at::Tensor& mask) {
+    require_table(self, "masked_select");
+    TORCH_CHECK(mask.scalar_type() == at::kBool, "masked_select: expected BoolTensor for mask");
+    const auto shape = at::infer_size(self.sizes(), mask.sizes());
+    at::Tensor xs = contiguous_vulkan(self.expand(shape)).reshape({-1}), m = contiguous_vulkan(mask.expand(shape)).reshape({-1});
+    if (xs.numel() == 0) return at::empty({0}, self.options());
+    const int64_t count = m.sum().item<int64_t>();
+    if (count == 0) return at::empty({0}, self.options());
+    at::Tensor keys = at::logical_not(m).to(at::kFloat);
+    at::Tensor order = std::get<1>(at::sort(keys, /*stable=*/true, /*dim=*/0, /*descending=*/false));
+    return take_along(xs, 0, order.narrow(0, 0, count));
+}
+at::Tensor& vk_masked_select_out(const at::Tensor& self, const at::Tensor& mask, at::Tensor& out) { return into(out, vk_masked_select(self, mask)); }
+
 // ---- flip, roll --------------------------------------------------------------------------------
 at::Tensor vk_flip(const at::Tensor& self, at::IntArrayRef dims) {
     require_table(self, "flip");
@@ -294,6 +313,8 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("index.Tensor", &vk_index_tensor);
     m.impl("index.Tensor_out", &vk_index_tensor_out);
     m.impl("_index_put_impl_", &vk_index_put_impl_);
+    m.impl("masked_select", &vk_masked_select);
+    m.impl("masked_select.out", &vk_masked_select_out);
     m.impl("flip", &vk_flip);
     m.impl("roll", &vk_roll);
     m.impl("prod", &vk_prod_all);
