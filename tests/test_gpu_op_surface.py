@@ -464,3 +464,28 @@ def test_masked_select_and_printing_a_device_tensor(vk):
     assert "requires_grad=True" in repr(xr) and "grad_fn" in repr((xr * 2).sum())
     squeeze = lambda t: "".join(repr(t).split()).replace(",device='vulkan:0'", "")   # noqa: E731  (the suffix may wrap onto its own line)
     assert squeeze(x.to(vk)) == squeeze(x)
+
+
+def test_multinomial(vk):
+    """torch.multinomial on the device (the sampling step of the reference's language-model example,
+    examples/llm.py:95-99): frequencies follow the probabilities, zero-probability classes are never drawn, sampling
+    without replacement returns distinct classes, the seed reproduces the draw."""
+    import torchvulkan
+
+    torchvulkan.manual_seed(3)
+    p = torch.tensor([[0.0, 0.1, 0.2, 0.0, 0.7, 0.0], [0.5, 0.0, 0.0, 0.5, 0.0, 0.0]])
+    draws = torch.multinomial(p.to(vk), 20000, replacement=True).cpu()
+    assert draws.shape == (2, 20000) and draws.dtype == torch.long
+    for r in range(2):
+        freq = torch.bincount(draws[r], minlength=6).float() / 20000
+        assert float((freq - p[r]).abs().max()) < 0.015 and float(freq[p[r] == 0].sum()) == 0.0
+    one = torch.stack([torch.multinomial(p.to(vk), 1).cpu() for _ in range(200)])
+    assert one.shape == (200, 2, 1) and set(one[:, 1, 0].tolist()) <= {0, 3} and set(one[:, 0, 0].tolist()) <= {1, 2, 4}
+    logits = torch.randn(4, 50)
+    nr = torch.multinomial(logits.softmax(-1).to(vk), 10, replacement=False).cpu()
+    assert nr.shape == (4, 10) and all(len(set(row.tolist())) == 10 for row in nr)
+    assert torch.multinomial(p[0].to(vk), 3, replacement=True).shape == (3,)
+    torchvulkan.manual_seed(11)
+    a = torch.multinomial(logits.softmax(-1).half().to(vk), 5, replacement=True).cpu()
+    torchvulkan.manual_seed(11)
+    assert torch.equal(a, torch.multinomial(logits.softmax(-1).half().to(vk), 5, replacement=True).cpu())

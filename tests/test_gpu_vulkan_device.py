@@ -845,3 +845,82 @@ def test_conv_bn_folding_for_inference_runs_on_the_device(vk):
         pair = dbn(dconv(x.to(vk)))
     close(out, ref, 1e-4)
     close(pair, ref, 1e-4)
+
+
+def test_language_model_script_flow(vk):
+    """What the reference's language-model example does around its model (examples/llm.py:100-135), in fp32 against the same
+    run on ATen CPU: AdamW with its default settings, clip_grad_norm_, loss.item(); then eval(), a sampling loop with
+    torch.multinomial over softmax(logits / temperature), torch.cat of the sampled ids, .tolist()."""
+    from models import Decoder
+
+    def run(device):
+        torch.manual_seed(0)
+        model = Decoder(vocab=64, seq=32, layers=2, width=64, heads=4, kv_heads=2, hidden=96).to(device)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-3, weight_decay=0.1)
+        g = torch.Generator().manual_seed(1)
+        losses, norms = [], []
+        model.train()
+        for _ in range(4):
+            windows = torch.randint(0, 64, (8, 33), generator=g)
+            inputs, targets = windows[:, :-1].to(device), windows[:, 1:].to(device)
+            logits = model(inputs)
+            loss = F.cross_entropy(logits.view(-1, logits.size(-1)), targets.reshape(-1))
+            opt.zero_grad()
+            loss.backward()
+            norms.append(float(torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)))
+            opt.step()
+            losses.append(loss.item())
+        return model, losses, norms
+
+    md, ld, nd = run(vk)
+    mc, lc, nc = run(torch.device("cpu"))
+    assert np.allclose(ld, lc, rtol=2e-4, atol=1e-5), (ld, lc)
+    assert np.allclose(nd, nc, rtol=2e-3), (nd, nc)
+    for pd, pc in zip(md.parameters(), mc.parameters()):
+        assert rel_fro(pd.detach().cpu().double().numpy(), pc.detach().double().numpy()) <= 1e-4
+    md.eval()
+    idx = torch.tensor([[3, 1, 4, 1]], device=vk)
+    assert idx.device.type == "vulkan"
+    with torch.no_grad():
+        for _ in range(6):
+            logits = md(idx[:, -32:])[:, -1] / 0.8
+            idx = torch.cat((idx, torch.multinomial(logits.softmax(-1), 1)), dim=1)
+    sample = idx[0].tolist()
+    assert len(sample) == 10 and sample[:4] == [3, 1, 4, 1] and all(0 <= t < 64 for t in sample)
+
+
+def test_image_classifier_script_flow(vk):
+    """What the reference's convolution example does around its model (examples/conv.py:58-86), in fp32 against ATen CPU:
+    SGD with momentum, Nesterov and weight decay under a OneCycleLR schedule, then eval() and the accuracy count
+    (argmax == targets).sum().item()."""
+    from models import SmallResNet
+
+    def run(device):
+        torch.manual_seed(0)
+        model = SmallResNet(8).to(device)
+        opt = torch.optim.SGD(model.parameters(), lr=0.1, momentum=0.9, nesterov=True, weight_decay=5e-4)
+        sched = torch.optim.lr_scheduler.OneCycleLR(opt, max_lr=0.1, total_steps=4)
+        crit = torch.nn.CrossEntropyLoss()
+        g = torch.Generator().manual_seed(2)
+        losses = []
+        model.train()
+        for _ in range(4):
+            data, targets = torch.randn(16, 3, 16, 16, generator=g), torch.randint(0, 10, (16,), generator=g)
+            loss = crit(model(data.to(device)), targets.to(device))
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+            sched.step()
+            losses.append(loss.item())
+        model.eval()
+        data, targets = torch.randn(64, 3, 16, 16, generator=g), torch.randint(0, 10, (64,), generator=g)
+        with torch.no_grad():
+            out = model(data.to(device))
+            correct = (out.argmax(dim=1) == targets.to(device)).sum().item()
+        return losses, out.cpu(), correct
+
+    ld, od, cd = run(vk)
+    lc, oc, cc = run(torch.device("cpu"))
+    assert np.allclose(ld, lc, rtol=2e-3, atol=1e-4), (ld, lc)
+    assert rel_fro(od.double().numpy(), oc.double().numpy()) <= 2e-2
+    assert isinstance(cd, int) and abs(cd - cc) <= 3

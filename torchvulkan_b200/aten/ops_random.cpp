@@ -68,9 +68,38 @@ at::Tensor native_dropout_backward(const at::Tensor& grad, const at::Tensor& mas
     return grad * mask.to(grad.scalar_type()) * scale;
 }
 
+// Categorical sampling (the generate() loop of a language model: torch.multinomial(probs, 1)), on the device end to end.
+// With replacement (or one sample): inverse CDF - the row's running sum, one uniform number in (0, total] per sample, and
+// the index is the count of prefix sums below it (an exact integer sum). Without replacement: the Gumbel top-k trick,
+// top-k of log p + Gumbel noise.
+at::Tensor multinomial(const at::Tensor& self, int64_t num_samples, bool replacement, c10::optional<at::Generator>) {
+    TORCH_CHECK(self.dim() == 1 || self.dim() == 2, "prob_dist must be 1 or 2 dim");
+    TORCH_CHECK(at::isFloatingType(self.scalar_type()), "multinomial only supports floating-point dtypes for input, got: ", self.scalar_type());
+    const int64_t n = self.size(-1);
+    TORCH_CHECK(num_samples > 0 && n > 0, "cannot sample n_sample <= 0 samples");
+    TORCH_CHECK(replacement || num_samples <= n, "cannot sample n_sample > prob_dist.size(-1) samples without replacement");
+    at::Tensor p = (self.dim() == 1 ? self.unsqueeze(0) : self).to(at::kFloat);
+    const int64_t rows = p.size(0);
+    at::Tensor u = at::empty({rows, num_samples}, p.options());
+    u.uniform_(0.0, 1.0);
+    at::Tensor result;
+    if (replacement || num_samples == 1) {
+        at::Tensor cdf = at::cumsum(p, -1);                                              // [rows, n]
+        at::Tensor total = cdf.narrow(-1, n - 1, 1);                                     // [rows, 1]
+        at::Tensor target = (1.0 - u) * total;                                           // in (0, total]
+        if (n == 1) result = at::zeros({rows, num_samples}, p.options().dtype(at::kLong));
+        else result = at::lt(cdf.narrow(-1, 0, n - 1).unsqueeze(1), target.unsqueeze(-1)).sum(at::IntArrayRef({-1}));   // [rows, samples]
+    } else {
+        at::Tensor gumbel = at::neg(at::log(at::neg(at::log(1.0 - u.narrow(1, 0, 1).expand({rows, n}).clone().uniform_(0.0, 1.0)))));
+        result = std::get<1>(at::topk(at::log(p) + gumbel, num_samples, -1, true, true));
+    }
+    return self.dim() == 1 ? result.squeeze(0) : result;
+}
+
 }  // namespace
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+    m.impl("multinomial", &multinomial);
     m.impl("uniform_", &uniform_);
     m.impl("normal_", &normal_);
     m.impl("bernoulli_.float", &bernoulli_float_);
