@@ -489,3 +489,25 @@ def test_multinomial(vk):
     a = torch.multinomial(logits.softmax(-1).half().to(vk), 5, replacement=True).cpu()
     torchvulkan.manual_seed(11)
     assert torch.equal(a, torch.multinomial(logits.softmax(-1).half().to(vk), 5, replacement=True).cpu())
+
+
+def test_boolean_mask_indexing(vk):
+    g = torch.Generator().manual_seed(18)
+    x = torch.randn(6, 5, 4, generator=g)
+    full, rows = torch.rand(6, 5, 4, generator=g) > 0.5, torch.tensor([True, False, True, True, False, False])
+    mid = torch.rand(6, 5, generator=g) > 0.5
+    for make in (lambda t, m: t[m], ):
+        for m in (full, rows, mid):
+            xd, xc = x.to(vk).requires_grad_(), x.clone().requires_grad_()
+            yd, yc = make(xd, m.to(vk)), make(xc, m)
+            _close(yd, yc, 0)
+            gy = torch.randn(yc.shape, generator=g)
+            yd.backward(gy.to(vk)); yc.backward(gy)
+            _close(xd.grad, xc.grad, 0)
+    _close(x.to(vk)[:, mid[0]], x[:, mid[0]], 0)                              # a mask on the second dimension
+    a, b = x.to(vk).clone(), x.clone()
+    a[a < 0] = 0.0; b[b < 0] = 0.0                                           # the usual in-place clean-up
+    _close(a, b, 0)
+    a[rows.to(vk)] = -1.0; b[rows] = -1.0
+    _close(a, b, 0)
+    assert x.to(vk)[torch.zeros(6, dtype=torch.bool).to(vk)].shape == (0, 5, 4)

@@ -175,14 +175,37 @@ at::Tensor& vk_scatter_value_(at::Tensor& self, int64_t dim, const at::Tensor& i
     return self;
 }
 
-// x[idx]: one Long index tensor at one position, the others absent (basic slices are views taken before the call)
+// Row-major positions of the true entries of a boolean mask, as a Long vector. The count is read back (the length depends
+// on the data: one synchronisation, as on any backend); the selection stays on the device: a stable sort of the negated
+// mask lists the selected positions first and in order.
+at::Tensor selected_positions(const at::Tensor& mask) {
+    at::Tensor m = contiguous_vulkan(mask).reshape({-1});
+    const int64_t count = m.numel() ? m.sum().item<int64_t>() : 0;
+    if (count == 0) return at::empty({0}, mask.options().dtype(at::kLong));
+    at::Tensor order = std::get<1>(at::sort(at::logical_not(m).to(at::kFloat), /*stable=*/true, /*dim=*/0, /*descending=*/false));
+    return order.narrow(0, 0, count);
+}
+// self with the dimensions a mask at position pos covers folded into one
+at::Tensor fold_masked_dims(const at::Tensor& self, int64_t pos, const at::Tensor& mask) {
+    TORCH_CHECK(pos + mask.dim() <= self.dim(), "too many indices for tensor of dimension ", self.dim());
+    std::vector<int64_t> shape;
+    for (int64_t d = 0; d < pos; ++d) shape.push_back(self.size(d));
+    for (int64_t d = 0; d < mask.dim(); ++d)
+        TORCH_CHECK(mask.size(d) == self.size(pos + d), "The shape of the mask ", mask.sizes(), " at index ", d, " does not match the shape of the indexed tensor ", self.sizes(),
+                    " at index ", pos + d);
+    shape.push_back(mask.numel());
+    for (int64_t d = pos + mask.dim(); d < self.dim(); ++d) shape.push_back(self.size(d));
+    return contiguous_vulkan(self).reshape(shape);
+}
+
+// x[idx]: one index tensor at one position, the others absent (basic slices are views taken before the call). A Long index
+// picks slices along its dimension; a boolean mask picks the slices where it is true over the dimensions it covers.
 int64_t single_index_position(const c10::List<c10::optional<at::Tensor>>& indices, at::Tensor* index) {
     int64_t pos = -1;
     for (size_t i = 0; i < indices.size(); ++i) {
         c10::optional<at::Tensor> t = indices.get(i);
         if (!t.has_value() || !t->defined()) continue;
         if (pos >= 0) TVK_NOT_IMPLEMENTED("indexing with more than one index tensor");
-        if (t->scalar_type() == at::kBool || t->scalar_type() == at::kByte) TVK_NOT_IMPLEMENTED("indexing with a boolean mask (use torch.where or masked_fill)");
         pos = (int64_t)i;
         *index = *t;
     }
@@ -193,6 +216,10 @@ at::Tensor vk_index_tensor(const at::Tensor& self, const c10::List<c10::optional
     require_table(self, "index");
     at::Tensor index;
     const int64_t pos = single_index_position(indices, &index);
+    if (index.scalar_type() == at::kBool || index.scalar_type() == at::kByte) {
+        at::Tensor mask = (is_vulkan(index) ? index : index.to(self.device())).to(at::kBool);
+        return take_along(fold_masked_dims(self, pos, mask), pos, selected_positions(mask));
+    }
     index = long_index(index, "index");
     at::Tensor idx = is_vulkan(index) ? index : index.to(self.device());
     // negative indices count from the end
@@ -202,9 +229,28 @@ at::Tensor vk_index_tensor(const at::Tensor& self, const c10::List<c10::optional
 at::Tensor& vk_index_tensor_out(const at::Tensor& self, const c10::List<c10::optional<at::Tensor>>& indices, at::Tensor& out) { return into(out, vk_index_tensor(self, indices)); }
 at::Tensor& vk_index_put_impl_(at::Tensor& self, const c10::List<c10::optional<at::Tensor>>& indices, const at::Tensor& values, bool accumulate, bool) {
     require_table(self, "index_put_");
-    if (!accumulate) TVK_NOT_IMPLEMENTED("index_put_ without accumulate (assignment through an index tensor)");
     at::Tensor index;
     const int64_t pos = single_index_position(indices, &index);
+    if (index.scalar_type() == at::kBool || index.scalar_type() == at::kByte) {
+        at::Tensor mask = (is_vulkan(index) ? index : index.to(self.device())).to(at::kBool);
+        if (!accumulate) {
+            // x[mask] = value with one value: a masked fill (the mask is aligned to the dimensions it covers)
+            if (values.numel() != 1) TVK_NOT_IMPLEMENTED("assignment of more than one value through a boolean mask");
+            std::vector<int64_t> view(self.dim(), 1);
+            TORCH_CHECK(pos + mask.dim() <= self.dim(), "too many indices for tensor of dimension ", self.dim());
+            for (int64_t d = 0; d < mask.dim(); ++d) view[pos + d] = mask.size(d);
+            self.masked_fill_(mask.reshape(view), values.reshape({}).to(self.scalar_type()));
+            return self;
+        }
+        at::Tensor rows = selected_positions(mask);
+        at::Tensor folded = fold_masked_dims(self, pos, mask);
+        std::vector<int64_t> shape(folded.sizes().begin(), folded.sizes().end());
+        shape[pos] = rows.numel();
+        at::Tensor delta = add_along(folded.sizes(), pos, rows, values.to(self.scalar_type()).expand(shape));
+        self.add_(delta.reshape(self.sizes()));
+        return self;
+    }
+    if (!accumulate) TVK_NOT_IMPLEMENTED("index_put_ without accumulate (assignment through an index tensor)");
     index = long_index(index, "index_put_");
     at::Tensor idx = is_vulkan(index) ? index : index.to(self.device());
     idx = at::where(at::lt(idx, 0), idx + self.size(pos), idx);
@@ -218,21 +264,17 @@ at::Tensor& vk_index_put_impl_(at::Tensor& self, const c10::List<c10::optional<a
 }
 
 // ---- masked_select ------------------------------------------------------------------------------
-// The elements of self where mask is true, in row-major order. The output's length depends on the data, so the count is
-// read back (one synchronisation, as on any backend); the selection itself stays on the device: a stable sort of the
-// negated mask lists the selected positions first and in order, and those rows are gathered. (Printing a floating tensor
-// goes through this: torch's formatter selects the finite non-zero values.)
+// The elements of self where mask is true, in row-major order (selected_positions, then a row gather). Printing a floating
+// tensor goes through this: torch's formatter selects the finite non-zero values.
 at::Tensor vk_masked_select(const at::Tensor& self, const at::Tensor& mask) {
     require_table(self, "masked_select");
     TORCH_CHECK(mask.scalar_type() == at::kBool, "masked_select: expected BoolTensor for mask");
     const auto shape = at::infer_size(self.sizes(), mask.sizes());
-    at::Tensor xs = contiguous_vulkan(self.expand(shape)).reshape({-1}), m = contiguous_vulkan(mask.expand(shape)).reshape({-1});
+    at::Tensor xs = contiguous_vulkan(self.expand(shape)).reshape({-1});
     if (xs.numel() == 0) return at::empty({0}, self.options());
-    const int64_t count = m.sum().item<int64_t>();
-    if (count == 0) return at::empty({0}, self.options());
-    at::Tensor keys = at::logical_not(m).to(at::kFloat);
-    at::Tensor order = std::get<1>(at::sort(keys, /*stable=*/true, /*dim=*/0, /*descending=*/false));
-    return take_along(xs, 0, order.narrow(0, 0, count));
+    at::Tensor rows = selected_positions(mask.expand(shape));
+    if (rows.numel() == 0) return at::empty({0}, self.options());
+    return take_along(xs, 0, rows);
 }
 at::Tensor& vk_masked_select_out(const at::Tensor& self, const at::Tensor& mask, at::Tensor& out) { return into(out, vk_masked_select(self, mask)); }
 
