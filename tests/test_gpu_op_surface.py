@@ -511,3 +511,81 @@ def test_boolean_mask_indexing(vk):
     a[rows.to(vk)] = -1.0; b[rows] = -1.0
     _close(a, b, 0)
     assert x.to(vk)[torch.zeros(6, dtype=torch.bool).to(vk)].shape == (0, 5, 4)
+
+
+def test_integer_arithmetic_is_exact(vk):
+    big = 2 ** 40 + 3
+    a = torch.tensor([[7, -7, big, -big, 0, 5], [1, 2, 3, -4, -5, 6]], dtype=torch.int64)
+    b = torch.tensor([[2, 2, 3, 3, 5, -3], [1, -2, 7, 3, -2, 4]], dtype=torch.int64)
+    ad, bd = a.to(vk), b.to(vk)
+    for fn in (torch.floor_divide, torch.remainder, torch.fmod, torch.maximum, torch.minimum, torch.add, torch.sub, torch.mul):
+        _close(fn(ad, bd), fn(a, b), 0)
+        _close(fn(ad.int()[1:], bd.int()[1:]), fn(a.int()[1:], b.int()[1:]), 0)
+    _close(ad // 3, a // 3, 0); _close(ad % 3, a % 3, 0); _close(ad % -3, a % -3, 0)
+    _close(-ad, -a, 0); _close(ad.abs(), a.abs(), 0); _close(ad.clamp(-5, 5), a.clamp(-5, 5), 0); _close(ad.clamp(min=0), a.clamp(min=0), 0)
+    _close(ad.clamp(min=bd), a.clamp(min=b), 0)
+    emb = torch.nn.Embedding(10, 4, padding_idx=0)
+    ids = torch.arange(24).reshape(4, 6)
+    _close(emb.to(vk)(ids.to(vk) % 10), emb.cpu()(ids % 10), 0)
+    x = torch.randn(5, 6)
+    _close(x.to(vk).clamp(min=torch.zeros(6).to(vk), max=torch.ones(6).to(vk)), x.clamp(min=torch.zeros(6), max=torch.ones(6)), 0)
+    _close(torch.lerp(x.to(vk), torch.ones(5, 6).to(vk), torch.rand(5, 6, generator=torch.Generator().manual_seed(1)).to(vk)),
+           torch.lerp(x, torch.ones(5, 6), torch.rand(5, 6, generator=torch.Generator().manual_seed(1))), 1e-6)
+    _close(F.threshold(x.to(vk), 0.1, -2.0), F.threshold(x, 0.1, -2.0), 0)
+    _close(F.hardshrink(x.to(vk), 0.5), F.hardshrink(x, 0.5), 0)
+    _close(F.cosine_similarity(x.to(vk), x.flip(0).to(vk)), F.cosine_similarity(x, x.flip(0)), 1e-6)
+
+
+def test_autocast_and_gradient_scaler(vk):
+    """torch.autocast("vulkan") with torch.amp.GradScaler, the mixed-precision recipe (reference: the AutocastPrivateUse1
+    registration, src/api/registration.cpp:4-21, and the two scaler operators, src/api/decompositions.cpp:1625-1626): linear
+    layers run in fp16 under autocast, the loss in fp32, the step matches the same recipe on ATen CPU in bf16/fp32 loosely and,
+    exactly, the scaler's own rules: unscale, skip on overflow, back off, grow after the interval."""
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.GELU(), torch.nn.Linear(64, 10)).to(vk)
+    ref = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.GELU(), torch.nn.Linear(64, 10))
+    ref.load_state_dict({k: v.cpu() for k, v in model.state_dict().items()})
+    x, y = torch.randn(16, 32), torch.randint(0, 10, (16,))
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    scaler = torch.amp.GradScaler("vulkan", init_scale=1024.0, growth_interval=2)
+    with torch.autocast("vulkan", dtype=torch.float16):
+        h = model[0](x.to(vk))
+        assert h.dtype == torch.float16                                        # the matmul family runs in the lower precision
+        logits = model(x.to(vk))
+        loss = F.cross_entropy(logits, y.to(vk))
+        assert loss.dtype == torch.float32                                     # the loss family runs in fp32
+    loss_ref = F.cross_entropy(ref(x), y)
+    assert abs(loss.item() - loss_ref.item()) < 5e-3
+    opt.zero_grad()
+    scaler.scale(loss).backward()
+    assert float(model[0].weight.grad.abs().max().cpu()) > 1.0                 # gradients carry the scale
+    scaler.unscale_(opt)
+    loss_ref.backward()
+    for p, q in zip(model.parameters(), ref.parameters()):
+        assert rel_fro_t(p.grad.cpu(), q.grad) < 2e-2
+    before = [p.detach().cpu().clone() for p in model.parameters()]
+    scaler.step(opt); scaler.update()
+    assert any(not torch.equal(b, p.detach().cpu()) for b, p in zip(before, model.parameters())) and scaler.get_scale() == 1024.0
+    # second clean step reaches the growth interval: the scale doubles
+    opt.zero_grad()
+    with torch.autocast("vulkan", dtype=torch.float16):
+        loss = F.cross_entropy(model(x.to(vk)), y.to(vk))
+    scaler.scale(loss).backward(); scaler.step(opt); scaler.update()
+    assert scaler.get_scale() == 2048.0
+    # an overflow: the step is skipped and the scale backs off
+    opt.zero_grad()
+    with torch.autocast("vulkan", dtype=torch.float16):
+        loss = F.cross_entropy(model(x.to(vk)), y.to(vk))
+    scaler.scale(loss).backward()
+    model[0].weight.grad[0, 0] = float("inf")
+    before = [p.detach().cpu().clone() for p in model.parameters()]
+    scaler.step(opt); scaler.update()
+    assert all(torch.equal(b, p.detach().cpu()) for b, p in zip(before, model.parameters())) and scaler.get_scale() == 1024.0
+    # bf16 autocast, and ops outside the context are untouched
+    with torch.autocast("vulkan", dtype=torch.bfloat16):
+        assert model(x.to(vk)).dtype == torch.bfloat16
+    assert model(x.to(vk)).dtype == torch.float32
+
+
+def rel_fro_t(a, b):
+    return float((a.double() - b.double()).norm() / b.double().norm())

@@ -55,17 +55,40 @@ void unary_into(int op, const at::Tensor& self, at::Tensor& out, const char* nam
     }
 }
 
+at::Tensor binary_impl(int op, const at::Tensor& a_in, const at::Tensor& b_in, double alpha, at::Tensor out, const char* name, bool integer_ok = false);
+at::Tensor scalar_tensor_like(const at::Scalar& s, const at::Tensor& like);
+// neg and abs of integer tensors ride the exact integer kernels: -x = x * -1, |x| = max(x, -x)
+template <int OP> at::Tensor unary_fn(const at::Tensor& self);
+template <int OP> bool integer_unary(const at::Tensor& self, at::Tensor* result) {
+    const at::ScalarType st = self.scalar_type();
+    // float64 tensors (torch.amp.GradScaler forms its inverse scale as scale.double().reciprocal().float()) are stored in
+    // full width but computed in fp32: this device's kernels compute in fp32, fp16 and bf16
+    if (st == at::kDouble) {
+        *result = unary_fn<OP>(self.to(at::kFloat)).to(at::kDouble);
+        return true;
+    }
+    if (!(st == at::kLong || st == at::kInt) || !(OP == TVK_U_NEG || OP == TVK_U_ABS)) return false;
+    at::Tensor negated = binary_impl(TVK_B_MUL, self, scalar_tensor_like(-1, self), 1.0, {}, "neg", true);
+    *result = OP == TVK_U_NEG ? negated : binary_impl(TVK_B_MAXIMUM, self, negated, 1.0, {}, "abs", true);
+    return true;
+}
 template <int OP> at::Tensor unary_fn(const at::Tensor& self) {
+    at::Tensor r;
+    if (integer_unary<OP>(self, &r)) return r;
     at::Tensor out = alloc_like(self, self.scalar_type());
     unary_into(OP, self, out, "unary op");
     return out;
 }
 template <int OP> at::Tensor& unary_fn_(at::Tensor& self) {
+    at::Tensor r;
+    if (integer_unary<OP>(self, &r)) { self.copy_(r); return self; }
     unary_into(OP, self, self, "unary op");
     return self;
 }
 template <int OP> at::Tensor& unary_out(const at::Tensor& self, at::Tensor& out) {
     if (out.sizes() != self.sizes()) out.resize_(self.sizes());
+    at::Tensor r;
+    if (integer_unary<OP>(self, &r)) { out.copy_(r); return out; }
     unary_into(OP, self, out, "unary op");
     return out;
 }
@@ -87,8 +110,7 @@ at::Tensor& gelu_out(const at::Tensor& self, c10::string_view approximate, at::T
 
 // ---- binary -----------------------------------------------------------------------------
 // out = op(a, b) with alpha. `out` may be undefined (allocate), or an existing tensor (in-place / out=).
-at::Tensor binary_impl(int op, const at::Tensor& a_in, const at::Tensor& b_in, double alpha, at::Tensor out, const char* name,
-                       bool integer_ok = false) {
+at::Tensor binary_impl(int op, const at::Tensor& a_in, const at::Tensor& b_in, double alpha, at::Tensor out, const char* name, bool integer_ok) {
     const at::Tensor& anchor = is_vulkan(a_in) ? a_in : b_in;
     at::ScalarType st = at::result_type(a_in, b_in);
     if (op == TVK_B_DIV && c10::isIntegralType(st, true)) st = c10::typeMetaToScalarType(at::get_default_dtype());
@@ -238,6 +260,14 @@ at::Tensor scalar_binary(int op, const at::Tensor& self, double bs, double alpha
 }
 at::Tensor clamp_impl(const at::Tensor& self, const c10::optional<at::Scalar>& lo, const c10::optional<at::Scalar>& hi, at::Tensor out) {
     TORCH_CHECK(lo.has_value() || hi.has_value(), "torch.clamp: At least one of 'min' or 'max' must not be None");
+    if (self.scalar_type() == at::kLong || self.scalar_type() == at::kInt) {        // exact: maximum then minimum with integer bounds
+        TORCH_CHECK((!lo.has_value() || lo->isIntegral(false)) && (!hi.has_value() || hi->isIntegral(false)), "torchvulkan [NOT IMPLEMENTED]: clamp of an integer tensor to floating bounds");
+        at::Tensor r = self;
+        if (lo.has_value()) r = binary_impl(TVK_B_MAXIMUM, r, scalar_tensor_like(*lo, self), 1.0, {}, "clamp", true);
+        if (hi.has_value()) r = binary_impl(TVK_B_MINIMUM, r, scalar_tensor_like(*hi, self), 1.0, {}, "clamp", true);
+        if (out.defined()) { if (out.sizes() != r.sizes()) out.resize_(r.sizes()); out.copy_(r); return out; }
+        return r;
+    }
     return scalar_binary(TVK_B_CLAMP, self, hi.has_value() ? hi->toDouble() : std::numeric_limits<double>::infinity(),
                          lo.has_value() ? lo->toDouble() : -std::numeric_limits<double>::infinity(), out, "clamp");
 }
@@ -306,6 +336,40 @@ std::tuple<at::Tensor, at::Tensor> log_sigmoid_forward(const at::Tensor& self) {
 }
 at::Tensor log_sigmoid_backward(const at::Tensor& grad, const at::Tensor& self, const at::Tensor&) {
     return binary_impl(TVK_B_LOGSIGMOID_BACKWARD, grad, self, 1.0, {}, "log_sigmoid_backward");
+}
+
+// clamp to tensor bounds: maximum then minimum (NaN in self or a bound propagates, as in ATen)
+at::Tensor clamp_tensor(const at::Tensor& self, const c10::optional<at::Tensor>& lo, const c10::optional<at::Tensor>& hi) {
+    TORCH_CHECK((lo.has_value() && lo->defined()) || (hi.has_value() && hi->defined()), "torch.clamp: At least one of 'min' or 'max' must not be None");
+    at::Tensor r = self;
+    if (lo.has_value() && lo->defined()) r = binary_impl(TVK_B_MAXIMUM, r, *lo, 1.0, {}, "clamp", true);
+    if (hi.has_value() && hi->defined()) r = binary_impl(TVK_B_MINIMUM, r, *hi, 1.0, {}, "clamp", true);
+    return r;
+}
+at::Tensor& clamp_tensor_out(const at::Tensor& self, const c10::optional<at::Tensor>& lo, const c10::optional<at::Tensor>& hi, at::Tensor& out) {
+    at::Tensor r = clamp_tensor(self, lo, hi);
+    if (out.sizes() != r.sizes()) out.resize_(r.sizes());
+    out.copy_(r);
+    return out;
+}
+at::Tensor clamp_min_tensor(const at::Tensor& self, const at::Tensor& lo) { return binary_impl(TVK_B_MAXIMUM, self, lo, 1.0, {}, "clamp_min", true); }
+at::Tensor& clamp_min_tensor_out(const at::Tensor& self, const at::Tensor& lo, at::Tensor& out) { binary_impl(TVK_B_MAXIMUM, self, lo, 1.0, out, "clamp_min", true); return out; }
+at::Tensor clamp_max_tensor(const at::Tensor& self, const at::Tensor& hi) { return binary_impl(TVK_B_MINIMUM, self, hi, 1.0, {}, "clamp_max", true); }
+at::Tensor& clamp_max_tensor_out(const at::Tensor& self, const at::Tensor& hi, at::Tensor& out) { binary_impl(TVK_B_MINIMUM, self, hi, 1.0, out, "clamp_max", true); return out; }
+// threshold(x, t, v) = x > t ? x : v;  hardshrink(x, l) = |x| > l ? x : 0
+at::Tensor vk_threshold(const at::Tensor& self, const at::Scalar& t, const at::Scalar& value) {
+    return at::where(at::gt(self, t), self, at::full({}, value, self.options()));
+}
+at::Tensor& threshold_(at::Tensor& self, const at::Scalar& t, const at::Scalar& value) { self.copy_(vk_threshold(self, t, value)); return self; }
+at::Tensor& threshold_out(const at::Tensor& self, const at::Scalar& t, const at::Scalar& value, at::Tensor& out) {
+    at::Tensor r = vk_threshold(self, t, value);
+    if (out.sizes() != r.sizes()) out.resize_(r.sizes());
+    out.copy_(r);
+    return out;
+}
+at::Tensor hardshrink(const at::Tensor& self, const at::Scalar& lambd) { return at::where(at::gt(at::abs(self), lambd), self, at::zeros({}, self.options())); }
+at::Tensor hardshrink_backward(const at::Tensor& grad, const at::Tensor& self, const at::Scalar& lambd) {
+    return at::where(at::gt(at::abs(self), lambd), grad, at::zeros({}, grad.options()));
 }
 
 // ---- logical ops on boolean tensors ------------------------------------------------------
@@ -403,6 +467,18 @@ at::Tensor& addcdiv_out(const at::Tensor& s, const at::Tensor& t1, const at::Ten
 at::Tensor lerp_scalar(const at::Tensor& s, const at::Tensor& e, const at::Scalar& w) { return ternary_impl(TVK_T_LERP, s, e, nullptr, w.toDouble(), {}, "lerp"); }
 at::Tensor& lerp_scalar_(at::Tensor& s, const at::Tensor& e, const at::Scalar& w) { ternary_impl(TVK_T_LERP, s, e, nullptr, w.toDouble(), s, "lerp_"); return s; }
 at::Tensor& lerp_scalar_out(const at::Tensor& s, const at::Tensor& e, const at::Scalar& w, at::Tensor& out) { ternary_impl(TVK_T_LERP, s, e, nullptr, w.toDouble(), out, "lerp.out"); return out; }
+// lerp with a tensor weight: start + weight * (end - start)
+at::Tensor lerp_tensor(const at::Tensor& s0, const at::Tensor& e, const at::Tensor& w) {
+    at::Tensor d = at::sub(e, s0);
+    return ternary_impl(TVK_T_ADDCMUL, s0, w, &d, 1.0, {}, "lerp");
+}
+at::Tensor& lerp_tensor_(at::Tensor& s0, const at::Tensor& e, const at::Tensor& w) { s0.copy_(lerp_tensor(s0, e, w)); return s0; }
+at::Tensor& lerp_tensor_out(const at::Tensor& s0, const at::Tensor& e, const at::Tensor& w, at::Tensor& out) {
+    at::Tensor r = lerp_tensor(s0, e, w);
+    if (out.sizes() != r.sizes()) out.resize_(r.sizes());
+    out.copy_(r);
+    return out;
+}
 
 at::Tensor where_self(const at::Tensor& cond, const at::Tensor& a_in, const at::Tensor& b_in) {
     TORCH_CHECK(cond.scalar_type() == at::kBool, "where expected condition to be a boolean tensor, but got a tensor with dtype ", cond.scalar_type());
@@ -490,10 +566,10 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("div.Tensor", &bin_fn<TVK_B_DIV, false>);
     m.impl("div_.Tensor", &bin_fn_<TVK_B_DIV, false>);
     m.impl("div.out", &bin_out<TVK_B_DIV, false>);
-    m.impl("maximum", &bin_fn<TVK_B_MAXIMUM, false>);
-    m.impl("maximum.out", &bin_out<TVK_B_MAXIMUM, false>);
-    m.impl("minimum", &bin_fn<TVK_B_MINIMUM, false>);
-    m.impl("minimum.out", &bin_out<TVK_B_MINIMUM, false>);
+    m.impl("maximum", &bin_fn<TVK_B_MAXIMUM, true>);
+    m.impl("maximum.out", &bin_out<TVK_B_MAXIMUM, true>);
+    m.impl("minimum", &bin_fn<TVK_B_MINIMUM, true>);
+    m.impl("minimum.out", &bin_out<TVK_B_MINIMUM, true>);
     m.impl("pow.Tensor_Tensor", &bin_fn<TVK_B_POW, false>);
     m.impl("pow.Tensor_Scalar", &pow_tensor_scalar);
     m.impl("pow.Tensor_Scalar_out", &pow_tensor_scalar_out);
@@ -531,18 +607,18 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     REG_UNARY(m, "hardsigmoid", TVK_U_HARDSIGMOID);
     REG_UNARY(m, "hardswish", TVK_U_HARDSWISH);
     REG_UNARY(m, "mish", TVK_U_MISH);
-    m.impl("fmod.Tensor", &bin_fn<TVK_B_FMOD, false>);
-    m.impl("fmod_.Tensor", &bin_fn_<TVK_B_FMOD, false>);
-    m.impl("fmod.Tensor_out", &bin_out<TVK_B_FMOD, false>);
-    m.impl("remainder.Tensor", &bin_fn<TVK_B_REMAINDER, false>);
-    m.impl("remainder_.Tensor", &bin_fn_<TVK_B_REMAINDER, false>);
-    m.impl("remainder.Tensor_out", &bin_out<TVK_B_REMAINDER, false>);
+    m.impl("fmod.Tensor", &bin_fn<TVK_B_FMOD, true>);
+    m.impl("fmod_.Tensor", &bin_fn_<TVK_B_FMOD, true>);
+    m.impl("fmod.Tensor_out", &bin_out<TVK_B_FMOD, true>);
+    m.impl("remainder.Tensor", &bin_fn<TVK_B_REMAINDER, true>);
+    m.impl("remainder_.Tensor", &bin_fn_<TVK_B_REMAINDER, true>);
+    m.impl("remainder.Tensor_out", &bin_out<TVK_B_REMAINDER, true>);
     m.impl("atan2", &bin_fn<TVK_B_ATAN2, false>);
     m.impl("atan2_", &bin_fn_<TVK_B_ATAN2, false>);
     m.impl("atan2.out", &bin_out<TVK_B_ATAN2, false>);
-    m.impl("floor_divide", &bin_fn<TVK_B_FLOOR_DIVIDE, false>);
-    m.impl("floor_divide_.Tensor", &bin_fn_<TVK_B_FLOOR_DIVIDE, false>);
-    m.impl("floor_divide.out", &bin_out<TVK_B_FLOOR_DIVIDE, false>);
+    m.impl("floor_divide", &bin_fn<TVK_B_FLOOR_DIVIDE, true>);
+    m.impl("floor_divide_.Tensor", &bin_fn_<TVK_B_FLOOR_DIVIDE, true>);
+    m.impl("floor_divide.out", &bin_out<TVK_B_FLOOR_DIVIDE, true>);
     m.impl("clamp", &clamp);
     m.impl("clamp_", &clamp_);
     m.impl("clamp.out", &clamp_out);
@@ -552,6 +628,17 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("clamp_max", &clamp_max);
     m.impl("clamp_max_", &clamp_max_);
     m.impl("clamp_max.out", &clamp_max_out);
+    m.impl("clamp.Tensor", &clamp_tensor);
+    m.impl("clamp.Tensor_out", &clamp_tensor_out);
+    m.impl("clamp_min.Tensor", &clamp_min_tensor);
+    m.impl("clamp_min.Tensor_out", &clamp_min_tensor_out);
+    m.impl("clamp_max.Tensor", &clamp_max_tensor);
+    m.impl("clamp_max.Tensor_out", &clamp_max_tensor_out);
+    m.impl("threshold", &vk_threshold);
+    m.impl("threshold_", &threshold_);
+    m.impl("threshold.out", &threshold_out);
+    m.impl("hardshrink", &hardshrink);
+    m.impl("hardshrink_backward", &hardshrink_backward);
     m.impl("hardtanh", &hardtanh);
     m.impl("hardtanh_", &hardtanh_);
     m.impl("hardtanh.out", &hardtanh_out);
@@ -607,6 +694,9 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     REG_CMP("ge", TVK_C_GE);
 #undef REG_CMP
 
+    m.impl("lerp.Tensor", &lerp_tensor);
+    m.impl("lerp_.Tensor", &lerp_tensor_);
+    m.impl("lerp.Tensor_out", &lerp_tensor_out);
     m.impl("addcmul", &addcmul);
     m.impl("addcmul_", &addcmul_);
     m.impl("addcmul.out", &addcmul_out);

@@ -679,14 +679,39 @@ template <typename F> static int dispatch_compare_op(int op, F&& f) {
     }
 }
 
-// Integer add/sub/mul (counters such as BatchNorm's num_batches_tracked live on the device).
+// Integer arithmetic (counters such as BatchNorm's num_batches_tracked, class indices and position ids live on the
+// device): add / sub / mul, maximum / minimum, floor division and the two remainders, exactly, in the tensor's own width.
+// Division by zero gives 0 (ATen's CUDA kernels leave it undefined; the CPU raises).
+__host__ __device__ inline bool int_op_supported(int op) {
+    return op == TVK_B_ADD || op == TVK_B_SUB || op == TVK_B_MUL || op == TVK_B_MAXIMUM || op == TVK_B_MINIMUM || op == TVK_B_FLOOR_DIVIDE ||
+           op == TVK_B_REMAINDER || op == TVK_B_FMOD;
+}
+template <typename T> __device__ __forceinline__ T int_apply(int op, T x, T y, T alpha) {
+    switch (op) {
+        case TVK_B_ADD: return x + alpha * y;
+        case TVK_B_SUB: return x - alpha * y;
+        case TVK_B_MUL: return x * y;
+        case TVK_B_MAXIMUM: return x > y ? x : y;
+        case TVK_B_MINIMUM: return x < y ? x : y;
+        case TVK_B_FLOOR_DIVIDE: {
+            if (y == 0) return 0;
+            T q = x / y;
+            if ((x % y != 0) && ((x < 0) != (y < 0))) --q;
+            return q;
+        }
+        case TVK_B_REMAINDER: {
+            if (y == 0) return 0;
+            T r = x % y;
+            if (r != 0 && ((r < 0) != (y < 0))) r += y;
+            return r;
+        }
+        default: return y == 0 ? 0 : x % y;      // TVK_B_FMOD: the sign of x
+    }
+}
 template <typename T>
 __global__ void int_binary_kernel(T* out, const T* a, const T* b, T bs, T alpha, int op, int64_t n) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        const T x = a[i], y = b ? b[i] : bs;
-        out[i] = op == TVK_B_ADD ? x + alpha * y : (op == TVK_B_SUB ? x - alpha * y : x * y);
-    }
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) out[i] = int_apply<T>(op, a[i], b ? b[i] : bs, alpha);
 }
 template <typename T>
 __global__ void int_binary_strided_kernel(T* out, const T* a, const T* b, T alpha, int op, IterArgs it) {
@@ -694,8 +719,7 @@ __global__ void int_binary_strided_kernel(T* out, const T* a, const T* b, T alph
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < it.total; i += stride) {
         int64_t off[3];
         iter_offsets<3>(it, i, off);
-        const T x = a[off[1]], y = b[off[2]];
-        out[off[0]] = op == TVK_B_ADD ? x + alpha * y : (op == TVK_B_SUB ? x - alpha * y : x * y);
+        out[off[0]] = int_apply<T>(op, a[off[1]], b[off[2]], alpha);
     }
 }
 
@@ -717,7 +741,7 @@ int tvk_binary(int op, int dtype, void* out, const void* a, const void* b, doubl
     if (n == 0) return TVK_OK;
     TVK_REQUIRE(out && a && n > 0, "tvk_binary: null pointer or negative size");
     cudaStream_t s = (cudaStream_t)stream;
-    if ((dtype == TVK_I64 || dtype == TVK_I32) && (op == TVK_B_ADD || op == TVK_B_SUB || op == TVK_B_MUL)) {
+    if ((dtype == TVK_I64 || dtype == TVK_I32) && int_op_supported(op)) {
         if (dtype == TVK_I64) int_binary_kernel<int64_t><<<scalar_grid(n), 256, 0, s>>>((int64_t*)out, (const int64_t*)a, (const int64_t*)b, (int64_t)b_scalar, (int64_t)alpha, op, n);
         else int_binary_kernel<int32_t><<<scalar_grid(n), 256, 0, s>>>((int32_t*)out, (const int32_t*)a, (const int32_t*)b, (int32_t)b_scalar, (int32_t)alpha, op, n);
         return launch_status("integer binary");
@@ -803,7 +827,7 @@ int tvk_binary_strided(int op, int dtype, void* out, const void* a, const void* 
     if (ia.total == 0) return TVK_OK;
     TVK_REQUIRE(out && a && b, "tvk_binary_strided: null pointer");
     cudaStream_t s = (cudaStream_t)stream;
-    if ((dtype == TVK_I64 || dtype == TVK_I32) && (op == TVK_B_ADD || op == TVK_B_SUB || op == TVK_B_MUL)) {
+    if ((dtype == TVK_I64 || dtype == TVK_I32) && int_op_supported(op)) {
         if (dtype == TVK_I64) int_binary_strided_kernel<int64_t><<<scalar_grid(ia.total), 256, 0, s>>>((int64_t*)out, (const int64_t*)a, (const int64_t*)b, (int64_t)alpha, op, ia);
         else int_binary_strided_kernel<int32_t><<<scalar_grid(ia.total), 256, 0, s>>>((int32_t*)out, (const int32_t*)a, (const int32_t*)b, (int32_t)alpha, op, ia);
         return launch_status("integer binary");
