@@ -42,7 +42,8 @@ UNARY = {
     "isposinf": (torch.isposinf, 1.0), "isneginf": (torch.isneginf, 1.0),
     "clamp": (lambda t: t.clamp(-1.0, 0.5), 2.0), "clamp_min": (lambda t: t.clamp_min(0.25), 2.0), "clamp_max": (lambda t: t.clamp(max=0.25), 2.0),
     "relu6": (F.relu6, 5.0), "hardtanh": (lambda t: F.hardtanh(t, -0.5, 1.5), 2.0), "leaky_relu": (lambda t: F.leaky_relu(t, 0.1), 2.0),
-    "elu": (lambda t: F.elu(t, 1.3), 2.0), "softplus": (lambda t: F.softplus(t, 2.0), 6.0),
+    "elu": (lambda t: F.elu(t, 1.3), 2.0), "softplus": (lambda t: F.softplus(t, 2.0), 6.0), "selu": (F.selu, 2.0), "celu": (lambda t: F.celu(t, 0.7), 2.0),
+    "glu": (lambda t: F.glu(t[:, :-1]), 2.0), "prelu": (lambda t: F.prelu(t, torch.full((1,), 0.2, dtype=t.dtype, device=t.device)), 2.0),
 }
 
 
@@ -61,14 +62,15 @@ def test_unary_surface(vk, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
-@pytest.mark.parametrize("name", ["clamp", "relu6", "hardtanh", "leaky_relu", "elu", "softplus", "hardsigmoid", "hardswish", "mish", "logsigmoid"])
+@pytest.mark.parametrize("name", ["clamp", "relu6", "hardtanh", "leaky_relu", "elu", "softplus", "hardsigmoid", "hardswish", "mish", "logsigmoid", "selu", "celu", "glu", "prelu"])
 def test_activation_gradients(vk, name, dtype):
     fn, spread = UNARY[name]
     g = torch.Generator().manual_seed(4)
     x = (torch.randn(41, 29, generator=g) * spread).to(dtype)
-    gy = torch.randn(41, 29, generator=g).to(dtype)
     xd, xc = x.to(vk).requires_grad_(), x.double().requires_grad_()
-    fn(xd).backward(gy.to(vk)); fn(xc).backward(gy.double())
+    yd, yc = fn(xd), fn(xc)
+    gy = torch.randn(yc.shape, generator=g).to(dtype)
+    yd.backward(gy.to(vk)); yc.backward(gy.double())
     tol = 2e-5 if dtype == torch.float32 else 1e-2
     _close(xd.grad.double(), xc.grad, tol)
 
@@ -589,3 +591,55 @@ def test_autocast_and_gradient_scaler(vk):
 
 def rel_fro_t(a, b):
     return float((a.double() - b.double()).norm() / b.double().norm())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_upsampling_adaptive_pools_bce_and_norms(vk, dtype):
+    g = torch.Generator().manual_seed(19)
+    x = torch.randn(2, 3, 6, 8, generator=g).to(dtype)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+
+    def both(fn):
+        xd, xc = x.to(vk).requires_grad_(), x.double().requires_grad_()
+        yd, yc = fn(xd), fn(xc)
+        _close(yd.double(), yc, tol)
+        gy = torch.randn(yc.shape, generator=g).to(dtype)
+        yd.backward(gy.to(vk)); yc.backward(gy.double())
+        _close(xd.grad.double(), xc.grad, tol)
+
+    both(lambda t: F.interpolate(t, scale_factor=2))
+    both(lambda t: F.interpolate(t, size=(9, 13)))
+    both(lambda t: F.interpolate(t, scale_factor=2, mode="bilinear"))
+    both(lambda t: F.interpolate(t, size=(11, 5), mode="bilinear", align_corners=True))
+    both(lambda t: F.interpolate(t, scale_factor=(1.5, 2.5), mode="bilinear", recompute_scale_factor=False))
+    both(lambda t: F.adaptive_avg_pool2d(t, (3, 2)))
+    both(lambda t: F.adaptive_max_pool2d(t, (2, 4)))
+    both(lambda t: F.pixel_shuffle(t.repeat(1, 4, 1, 1)[:, :4], 2))
+    with pytest.raises(RuntimeError, match="NOT IMPLEMENTED"):
+        F.adaptive_avg_pool2d(x.to(vk), (4, 3))
+    p, t = torch.rand(7, 5, generator=g).clamp(0.02, 0.98), (torch.rand(7, 5, generator=g) > 0.5).float()
+    pd, pc = p.to(vk).requires_grad_(), p.clone().requires_grad_()
+    ld, lc = F.binary_cross_entropy(pd, t.to(vk)), F.binary_cross_entropy(pc, t)
+    _close(ld, lc, 1e-6)
+    ld.backward(); lc.backward()
+    _close(pd.grad, pc.grad, 1e-5)
+    a, b = torch.randn(6, 9, generator=g), torch.randn(6, 9, generator=g)
+    _close(F.pairwise_distance(a.to(vk), b.to(vk)), F.pairwise_distance(a, b), 1e-6)
+    _close(torch.norm(a.to(vk), p=3, dim=1), torch.norm(a, p=3, dim=1), 1e-6)
+    _close(a.to(vk).norm(1), a.norm(1), 1e-6)
+    _close(F.triplet_margin_loss(a.to(vk), b.to(vk), b.flip(0).to(vk)), F.triplet_margin_loss(a, b, b.flip(0)), 1e-6)
+
+
+def test_integer_random_fills_and_permutations(vk):
+    import torchvulkan
+
+    torchvulkan.manual_seed(21)
+    r = torch.randint(3, 11, (20000,), device=vk).cpu()
+    assert r.dtype == torch.long and int(r.min()) == 3 and int(r.max()) == 10
+    freq = torch.bincount(r - 3, minlength=8).float() / 20000
+    assert float((freq - 0.125).abs().max()) < 0.01
+    assert torch.randint(5, (4, 3), device=vk).shape == (4, 3)
+    perm = torch.randperm(1000, device=vk).cpu()
+    assert perm.dtype == torch.long and torch.equal(perm.sort().values, torch.arange(1000)) and not torch.equal(perm, torch.arange(1000))
+    torchvulkan.manual_seed(21)
+    assert torch.equal(torch.randint(3, 11, (20000,), device=vk).cpu(), r)

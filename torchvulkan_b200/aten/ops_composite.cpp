@@ -245,9 +245,175 @@ at::Tensor vk_xlogy(const at::Tensor& x, const at::Tensor& y) {
 }
 at::Tensor& xlogy_out(const at::Tensor& x, const at::Tensor& y, at::Tensor& out) { return into(out, vk_xlogy(x, y)); }
 
+// binary_cross_entropy on probabilities: -(t log x + (1 - t) log(1 - x)), each logarithm clamped at -100 as ATen does
+at::Tensor bce(const at::Tensor& self, const at::Tensor& target, const c10::optional<at::Tensor>& weight, int64_t reduction) {
+    at::Tensor lx = at::clamp_min(at::log(self), -100.0), l1x = at::clamp_min(at::log1p(at::neg(self)), -100.0);
+    at::Tensor v = at::neg(target * lx + (1.0 - target) * l1x);
+    if (weight.has_value() && weight->defined()) v = v * *weight;
+    return reduce_loss(v, reduction);
+}
+at::Tensor bce_backward(const at::Tensor& grad, const at::Tensor& self, const at::Tensor& target, const c10::optional<at::Tensor>& weight, int64_t reduction) {
+    // d/dx = (x - t) / max(x (1 - x), eps)
+    at::Tensor g = (self - target) / at::clamp_min(self * (1.0 - self), 1e-12) * grad * loss_norm(self, reduction);
+    if (weight.has_value() && weight->defined()) g = g * *weight;
+    return g;
+}
+
+// adaptive pooling to an output that divides the input evenly is ordinary pooling with kernel = stride = in / out
+std::array<int64_t, 2> even_windows(const at::Tensor& self, at::IntArrayRef output_size, const char* name) {
+    TORCH_CHECK(output_size.size() == 2 && (self.dim() == 3 || self.dim() == 4), name, ": expected a 3-D or 4-D input and two output sizes");
+    const int64_t H = self.size(-2), W = self.size(-1);
+    if (output_size[0] <= 0 || output_size[1] <= 0 || H % output_size[0] != 0 || W % output_size[1] != 0)
+        TVK_NOT_IMPLEMENTED(name, " to an output size that does not divide the input (", H, " x ", W, " -> ", output_size[0], " x ", output_size[1], ")");
+    return {H / output_size[0], W / output_size[1]};
+}
+at::Tensor adaptive_avg_pool2d(const at::Tensor& self, at::IntArrayRef output_size) {
+    const auto k = even_windows(self, output_size, "adaptive_avg_pool2d");
+    return at::avg_pool2d(self, {k[0], k[1]}, {k[0], k[1]});
+}
+at::Tensor adaptive_avg_pool2d_backward(const at::Tensor& grad, const at::Tensor& self) {
+    const auto k = even_windows(self, {grad.size(-2), grad.size(-1)}, "adaptive_avg_pool2d_backward");
+    return at::avg_pool2d_backward(grad, self, {k[0], k[1]}, {k[0], k[1]}, {0, 0}, false, true, c10::nullopt);
+}
+std::tuple<at::Tensor, at::Tensor> adaptive_max_pool2d(const at::Tensor& self, at::IntArrayRef output_size) {
+    const auto k = even_windows(self, output_size, "adaptive_max_pool2d");
+    return at::max_pool2d_with_indices(self, {k[0], k[1]}, {k[0], k[1]});
+}
+at::Tensor adaptive_max_pool2d_backward(const at::Tensor& grad, const at::Tensor& self, const at::Tensor& indices) {
+    const auto k = even_windows(self, {grad.size(-2), grad.size(-1)}, "adaptive_max_pool2d_backward");
+    return at::max_pool2d_with_indices_backward(grad, self, {k[0], k[1]}, {k[0], k[1]}, {0, 0}, {1, 1}, false, indices);
+}
+
+// prelu with its weight already broadcast to the input (ATen reshapes it before calling the kernel)
+at::Tensor prelu_kernel(const at::Tensor& self, const at::Tensor& weight) { return at::where(at::gt(self, 0), self, weight * self); }
+std::tuple<at::Tensor, at::Tensor> prelu_kernel_backward(const at::Tensor& grad, const at::Tensor& self, const at::Tensor& weight) {
+    at::Tensor pos = at::gt(self, 0), zero = at::zeros({}, grad.options());
+    return {at::where(pos, grad, weight * grad), at::where(pos, zero, self * grad)};
+}
+// glu(x) = a * sigmoid(b) over the two halves of dim
+at::Tensor glu(const at::Tensor& self, int64_t dim) {
+    dim = at::maybe_wrap_dim(dim, self.dim());
+    TORCH_CHECK(self.size(dim) % 2 == 0, "Halving dimension must be even, but dimension ", dim, " is size ", self.size(dim));
+    const int64_t h = self.size(dim) / 2;
+    return self.narrow(dim, 0, h) * at::sigmoid(self.narrow(dim, h, h));
+}
+at::Tensor glu_backward(const at::Tensor& grad, const at::Tensor& self, int64_t dim) {
+    dim = at::maybe_wrap_dim(dim, self.dim());
+    const int64_t h = self.size(dim) / 2;
+    at::Tensor a = self.narrow(dim, 0, h), sg = at::sigmoid(self.narrow(dim, h, h));
+    return at::cat({grad * sg, grad * a * sg * (1.0 - sg)}, dim);
+}
+
+// the norm family of torch.norm / F.pairwise_distance: the vector norm over the given dimensions
+at::Tensor norm_dim(const at::Tensor& self, const c10::optional<at::Scalar>& p, at::IntArrayRef dim, bool keepdim) {
+    return vector_norm(self, p.value_or(2.0), dim, keepdim, c10::nullopt);
+}
+at::Tensor norm_dim_dtype(const at::Tensor& self, const c10::optional<at::Scalar>& p, at::IntArrayRef dim, bool keepdim, at::ScalarType dtype) {
+    return vector_norm(self, p.value_or(2.0), dim, keepdim, dtype);
+}
+at::Tensor norm_scalar(const at::Tensor& self, const at::Scalar& p) { return vector_norm(self, p, c10::nullopt, false, c10::nullopt); }
+at::Tensor norm_dtype(const at::Tensor& self, const c10::optional<at::Scalar>& p, at::ScalarType dtype) { return vector_norm(self, p.value_or(2.0), c10::nullopt, false, dtype); }
+at::Tensor& norm_out(const at::Tensor& self, const c10::optional<at::Scalar>& p, at::IntArrayRef dim, bool keepdim, at::Tensor& out) {
+    return into(out, norm_dim(self, p, dim, keepdim));
+}
+at::Tensor& norm_dtype_out(const at::Tensor& self, const c10::optional<at::Scalar>& p, at::IntArrayRef dim, bool keepdim, at::ScalarType dtype, at::Tensor& out) {
+    return into(out, norm_dim_dtype(self, p, dim, keepdim, dtype));
+}
+
+// ---- nearest and bilinear 2-D upsampling ---------------------------------------------------------------------------
+// Both are separable: rows of the output are rows of the input picked (nearest) or blended (bilinear) by per-axis index
+// and weight vectors, which are computed on the host (a few hundred numbers) exactly as ATen computes them, and applied
+// with index_select and lerp on the device; the gradients are the adjoints (index_add) of the same selections.
+struct AxisMap {
+    at::Tensor i0, i1, w1;      // source indices and the weight of i1 (bilinear); nearest uses i0 only
+};
+double area_scale(int64_t in, int64_t out, bool align_corners, const c10::optional<double>& scale) {
+    if (align_corners) return out > 1 ? (double)(in - 1) / (double)(out - 1) : 0.0;
+    return (scale.has_value() && *scale > 0) ? 1.0 / *scale : (double)in / (double)out;
+}
+AxisMap nearest_axis(int64_t in, int64_t out, const c10::optional<double>& scale, const at::Device& dev) {
+    const float s = (float)((scale.has_value() && *scale > 0) ? 1.0 / *scale : (double)in / (double)out);
+    std::vector<int64_t> idx(out);
+    for (int64_t o = 0; o < out; ++o) idx[o] = std::min<int64_t>((int64_t)std::floor((float)o * s), in - 1);
+    AxisMap m;
+    m.i0 = at::tensor(idx, at::TensorOptions().dtype(at::kLong)).to(dev);
+    return m;
+}
+AxisMap bilinear_axis(int64_t in, int64_t out, bool align_corners, const c10::optional<double>& scale, const at::Device& dev) {
+    const float s = (float)area_scale(in, out, align_corners, scale);
+    std::vector<int64_t> i0(out), i1(out);
+    std::vector<float> w(out);
+    for (int64_t o = 0; o < out; ++o) {
+        float src = align_corners ? s * (float)o : std::max(s * ((float)o + 0.5f) - 0.5f, 0.0f);
+        int64_t lo = std::min<int64_t>((int64_t)src, in - 1);
+        i0[o] = lo;
+        i1[o] = std::min<int64_t>(lo + 1, in - 1);
+        w[o] = std::min(std::max(src - (float)lo, 0.0f), 1.0f);
+    }
+    AxisMap m;
+    m.i0 = at::tensor(i0, at::TensorOptions().dtype(at::kLong)).to(dev);
+    m.i1 = at::tensor(i1, at::TensorOptions().dtype(at::kLong)).to(dev);
+    m.w1 = at::tensor(w, at::TensorOptions().dtype(at::kFloat)).to(dev);
+    return m;
+}
+at::Tensor upsample_nearest2d(const at::Tensor& self, at::IntArrayRef size, c10::optional<double> sh, c10::optional<double> sw) {
+    TORCH_CHECK(self.dim() == 4 && size.size() == 2, "upsample_nearest2d: expected a 4-D input and two output sizes");
+    const AxisMap h = nearest_axis(self.size(2), size[0], sh, self.device()), w = nearest_axis(self.size(3), size[1], sw, self.device());
+    return at::index_select(at::index_select(self, 2, h.i0), 3, w.i0);
+}
+at::Tensor upsample_nearest2d_backward(const at::Tensor& grad, at::IntArrayRef size, at::IntArrayRef input_size, c10::optional<double> sh, c10::optional<double> sw) {
+    const AxisMap h = nearest_axis(input_size[2], size[0], sh, grad.device()), w = nearest_axis(input_size[3], size[1], sw, grad.device());
+    at::Tensor gw = at::zeros({grad.size(0), grad.size(1), grad.size(2), input_size[3]}, grad.options()).index_add(3, w.i0, grad);
+    return at::zeros({grad.size(0), grad.size(1), input_size[2], input_size[3]}, grad.options()).index_add(2, h.i0, gw);
+}
+at::Tensor blend_axis(const at::Tensor& x, int64_t dim, const AxisMap& m) {
+    std::vector<int64_t> view(x.dim(), 1);
+    view[dim] = m.w1.numel();
+    at::Tensor w = m.w1.to(x.scalar_type()).view(view);
+    at::Tensor a = at::index_select(x, dim, m.i0), b = at::index_select(x, dim, m.i1);
+    return a + (b - a) * w;
+}
+at::Tensor blend_axis_backward(const at::Tensor& g, int64_t dim, const AxisMap& m, int64_t in) {
+    std::vector<int64_t> view(g.dim(), 1), shape(g.sizes().begin(), g.sizes().end());
+    view[dim] = m.w1.numel();
+    shape[dim] = in;
+    at::Tensor w = m.w1.to(g.scalar_type()).view(view);
+    return at::zeros(shape, g.options()).index_add(dim, m.i0, g * (1.0 - w)).index_add(dim, m.i1, g * w);
+}
+at::Tensor upsample_bilinear2d(const at::Tensor& self, at::IntArrayRef size, bool align_corners, c10::optional<double> sh, c10::optional<double> sw) {
+    TORCH_CHECK(self.dim() == 4 && size.size() == 2, "upsample_bilinear2d: expected a 4-D input and two output sizes");
+    const AxisMap h = bilinear_axis(self.size(2), size[0], align_corners, sh, self.device()), w = bilinear_axis(self.size(3), size[1], align_corners, sw, self.device());
+    return blend_axis(blend_axis(self, 2, h), 3, w);
+}
+at::Tensor upsample_bilinear2d_backward(const at::Tensor& grad, at::IntArrayRef size, at::IntArrayRef input_size, bool align_corners, c10::optional<double> sh,
+                                        c10::optional<double> sw) {
+    const AxisMap h = bilinear_axis(input_size[2], size[0], align_corners, sh, grad.device()), w = bilinear_axis(input_size[3], size[1], align_corners, sw, grad.device());
+    return blend_axis_backward(blend_axis_backward(grad, 3, w, input_size[3]), 2, h, input_size[2]);
+}
+
 }  // namespace
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+    m.impl("binary_cross_entropy", &bce);
+    m.impl("binary_cross_entropy_backward", &bce_backward);
+    m.impl("_adaptive_avg_pool2d", &adaptive_avg_pool2d);
+    m.impl("_adaptive_avg_pool2d_backward", &adaptive_avg_pool2d_backward);
+    m.impl("adaptive_max_pool2d", &adaptive_max_pool2d);
+    m.impl("adaptive_max_pool2d_backward", &adaptive_max_pool2d_backward);
+    m.impl("_prelu_kernel", &prelu_kernel);
+    m.impl("_prelu_kernel_backward", &prelu_kernel_backward);
+    m.impl("glu", &glu);
+    m.impl("glu_backward", &glu_backward);
+    m.impl("norm.ScalarOpt_dim", &norm_dim);
+    m.impl("norm.ScalarOpt_dim_dtype", &norm_dim_dtype);
+    m.impl("norm.Scalar", &norm_scalar);
+    m.impl("norm.ScalarOpt_dtype", &norm_dtype);
+    m.impl("norm.out", &norm_out);
+    m.impl("norm.dtype_out", &norm_dtype_out);
+    m.impl("upsample_nearest2d", &upsample_nearest2d);
+    m.impl("upsample_nearest2d_backward", &upsample_nearest2d_backward);
+    m.impl("upsample_bilinear2d", &upsample_bilinear2d);
+    m.impl("upsample_bilinear2d_backward", &upsample_bilinear2d_backward);
     m.impl("smooth_l1_loss", &smooth_l1_loss);
     m.impl("smooth_l1_loss_backward", &smooth_l1_loss_backward);
     m.impl("huber_loss", &huber_loss);

@@ -295,29 +295,38 @@ at::Tensor leaky_relu_backward(const at::Tensor& grad, const at::Tensor& self, c
     TORCH_CHECK(!self_is_result || slope.toDouble() > 0.0, "In-place leakyReLu backward calculation is triggered with a negative slope which is not supported.");
     return binary_impl(TVK_B_LEAKY_RELU_BACKWARD, grad, self, slope.toDouble(), {}, "leaky_relu_backward");
 }
-void elu_check(const at::Scalar& scale, const at::Scalar& input_scale) {
-    if (scale.toDouble() != 1.0 || input_scale.toDouble() != 1.0) TVK_NOT_IMPLEMENTED("elu with scale or input_scale other than 1 (selu, celu)");
+// elu(x) = scale * (x > 0 ? x : alpha * (exp(input_scale * x) - 1)). The kernel covers scale = input_scale = 1 (elu); selu and
+// celu, which set the other two, are composed from where / expm1.
+bool plain_elu(const at::Scalar& scale, const at::Scalar& input_scale) { return scale.toDouble() == 1.0 && input_scale.toDouble() == 1.0; }
+at::Tensor elu_general(const at::Tensor& self, const at::Scalar& alpha, const at::Scalar& scale, const at::Scalar& input_scale) {
+    return at::where(at::gt(self, 0), self * scale, at::expm1(self * input_scale) * (alpha.toDouble() * scale.toDouble()));
 }
 at::Tensor elu(const at::Tensor& self, const at::Scalar& alpha, const at::Scalar& scale, const at::Scalar& input_scale) {
-    elu_check(scale, input_scale);
+    if (!plain_elu(scale, input_scale)) return elu_general(self, alpha, scale, input_scale);
     return scalar_binary(TVK_B_ELU, self, 0.0, alpha.toDouble(), {}, "elu");
 }
 at::Tensor& elu_(at::Tensor& self, const at::Scalar& alpha, const at::Scalar& scale, const at::Scalar& input_scale) {
-    elu_check(scale, input_scale);
+    if (!plain_elu(scale, input_scale)) { self.copy_(elu_general(self, alpha, scale, input_scale)); return self; }
     scalar_binary(TVK_B_ELU, self, 0.0, alpha.toDouble(), self, "elu_");
     return self;
 }
 at::Tensor& elu_out(const at::Tensor& self, const at::Scalar& alpha, const at::Scalar& scale, const at::Scalar& input_scale, at::Tensor& out) {
-    elu_check(scale, input_scale);
+    if (!plain_elu(scale, input_scale)) {
+        at::Tensor r = elu_general(self, alpha, scale, input_scale);
+        if (out.sizes() != r.sizes()) out.resize_(r.sizes());
+        out.copy_(r);
+        return out;
+    }
     scalar_binary(TVK_B_ELU, self, 0.0, alpha.toDouble(), out, "elu.out");
     return out;
 }
 at::Tensor elu_backward(const at::Tensor& grad, const at::Scalar& alpha, const at::Scalar& scale, const at::Scalar& input_scale, bool is_result,
                         const at::Tensor& self_or_result) {
-    elu_check(scale, input_scale);
-    // from the result y = alpha * (exp(x) - 1) for x <= 0: dy/dx = y + alpha
-    if (is_result) return at::where(at::gt(self_or_result, 0), grad, grad * (self_or_result + alpha));
-    return binary_impl(TVK_B_ELU_BACKWARD, grad, self_or_result, alpha.toDouble(), {}, "elu_backward");
+    const double a = alpha.toDouble(), sc = scale.toDouble(), is = input_scale.toDouble();
+    // from the result y = scale * alpha * (exp(is * x) - 1) for x <= 0: dy/dx = is * (y + scale * alpha)
+    if (is_result) return at::where(at::gt(self_or_result, 0), grad * sc, grad * (self_or_result + a * sc) * is);
+    if (!plain_elu(scale, input_scale)) return at::where(at::gt(self_or_result, 0), grad * sc, grad * at::exp(self_or_result * is) * (a * sc * is));
+    return binary_impl(TVK_B_ELU_BACKWARD, grad, self_or_result, a, {}, "elu_backward");
 }
 at::Tensor softplus(const at::Tensor& self, const at::Scalar& beta, const at::Scalar& threshold) {
     return scalar_binary(TVK_B_SOFTPLUS, self, threshold.toDouble(), beta.toDouble(), {}, "softplus");

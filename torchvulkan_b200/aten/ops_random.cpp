@@ -96,9 +96,40 @@ at::Tensor multinomial(const at::Tensor& self, int64_t num_samples, bool replace
     return self.dim() == 1 ? result.squeeze(0) : result;
 }
 
+// Integer uniform fills: low + floor(u * (high - low)) with u from the float generator. The range must fit fp32's 24-bit
+// integers (class counts, vocabulary sizes, dataset indices); wider ranges raise.
+at::Tensor& random_range_(at::Tensor& self, int64_t low, int64_t high, const char* name) {
+    TORCH_CHECK(high > low, name, " expects 'from' to be less than 'to', but got from=", low, " >= to=", high);
+    if (high - low > (int64_t(1) << 24)) TVK_NOT_IMPLEMENTED(name, " over a range of more than 2^24 values");
+    at::Tensor u = at::empty(self.sizes(), self.options().dtype(at::kFloat));
+    u.uniform_(0.0, 1.0);
+    at::Tensor v = at::floor(u * (double)(high - low));
+    v = at::clamp_max(v, (double)(high - low - 1)) + (double)low;          // u * range may round up to the range itself
+    self.copy_(v.to(self.scalar_type()));
+    return self;
+}
+at::Tensor& random_from_(at::Tensor& self, int64_t from, c10::optional<int64_t> to, c10::optional<at::Generator>) {
+    TORCH_CHECK(to.has_value(), "torchvulkan [NOT IMPLEMENTED]: random_ with an open upper bound");
+    return random_range_(self, from, *to, "random_");
+}
+at::Tensor& random_to_(at::Tensor& self, int64_t to, c10::optional<at::Generator>) { return random_range_(self, 0, to, "random_"); }
+// a random permutation: the order that sorts n uniform numbers
+at::Tensor& randperm_out(int64_t n, c10::optional<at::Generator>, at::Tensor& out) {
+    TORCH_CHECK(n >= 0, "n must be non-negative, got", n);
+    if (out.numel() != n) out.resize_({n});
+    if (n == 0) return out;
+    at::Tensor u = at::empty({n}, out.options().dtype(at::kFloat));
+    u.uniform_(0.0, 1.0);
+    out.copy_(std::get<1>(at::sort(u, /*stable=*/true, 0, false)).to(out.scalar_type()));
+    return out;
+}
+
 }  // namespace
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+    m.impl("random_.from", &random_from_);
+    m.impl("random_.to", &random_to_);
+    m.impl("randperm.generator_out", &randperm_out);
     m.impl("multinomial", &multinomial);
     m.impl("uniform_", &uniform_);
     m.impl("normal_", &normal_);
