@@ -554,7 +554,7 @@ def run_sharded_bmm(rank, world, dev, pk):
 
 
 KERNEL_WORKLOADS = ("k_gemm4096", "k_gemm_mlp", "k_wgrad", "k_add", "k_exp", "k_sum", "k_argmax", "k_softmax", "k_rmsnorm", "k_layernorm",
-                    "k_bn", "k_sort", "k_embedding", "k_xent")
+                    "k_bn", "k_sort", "k_embedding", "k_xent", "k_scaled_mm")
 
 
 def profile_kernels(args, dev):
@@ -577,6 +577,14 @@ def profile_kernels(args, dev):
         out = torch.empty(m, n, device=dev, dtype=h)
         run = lambda: ops.gemm(A, B, out=out)  # noqa: E731
         info = {"flops": 2.0 * m * n * k, "bytes": 2.0 * (m * k + k * n + m * n), "shape": [m, n, k]}
+    elif w == "k_scaled_mm":
+        m = n = k = 8192                                              # float8 operands: 64 MiB each, bf16 result 128 MiB
+        a = torch.randn(m, k, device=dev).to(torch.float8_e4m3fn)
+        b = torch.randn(n, k, device=dev).to(torch.float8_e4m3fn).t()     # k contiguous: read in place by the float8 kernel
+        sa, sb = torch.tensor(0.5, device=dev), torch.tensor(2.0, device=dev)
+        out = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+        run = lambda: ops.scaled_mm(a, b, sa, sb, out=out)  # noqa: E731
+        info = {"flops": 2.0 * m * n * k, "bytes": 1.0 * (m * k + k * n) + 2.0 * m * n, "shape": [m, n, k], "operands": "float8_e4m3fn", "result": "bf16"}
     elif w in ("k_add", "k_exp", "k_sum", "k_argmax"):
         n = 1 << 28          # 1 GiB per fp32 tensor: the code path of the 2^30 config at a quarter of its footprint
         x = torch.randn(n, device=dev)

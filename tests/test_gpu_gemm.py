@@ -394,3 +394,34 @@ def test_config5_bmm_slice(cuda, dtype):
     err = rel_fro(f64(out[:, rows]), ref)
     assert err <= 1e-2, err
     assert not torch.isnan(out).any()
+
+
+@pytest.mark.parametrize("a_dt,b_dt", [(torch.float8_e4m3fn, torch.float8_e4m3fn), (torch.float8_e5m2, torch.float8_e4m3fn)])
+@pytest.mark.parametrize("m,n,k", [(256, 512, 128), (300, 520, 1040), (128, 64, 144), (1024, 1024, 2048)])
+def test_scaled_mm_float8_kernel_through_the_c_abi(cuda, a_dt, b_dt, m, n, k):
+    """tvk_scaled_mm on k-contiguous float8 operands (the tcgen05 kind::f8f6f4 kernel, scales / bias / cast in its epilogue)
+    against the float64 product of the same float8 values: products of float8 numbers are exact in fp32, so only the order
+    of the fp32 additions differs (1e-5 relative for an fp32 result; the 16-bit results to their rounding)."""
+    g = torch.Generator().manual_seed(71)
+    a = torch.randn(m, k, generator=g).to(a_dt)
+    b = torch.randn(n, k, generator=g).to(b_dt).t()
+    bias = torch.randn(n, generator=g)
+    ref = f64(a.float()) @ f64(b.float())
+    for rowwise in (False, True):
+        sa = (torch.rand(m, 1, generator=g) + 0.5) if rowwise else torch.tensor(0.75)
+        sb = (torch.rand(1, n, generator=g) + 0.5) if rowwise else torch.tensor(1.5)
+        want = ref * f64(sa) * f64(sb)
+        for out_dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 1e-2), (torch.float16, 1e-3)):
+            bdev = bias.to(out_dtype).to(cuda)
+            got = ops().scaled_mm(a.to(cuda), torch.empty_strided(b.shape, b.stride(), dtype=b_dt, device=cuda).copy_(b), sa.to(cuda), sb.to(cuda),
+                                  out_dtype=out_dtype, bias=bdev)
+            ops().check_device_status()
+            assert rel_fro(f64(got), want + f64(bias.to(out_dtype))) <= tol
+    # float8 output divided by scale_result (the accumulator route + finishing pass)
+    sr = torch.tensor(4.0)
+    got8 = ops().scaled_mm(a.to(cuda), torch.empty_strided(b.shape, b.stride(), dtype=b_dt, device=cuda).copy_(b), torch.tensor(0.75).to(cuda),
+                           torch.tensor(1.5).to(cuda), out_dtype=torch.float8_e4m3fn, scale_result=sr.to(cuda))
+    want8 = torch.from_numpy(ref * 0.75 * 1.5 / 4.0).float().to(torch.float8_e4m3fn).float()
+    g8 = got8.cpu().float()
+    same = (g8 == want8) | (g8.isnan() & want8.isnan())
+    assert same.float().mean() >= 0.995

@@ -108,6 +108,36 @@ def gemm(a, b, bias=None, alpha=1.0, beta=1.0, act=None, out=None, force_path=0,
     return out
 
 
+def scaled_mm(a, b, scale_a, scale_b, out_dtype=torch.bfloat16, bias=None, scale_result=None, out=None):
+    """out = cast((a * scale_a) @ (b * scale_b) + bias) for float8 a [m, k] and b [k, n] (any strides; k-contiguous operands are
+    read in place by the float8 tensor-core kernel). scale_a: fp32 scalar or [m, 1]; scale_b: fp32 scalar or [1, n]."""
+    kinds = {torch.float8_e4m3fn: capi.F8_E4M3, torch.float8_e5m2: capi.F8_E5M2}
+    outs = {torch.float32: capi.SCALED_OUT_F32, torch.float16: capi.SCALED_OUT_F16, torch.bfloat16: capi.SCALED_OUT_BF16,
+            torch.float8_e4m3fn: capi.SCALED_OUT_E4M3, torch.float8_e5m2: capi.SCALED_OUT_E5M2}
+    m, k = a.shape
+    n = b.shape[1]
+    assert b.shape[0] == k and scale_a.dtype == torch.float32 and scale_b.dtype == torch.float32
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype, device=a.device)
+    d = capi.ScaledMmDesc()
+    d.a_kind, d.b_kind, d.out_kind = kinds[a.dtype], kinds[b.dtype], outs[out.dtype]
+    d.m, d.n, d.k = m, n, k
+    d.a, d.a_rs, d.a_cs = a.data_ptr(), a.stride(0), a.stride(1)
+    d.b, d.b_rs, d.b_cs = b.data_ptr(), b.stride(0), b.stride(1)
+    d.out = out.data_ptr()
+    d.scale_a, d.sa_stride = scale_a.data_ptr(), (1 if scale_a.numel() > 1 else 0)
+    d.scale_b, d.sb_stride = scale_b.data_ptr(), (1 if scale_b.numel() > 1 else 0)
+    if bias is not None:
+        d.bias, d.bias_dtype = bias.data_ptr(), dt(bias)
+    if scale_result is not None:
+        d.scale_result = scale_result.data_ptr()
+    nbytes = C.c_uint64(0)
+    capi.call("tvk_scaled_mm_workspace_size", C.byref(d), C.byref(nbytes))
+    ws = _ws(nbytes.value, a.device)
+    capi.call("tvk_scaled_mm", C.byref(d), ptr(ws), nbytes.value, stream())
+    return out
+
+
 def gemm_path(a, b, out, **kw) -> int:
     d = gemm_desc(a, b, out, **kw)
     p = C.c_int(0)
