@@ -643,3 +643,26 @@ def test_integer_random_fills_and_permutations(vk):
     assert perm.dtype == torch.long and torch.equal(perm.sort().values, torch.arange(1000)) and not torch.equal(perm, torch.arange(1000))
     torchvulkan.manual_seed(21)
     assert torch.equal(torch.randint(3, 11, (20000,), device=vk).cpu(), r)
+
+
+def test_nonzero_and_assignment_through_an_index(vk):
+    g = torch.Generator().manual_seed(20)
+    x = torch.randn(5, 4, 3, generator=g)
+    x[x.abs() < 0.6] = 0
+    _close(x.to(vk).nonzero(), x.nonzero(), 0)
+    _close((x > 0).to(vk).nonzero(), (x > 0).nonzero(), 0)
+    for got, want in zip(torch.where(x.to(vk) > 0), torch.where(x > 0)):
+        _close(got, want, 0)
+    assert torch.zeros(3, 2).to(vk).nonzero().shape == (0, 2)
+    a, b = x.to(vk).clone(), x.clone()
+    idx = torch.tensor([4, 0, 2])
+    v = torch.randn(3, 4, 3, generator=g)
+    a[idx.to(vk)] = v.to(vk); b[idx] = v
+    _close(a, b, 0)
+    cols = torch.tensor([3, 0])
+    a[:, cols.to(vk)] = 7.0; b[:, cols] = 7.0
+    _close(a, b, 0)
+    w = torch.zeros(6, 3)
+    wd = w.to(vk)
+    wd[torch.tensor([1, 5]).to(vk)] = torch.ones(3).to(vk); w[torch.tensor([1, 5])] = torch.ones(3)
+    _close(wd, w, 0)

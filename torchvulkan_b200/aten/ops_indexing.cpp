@@ -250,7 +250,6 @@ at::Tensor& vk_index_put_impl_(at::Tensor& self, const c10::List<c10::optional<a
         self.add_(delta.reshape(self.sizes()));
         return self;
     }
-    if (!accumulate) TVK_NOT_IMPLEMENTED("index_put_ without accumulate (assignment through an index tensor)");
     index = long_index(index, "index_put_");
     at::Tensor idx = is_vulkan(index) ? index : index.to(self.device());
     idx = at::where(at::lt(idx, 0), idx + self.size(pos), idx);
@@ -259,7 +258,17 @@ at::Tensor& vk_index_put_impl_(at::Tensor& self, const c10::List<c10::optional<a
     for (int64_t d = 0; d < idx.dim(); ++d) shape.push_back(idx.size(d));
     for (int64_t d = pos + 1; d < self.dim(); ++d) shape.push_back(self.size(d));
     at::Tensor src = values.to(self.scalar_type()).expand(shape);
-    self.add_(add_along(self.sizes(), pos, idx, src));
+    at::Tensor delta = add_along(self.sizes(), pos, idx, src);
+    if (accumulate) {
+        self.add_(delta);
+        return self;
+    }
+    // assignment: the addressed slices take the new values, the others stay. (An index that names a slice twice is left
+    // undefined by ATen - one of the values wins; here they add up.)
+    std::vector<int64_t> view(self.dim(), 1);
+    view[pos] = self.size(pos);
+    at::Tensor hit = at::gt(add_along({self.size(pos)}, 0, idx.reshape({-1}), at::ones({idx.numel()}, self.options())), 0).view(view);
+    self.copy_(at::where(hit, delta, self));
     return self;
 }
 
@@ -277,6 +286,23 @@ at::Tensor vk_masked_select(const at::Tensor& self, const at::Tensor& mask) {
     return take_along(xs, 0, rows);
 }
 at::Tensor& vk_masked_select_out(const at::Tensor& self, const at::Tensor& mask, at::Tensor& out) { return into(out, vk_masked_select(self, mask)); }
+
+// nonzero: the positions from selected_positions, unravelled into one column per dimension with exact integer division
+at::Tensor vk_nonzero(const at::Tensor& self) {
+    at::Tensor mask = self.scalar_type() == at::kBool ? self : at::ne(self, 0);
+    at::Tensor flat = selected_positions(mask);
+    const int64_t nd = self.dim();
+    if (nd == 0) return at::empty({flat.numel(), 0}, flat.options());
+    std::vector<at::Tensor> cols(nd);
+    at::Tensor rest = flat;
+    for (int64_t d = nd - 1; d >= 0; --d) {
+        const int64_t size = std::max<int64_t>(self.size(d), 1);
+        cols[d] = at::remainder(rest, size);
+        rest = at::floor_divide(rest, size);
+    }
+    return at::stack(cols, 1);
+}
+at::Tensor& vk_nonzero_out(const at::Tensor& self, at::Tensor& out) { return into(out, vk_nonzero(self)); }
 
 // ---- flip, roll --------------------------------------------------------------------------------
 at::Tensor vk_flip(const at::Tensor& self, at::IntArrayRef dims) {
@@ -355,6 +381,8 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("index.Tensor", &vk_index_tensor);
     m.impl("index.Tensor_out", &vk_index_tensor_out);
     m.impl("_index_put_impl_", &vk_index_put_impl_);
+    m.impl("nonzero", &vk_nonzero);
+    m.impl("nonzero.out", &vk_nonzero_out);
     m.impl("masked_select", &vk_masked_select);
     m.impl("masked_select.out", &vk_masked_select_out);
     m.impl("flip", &vk_flip);
