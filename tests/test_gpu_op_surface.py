@@ -666,3 +666,20 @@ def test_nonzero_and_assignment_through_an_index(vk):
     wd = w.to(vk)
     wd[torch.tensor([1, 5]).to(vk)] = torch.ones(3).to(vk); w[torch.tensor([1, 5])] = torch.ones(3)
     _close(wd, w, 0)
+
+
+def test_selections_on_integer_and_boolean_tensors_are_bit_exact(vk):
+    g = torch.Generator().manual_seed(22)
+    big = torch.randint(-2 ** 62, 2 ** 62, (7, 5, 3), generator=g)
+    idx = torch.tensor([6, 0, 0, 3])
+    for t in (big, big.int(), big > 0, (big % 200).to(torch.uint8)):
+        td = t.to(vk)
+        _close(td[idx.to(vk)], t[idx], 0)
+        _close(td.index_select(1, idx[:3].to(vk) % 5), t.index_select(1, idx[:3] % 5), 0)
+        _close(td[:, torch.tensor([True, False, True, True, False]).to(vk)], t[:, torch.tensor([True, False, True, True, False])], 0)
+        _close(td.flip(0), t.flip(0), 0)
+        _close(td.gather(2, torch.zeros(7, 5, 2, dtype=torch.long).to(vk)), t.gather(2, torch.zeros(7, 5, 2, dtype=torch.long)), 0)
+    labels = torch.randint(0, 10, (64,), generator=g)
+    perm = torch.randperm(64, generator=g)
+    _close(labels.to(vk)[perm.to(vk)], labels[perm], 0)                      # shuffling a label vector
+    _close(labels.to(vk).masked_select((labels > 4).to(vk)), labels.masked_select(labels > 4), 0)

@@ -16,6 +16,12 @@ namespace {
 void require_table(const at::Tensor& t, const char* op) {
     if (!is_hot_float(t.scalar_type())) TVK_NOT_IMPLEMENTED(op, " for dtype ", t.scalar_type(), " on the vulkan device (floating tensors are supported)");
 }
+// selections only move values: integer, boolean and float64 tensors are gathered bit for bit
+void require_gatherable(const at::Tensor& t, const char* op) {
+    const at::ScalarType st = t.scalar_type();
+    if (!(is_hot_float(st) || st == at::kLong || st == at::kInt || st == at::kBool || st == at::kByte || st == at::kDouble))
+        TVK_NOT_IMPLEMENTED(op, " for dtype ", st, " on the vulkan device");
+}
 at::Tensor long_index(const at::Tensor& index, const char* op) {
     TORCH_CHECK(index.scalar_type() == at::kLong || index.scalar_type() == at::kInt, op, "(): Expected dtype int32/int64 for index");
     return index.scalar_type() == at::kLong ? index : index.to(at::kLong);
@@ -33,7 +39,19 @@ at::Tensor take_along(const at::Tensor& self, int64_t dim, const at::Tensor& ind
     std::vector<int64_t> moved_shape(index.sizes().begin(), index.sizes().end());
     for (int64_t d = 0; d < self.dim(); ++d)
         if (d != dim) moved_shape.push_back(self.size(d));
-    at::Tensor rows = at::embedding(table, index.reshape({-1})).reshape(moved_shape);        // [index..., rest...]
+    // The row gather copies bits, so integer and boolean tables ride it as fp32 words: Int as it is, Long as two words per
+    // element, Bool / Byte widened to Int first (exact) and narrowed afterwards.
+    const at::ScalarType st = self.scalar_type();
+    at::Tensor rows;
+    if (is_hot_float(st)) {
+        rows = at::embedding(table, index.reshape({-1}));
+    } else {
+        const at::ScalarType word = (st == at::kLong || st == at::kDouble) ? st : at::kInt;
+        at::Tensor words = (word == st ? table : table.to(at::kInt)).view(at::kFloat);
+        rows = at::embedding(words, index.reshape({-1})).view(word);
+        if (word != st) rows = rows.to(st);
+    }
+    rows = rows.reshape(moved_shape);                                                       // [index..., rest...]
     // bring the index dimensions back to position dim
     const int64_t k = index.dim(), nd = (int64_t)moved_shape.size();
     std::vector<int64_t> perm;
@@ -59,7 +77,7 @@ at::Tensor add_along(at::IntArrayRef sizes, int64_t dim, const at::Tensor& index
 }
 
 at::Tensor vk_index_select(const at::Tensor& self, int64_t dim, const at::Tensor& index_in) {
-    require_table(self, "index_select");
+    require_gatherable(self, "index_select");
     TORCH_CHECK(index_in.dim() <= 1, "index_select(): Index is supposed to be a vector, but got dim: ", index_in.dim());
     at::Tensor index = long_index(index_in, "index_select");
     if (self.dim() == 0) {
@@ -105,7 +123,7 @@ at::Tensor flat_offsets(at::IntArrayRef sizes, int64_t dim, const at::Tensor& in
     return flat;
 }
 at::Tensor vk_gather(const at::Tensor& self, int64_t dim, const at::Tensor& index_in, bool) {
-    require_table(self, "gather");
+    require_gatherable(self, "gather");
     at::Tensor index = long_index(index_in, "gather");
     if (self.dim() == 0) return self.expand(index.sizes()).clone();
     dim = at::maybe_wrap_dim(dim, self.dim());
@@ -114,8 +132,7 @@ at::Tensor vk_gather(const at::Tensor& self, int64_t dim, const at::Tensor& inde
         TORCH_CHECK(d == dim || index.size(d) <= self.size(d), "Size does not match at dimension ", d, " expected index ", index.sizes(), " to be no larger than self ", self.sizes(), " apart from dimension ", dim);
     if (index.numel() == 0) return at::empty(index.sizes(), self.options());
     at::Tensor flat = flat_offsets(self.sizes(), dim, index);
-    at::Tensor table = contiguous_vulkan(self).reshape({-1, 1});
-    return at::embedding(table, flat.reshape({-1})).reshape(index.sizes());
+    return take_along(contiguous_vulkan(self).reshape({-1}), 0, flat.reshape({-1})).reshape(index.sizes());
 }
 at::Tensor& vk_gather_out(const at::Tensor& self, int64_t dim, const at::Tensor& index, bool sparse_grad, at::Tensor& out) { return into(out, vk_gather(self, dim, index, sparse_grad)); }
 
@@ -213,7 +230,7 @@ int64_t single_index_position(const c10::List<c10::optional<at::Tensor>>& indice
     return pos;
 }
 at::Tensor vk_index_tensor(const at::Tensor& self, const c10::List<c10::optional<at::Tensor>>& indices) {
-    require_table(self, "index");
+    require_gatherable(self, "index");
     at::Tensor index;
     const int64_t pos = single_index_position(indices, &index);
     if (index.scalar_type() == at::kBool || index.scalar_type() == at::kByte) {
@@ -276,7 +293,7 @@ at::Tensor& vk_index_put_impl_(at::Tensor& self, const c10::List<c10::optional<a
 // The elements of self where mask is true, in row-major order (selected_positions, then a row gather). Printing a floating
 // tensor goes through this: torch's formatter selects the finite non-zero values.
 at::Tensor vk_masked_select(const at::Tensor& self, const at::Tensor& mask) {
-    require_table(self, "masked_select");
+    require_gatherable(self, "masked_select");
     TORCH_CHECK(mask.scalar_type() == at::kBool, "masked_select: expected BoolTensor for mask");
     const auto shape = at::infer_size(self.sizes(), mask.sizes());
     at::Tensor xs = contiguous_vulkan(self.expand(shape)).reshape({-1});
@@ -306,7 +323,7 @@ at::Tensor& vk_nonzero_out(const at::Tensor& self, at::Tensor& out) { return int
 
 // ---- flip, roll --------------------------------------------------------------------------------
 at::Tensor vk_flip(const at::Tensor& self, at::IntArrayRef dims) {
-    require_table(self, "flip");
+    require_gatherable(self, "flip");
     at::Tensor r = self;
     for (int64_t d : dims) {
         d = at::maybe_wrap_dim(d, self.dim());
