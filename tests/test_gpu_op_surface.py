@@ -683,3 +683,15 @@ def test_selections_on_integer_and_boolean_tensors_are_bit_exact(vk):
     perm = torch.randperm(64, generator=g)
     _close(labels.to(vk)[perm.to(vk)], labels[perm], 0)                      # shuffling a label vector
     _close(labels.to(vk).masked_select((labels > 4).to(vk)), labels.masked_select(labels > 4), 0)
+
+
+def test_kthvalue_and_median(vk):
+    g = torch.Generator().manual_seed(23)
+    x = torch.randn(6, 9, generator=g)
+    for k, dim, keep in ((1, 1, False), (4, 1, True), (6, 0, False)):
+        (vd, idd), (vc, idc) = x.to(vk).kthvalue(k, dim, keep), x.kthvalue(k, dim, keep)
+        _close(vd, vc, 0); _close(idd, idc, 0)
+    (vd, idd), (vc, idc) = x.to(vk).median(1), x.median(1)
+    _close(vd, vc, 0); _close(idd, idc, 0)
+    _close(x.to(vk).median(), x.median(), 0)
+    _close(x[:, :8].to(vk).median(1).values, x[:, :8].median(1).values, 0)     # even count: the lower middle value

@@ -373,6 +373,30 @@ at::Tensor vk_prod_all(const at::Tensor& self, c10::optional<at::ScalarType> dty
 at::Tensor& vk_prod_int_out(const at::Tensor& self, int64_t dim, bool keepdim, c10::optional<at::ScalarType> dtype, at::Tensor& out) {
     return into(out, vk_prod_dim(self, dim, keepdim, dtype));
 }
+// k-th smallest value along dim and its index (k counts from 1): the k-th column of the sort. median = the lower middle one.
+std::tuple<at::Tensor, at::Tensor> vk_kthvalue(const at::Tensor& self, int64_t k, int64_t dim, bool keepdim) {
+    require_table(self, "kthvalue");
+    at::Tensor x = self.dim() == 0 ? self.reshape({1}) : self;
+    dim = at::maybe_wrap_dim(dim, x.dim());
+    TORCH_CHECK(k >= 1 && k <= x.size(dim), "kthvalue(): selected number k out of range for dimension ", dim);
+    at::Tensor values, indices;
+    std::tie(values, indices) = at::sort(x, /*stable=*/true, dim, false);
+    values = contiguous_vulkan(values.narrow(dim, k - 1, 1));
+    indices = contiguous_vulkan(indices.narrow(dim, k - 1, 1));
+    if (self.dim() == 0) return {values.reshape({}), indices.reshape({})};
+    if (!keepdim) return {values.squeeze(dim), indices.squeeze(dim)};
+    return {values, indices};
+}
+std::tuple<at::Tensor, at::Tensor> vk_median_dim(const at::Tensor& self, int64_t dim, bool keepdim) {
+    const int64_t n = self.dim() == 0 ? 1 : self.size(at::maybe_wrap_dim(dim, self.dim()));
+    TORCH_CHECK(n > 0, "median(): Expected reduction dim ", dim, " to have non-zero size.");
+    return vk_kthvalue(self, (n + 1) / 2, dim, keepdim);
+}
+at::Tensor vk_median(const at::Tensor& self) {
+    TORCH_CHECK(self.numel() > 0, "median(): cannot compute the median of an empty tensor");
+    return std::get<0>(vk_median_dim(contiguous_vulkan(self).reshape({-1}), 0, false));
+}
+
 bool vk_equal(const at::Tensor& a, const at::Tensor& b) {
     if (a.sizes() != b.sizes()) return false;
     if (a.numel() == 0) return true;
@@ -408,6 +432,9 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("prod.dim_int", &vk_prod_dim);
     m.impl("prod.int_out", &vk_prod_int_out);
     m.impl("equal", &vk_equal);
+    m.impl("kthvalue", &vk_kthvalue);
+    m.impl("median", &vk_median);
+    m.impl("median.dim", &vk_median_dim);
 }
 
 }  // namespace tvk_aten
