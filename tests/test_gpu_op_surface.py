@@ -695,3 +695,19 @@ def test_kthvalue_and_median(vk):
     _close(vd, vc, 0); _close(idd, idc, 0)
     _close(x.to(vk).median(), x.median(), 0)
     _close(x[:, :8].to(vk).median(1).values, x[:, :8].median(1).values, 0)     # even count: the lower middle value
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_dropout_packet_and_scalar_kernels_draw_the_same_mask(vk, dtype):
+    """The dropout stream is a function of (seed, offset, element index) alone: an aligned tensor (eight elements per thread)
+    and the same values at an odd address (one block of four per thread) are dropped at the same positions."""
+    import torchvulkan
+
+    n = 8 * 1000 + 5
+    data = torch.randn(n + 1).to(dtype)
+    aligned, shifted = data[1:].clone().to(vk), data.to(vk)[1:]
+    torchvulkan.manual_seed(9)
+    ya = F.dropout(aligned, 0.3, training=True).cpu()
+    torchvulkan.manual_seed(9)
+    ys = F.dropout(shifted, 0.3, training=True).cpu()
+    assert torch.equal(ya, ys) and abs(float((ya != 0).float().mean()) - 0.7) < 0.02
