@@ -924,3 +924,45 @@ def test_image_classifier_script_flow(vk):
     assert np.allclose(ld, lc, rtol=2e-3, atol=1e-4), (ld, lc)
     assert rel_fro(od.double().numpy(), oc.double().numpy()) <= 2e-2
     assert isinstance(cd, int) and abs(cd - cc) <= 3
+
+
+def test_mixed_precision_training_loops(vk):
+    """The usual mixed-precision recipes end to end on the device: a small decoder with dropout under fp16 autocast with
+    GradScaler, gradient clipping after unscale_ and the fused AdamW (which receives the scaler's found_inf); a small ResNet in
+    channels-last under bf16 autocast with momentum SGD. The losses stay finite and go down."""
+    from models import Decoder, SmallResNet
+
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(Decoder(vocab=64, seq=64, layers=2, width=128, heads=4, kv_heads=2, hidden=256), torch.nn.Dropout(0.1)).to(vk)
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-3, fused=True)
+    scaler = torch.amp.GradScaler("vulkan")
+    g = torch.Generator().manual_seed(1)
+    data = torch.randint(0, 64, (16, 65), generator=g)
+    losses = []
+    for _ in range(16):
+        x, y = data[:, :-1].to(vk), data[:, 1:].to(vk)
+        with torch.autocast("vulkan", dtype=torch.float16):
+            loss = F.cross_entropy(model(x).view(-1, 64), y.reshape(-1))
+        opt.zero_grad(set_to_none=True)
+        scaler.scale(loss).backward()
+        scaler.unscale_(opt)
+        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+        scaler.step(opt); scaler.update()
+        losses.append(loss.item())
+    assert all(np.isfinite(losses)) and losses[-1] < losses[0] - 0.3, losses
+    # the scaler without unscale_(): the fused optimizer divides the gradients by grad_scale itself
+    w = torch.nn.Parameter(torch.ones(8, device=vk))
+    o2 = torch.optim.AdamW([w], lr=0.1, fused=True, weight_decay=0.0)
+    s2 = torch.amp.GradScaler("vulkan", init_scale=256.0)
+    s2.scale((w * torch.arange(8.0, device=vk)).sum()).backward()
+    s2.step(o2); s2.update()
+    assert torch.allclose(w.grad.cpu(), torch.arange(8.0)) and float(w.detach().cpu()[1]) < 1.0 and float(w.detach().cpu()[0]) == 1.0
+    net = torch.nn.Sequential(SmallResNet(8), torch.nn.Dropout(0.2)).to(vk).to(memory_format=torch.channels_last)
+    o3 = torch.optim.SGD(net.parameters(), lr=0.05, momentum=0.9)
+    img, lab = torch.randn(32, 3, 16, 16, generator=g), torch.randint(0, 10, (32,), generator=g)
+    ls = []
+    for _ in range(12):
+        with torch.autocast("vulkan", dtype=torch.bfloat16):
+            loss = F.cross_entropy(net(img.to(vk).contiguous(memory_format=torch.channels_last)), lab.to(vk))
+        o3.zero_grad(); loss.backward(); o3.step(); ls.append(loss.item())
+    assert all(np.isfinite(ls)) and ls[-1] < ls[0], ls

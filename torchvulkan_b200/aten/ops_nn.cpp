@@ -404,6 +404,21 @@ at::Tensor cat(const at::ITensorListRef& tensors, int64_t dim) {
 at::Tensor& cat_out(const at::ITensorListRef& tensors, int64_t dim, at::Tensor& out) { return copy_into(out, (cat)(tensors, dim)); }
 
 // ---- optimizers -------------------------------------------------------------------------
+// torch.amp.GradScaler hands fused optimizers its state instead of stepping around them: found_inf (skip the whole step when
+// it is set) and, when unscale_() was not called first, grad_scale (the gradients are divided by it in place, as ATen's CUDA
+// kernels do). The skip decision is read back - one synchronisation per step, where the unfused path has one as well.
+// Returns false when the step is to be skipped.
+bool apply_grad_scaler(at::TensorList grads, const c10::optional<at::Tensor>& grad_scale, const c10::optional<at::Tensor>& found_inf) {
+    if (found_inf.has_value() && found_inf->defined() && found_inf->item<float>() != 0.f) return false;
+    if (grad_scale.has_value() && grad_scale->defined()) {
+        for (const at::Tensor& g : grads) {
+            if (!g.defined() || g.numel() == 0) continue;
+            at::Tensor gm = g;
+            gm.div_(grad_scale->to(g.scalar_type()).reshape({}));
+        }
+    }
+    return true;
+}
 double host_scalar(const at::Tensor& t) { return t.item<double>(); }  // CPU step counters cost nothing; device ones sync
 
 void fused_adam_impl(at::TensorList params, at::TensorList grads, at::TensorList exp_avgs, at::TensorList exp_avg_sqs, at::TensorList max_exp_avg_sqs,
@@ -413,8 +428,7 @@ void fused_adam_impl(at::TensorList params, at::TensorList grads, at::TensorList
     TORCH_CHECK(grads.size() == n && exp_avgs.size() == n && exp_avg_sqs.size() == n && state_steps.size() == n, "torchvulkan [ERROR]: fused adam: list sizes differ");
     if (amsgrad) TVK_NOT_IMPLEMENTED("fused Adam with amsgrad");
     (void)max_exp_avg_sqs;
-    if ((grad_scale.has_value() && grad_scale->defined()) || (found_inf.has_value() && found_inf->defined()))
-        TVK_NOT_IMPLEMENTED("fused Adam with grad_scale / found_inf");
+    if (!apply_grad_scaler(grads, grad_scale, found_inf)) return;
     // One list launch per (device, dtype) run of the list. Step counters that live on the device (fp32 scalars, as
     // torch.optim creates them for fused optimizers) are read by the kernel; host counters are read here.
     std::vector<tvk_multi_item> items;
@@ -478,8 +492,7 @@ void fused_sgd_(at::TensorList params, at::TensorList grads, at::TensorList bufs
     TORCH_CHECK(grads.size() == n, "torchvulkan [ERROR]: fused sgd: list sizes differ");
     const bool has_momentum = momentum != 0.0;
     TORCH_CHECK(has_momentum ? bufs.size() == n : bufs.empty(), "torchvulkan [ERROR]: fused sgd: momentum buffer list size");
-    if ((grad_scale.has_value() && grad_scale->defined()) || (found_inf.has_value() && found_inf->defined()))
-        TVK_NOT_IMPLEMENTED("fused SGD with grad_scale / found_inf");
+    if (!apply_grad_scaler(grads, grad_scale, found_inf)) return;
     std::vector<tvk_multi_item> items;
     size_t i = 0;
     while (i < n) {
