@@ -966,3 +966,63 @@ def test_mixed_precision_training_loops(vk):
             loss = F.cross_entropy(net(img.to(vk).contiguous(memory_format=torch.channels_last)), lab.to(vk))
         o3.zero_grad(); loss.backward(); o3.step(); ls.append(loss.item())
     assert all(np.isfinite(ls)) and ls[-1] < ls[0], ls
+
+
+def _module_matches_cpu(vk, make, inputs, tol=2e-4, loss=None):
+    """The same module (same initial state) on the device and on ATen CPU: output and every gradient."""
+    torch.manual_seed(0)
+    ref = make()
+    dev = make()
+    dev.load_state_dict(ref.state_dict())
+    dev = dev.to(vk)
+    xs_c = [t.clone().requires_grad_(t.is_floating_point()) for t in inputs]
+    xs_d = [t.to(vk).requires_grad_(t.is_floating_point()) for t in inputs]
+    loss = loss or (lambda o: (o[0] if isinstance(o, tuple) else o).pow(2).mean())
+    lc, ld = loss(ref(*xs_c)), loss(dev(*xs_d))
+    assert abs(lc.item() - ld.item()) <= tol * (1 + abs(lc.item())), (lc.item(), ld.item())
+    lc.backward(); ld.backward()
+    def close(d, c, what):
+        # relative to the gradient's own size, with a floor: a gradient that is numerically zero (1e-9) is compared absolutely
+        d, c = d.cpu().double(), c.double()
+        err = float((d - c).norm()) / max(float(c.norm()), 1e-5 * c.numel() ** 0.5)
+        assert err <= 50 * tol, (what, err)
+
+    for (n, pc), pd in zip(ref.named_parameters(), dev.parameters()):
+        close(pd.grad, pc.grad, n)
+    for c, d in zip(xs_c, xs_d):
+        if c.grad is not None:
+            close(d.grad, c.grad, "input")
+
+
+def test_recurrent_transformer_and_padding_modules_match_cpu(vk):
+    """nn.LSTM / nn.GRU (the fused cells every non-CPU device is routed to), nn.TransformerEncoderLayer in training mode,
+    MultiheadAttention with a padding mask, reflection / replication padding, the 4-D cross-entropy of a segmentation head and
+    weight normalisation, each against the same module on ATen CPU in fp32."""
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(4, 10, 32, generator=g)
+    img = torch.randn(2, 8, 12, 10, generator=g)
+    _module_matches_cpu(vk, lambda: torch.nn.LSTM(32, 24, num_layers=2, batch_first=True), [x])
+    _module_matches_cpu(vk, lambda: torch.nn.GRU(32, 24, batch_first=True, bidirectional=True), [x])
+    _module_matches_cpu(vk, lambda: torch.nn.LSTM(32, 24, bias=False), [x])
+    _module_matches_cpu(vk, lambda: torch.nn.TransformerEncoderLayer(32, 4, 64, dropout=0.0, batch_first=True), [x])
+    _module_matches_cpu(vk, lambda: torch.nn.TransformerDecoderLayer(32, 4, 64, dropout=0.0, batch_first=True, norm_first=True), [x, x.flip(0)])
+    pad_mask = (torch.arange(10)[None] > 6).expand(4, 10)
+
+    class Mha(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.m = torch.nn.MultiheadAttention(32, 4, batch_first=True)
+
+        def forward(self, t):
+            return self.m(t, t, t, key_padding_mask=pad_mask.to(t.device), need_weights=False)[0]
+
+    _module_matches_cpu(vk, Mha, [x])
+    _module_matches_cpu(vk, lambda: torch.nn.Sequential(torch.nn.ReflectionPad2d((2, 1, 0, 3)), torch.nn.Conv2d(8, 4, 3)), [img])
+    _module_matches_cpu(vk, lambda: torch.nn.Sequential(torch.nn.ReplicationPad2d(2), torch.nn.Conv2d(8, 4, 3)), [img])
+    _module_matches_cpu(vk, lambda: torch.nn.Sequential(torch.nn.ReflectionPad1d(3), torch.nn.Conv1d(10, 6, 3)), [x])
+    _module_matches_cpu(vk, lambda: torch.nn.utils.parametrizations.weight_norm(torch.nn.Linear(32, 16)), [x])
+    tgt = torch.randint(0, 8, (2, 12, 10), generator=g)
+    tgt[0, :2] = -100
+    for red in ("mean", "sum", "none"):
+        _module_matches_cpu(vk, lambda: torch.nn.Conv2d(8, 8, 1), [img],
+                            loss=lambda o, red=red: F.cross_entropy(o, tgt.to(o.device), reduction=red, ignore_index=-100).sum())
