@@ -711,3 +711,15 @@ def test_dropout_packet_and_scalar_kernels_draw_the_same_mask(vk, dtype):
     torchvulkan.manual_seed(9)
     ys = F.dropout(shifted, 0.3, training=True).cpu()
     assert torch.equal(ya, ys) and abs(float((ya != 0).float().mean()) - 0.7) < 0.02
+
+
+def test_new_operators_on_empty_tensors(vk):
+    e = torch.empty(0, 5)
+    none = torch.empty(0, dtype=torch.long)
+    for fn in (lambda t: t.clamp(0, 1), lambda t: F.leaky_relu(t), lambda t: (t > 0) & (t < 1), lambda t: t.sum(0), lambda t: (t > 0).all(1), lambda t: t.masked_fill(t > 0, 1.0),
+               lambda t: t.index_select(0, none.to(t.device)), lambda t: t[none.to(t.device)], lambda t: t[t[:, 0] > 0], lambda t: t.masked_select(t > 0), lambda t: t.nonzero(),
+               lambda t: t.flip(0), lambda t: F.dropout(t, 0.5, training=True), lambda t: t.clone().normal_(), lambda t: t.prod(0), lambda t: t @ t.t()):
+        got, want = fn(e.to(vk)), fn(e)
+        assert got.shape == want.shape and got.dtype == want.dtype
+    assert float(e.to(vk).sum().cpu()) == 0.0 and int((e.to(vk) > 0).sum().cpu()) == 0 and not bool((e.to(vk) > 0).any().cpu())
+    assert torch.ones(3, 4).to(vk)[none.to(vk)].shape == (0, 4)

@@ -35,10 +35,19 @@ at::Tensor& into(at::Tensor& out, const at::Tensor& value) {
 // rows of self along `dim` picked by a Long tensor of any shape: result shape = self[:dim] + index.shape + self[dim+1:]
 at::Tensor take_along(const at::Tensor& self, int64_t dim, const at::Tensor& index) {
     const int64_t n = self.size(dim);
-    at::Tensor table = contiguous_vulkan(self.movedim(dim, 0)).reshape({n, -1});
+    int64_t rest = 1;
     std::vector<int64_t> moved_shape(index.sizes().begin(), index.sizes().end());
     for (int64_t d = 0; d < self.dim(); ++d)
-        if (d != dim) moved_shape.push_back(self.size(d));
+        if (d != dim) { moved_shape.push_back(self.size(d)); rest *= self.size(d); }
+    if (n == 0 || rest == 0 || index.numel() == 0) {                 // nothing to gather (an index into an empty dimension must be empty)
+        TORCH_CHECK(index.numel() == 0 || n > 0, "index out of range in self");
+        std::vector<int64_t> shape;
+        for (int64_t d = 0; d < dim; ++d) shape.push_back(self.size(d));
+        for (int64_t d = 0; d < index.dim(); ++d) shape.push_back(index.size(d));
+        for (int64_t d = dim + 1; d < self.dim(); ++d) shape.push_back(self.size(d));
+        return at::empty(shape, self.options());
+    }
+    at::Tensor table = contiguous_vulkan(self.movedim(dim, 0)).reshape({n, rest});
     // The row gather copies bits, so integer and boolean tables ride it as fp32 words: Int as it is, Long as two words per
     // element, Bool / Byte widened to Int first (exact) and narrowed afterwards.
     const at::ScalarType st = self.scalar_type();
@@ -71,7 +80,8 @@ at::Tensor add_along(at::IntArrayRef sizes, int64_t dim, const at::Tensor& index
     std::vector<int64_t> moved_sizes{n};
     for (int64_t d = 0; d < (int64_t)sizes.size(); ++d)
         if (d != dim) { rest *= sizes[d]; moved_sizes.push_back(sizes[d]); }
-    at::Tensor g = contiguous_vulkan(source.permute(perm)).reshape({-1, rest});
+    if (n == 0 || rest == 0 || index.numel() == 0) return at::zeros(sizes, source.options());
+    at::Tensor g = contiguous_vulkan(source.permute(perm)).reshape({index.numel(), rest});
     at::Tensor table = at::embedding_dense_backward(g, index.reshape({-1}), n, -1, false);      // [n, rest]
     return contiguous_vulkan(table.reshape(moved_sizes).movedim(0, dim));
 }
