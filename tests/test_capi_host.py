@@ -67,6 +67,32 @@ def test_argument_validation_without_a_gpu():
     assert lib.tvk_gemm(C.byref(d), None, 0, None) == capi.OK
 
 
+def test_validation_of_pooling_random_and_logical_calls_without_a_gpu():
+    """The argument checks of the pooling, random-fill, dropout and logical entry points run before any launch."""
+    from torchvulkan_b200 import capi
+
+    lib = capi.lib()
+    ok = capi.Pool2dDesc(capi.F16, 6, 8, 8, 4, 4, 2, 2, 2, 2, 0, 0, 1, 1, 1, 0)
+    assert C.sizeof(capi.Pool2dDesc) == 8 + 13 * 8 + 8 + 8            # the struct the header declares (with its padding)
+    assert lib.tvk_max_pool2d_forward(C.byref(ok), None, None, None, None) == capi.ERR_INVALID and b"null pointer" in lib.tvk_last_error()
+    for field, value, what in (("kh", 0, b"bad kernel"), ("stride_w", 0, b"bad kernel"), ("pad_h", 2, b"half of the kernel"), ("ho", 0, b"bad extent")):
+        d = capi.Pool2dDesc(capi.F16, 6, 8, 8, 4, 4, 2, 2, 2, 2, 0, 0, 1, 1, 1, 0)
+        setattr(d, field, value)
+        assert lib.tvk_max_pool2d_forward(C.byref(d), 1, 1, 1, None) == capi.ERR_INVALID and what in lib.tvk_last_error(), field
+    d = capi.Pool2dDesc(capi.F16, 6, 8, 8, 4, 4, 2, 2, 2, 2, 0, 0, 2, 1, 1, 0)
+    assert lib.tvk_avg_pool2d_forward(C.byref(d), 1, 1, None) == capi.ERR_INVALID and b"no dilation" in lib.tvk_last_error()
+    empty = capi.Pool2dDesc(capi.F16, 0, 8, 8, 4, 4, 2, 2, 2, 2, 0, 0, 1, 1, 1, 0)
+    assert lib.tvk_max_pool2d_backward(C.byref(empty), None, None, None, None) == capi.OK      # no planes: nothing to do
+    assert lib.tvk_random_fill(7, capi.F32, 1, 16, 0.0, 1.0, 0, 0, None, None) == capi.ERR_INVALID and b"distribution" in lib.tvk_last_error()
+    assert lib.tvk_random_fill(0, capi.F32, 1, 16, 2.0, 1.0, 0, 0, None, None) == capi.ERR_INVALID      # from > to
+    assert lib.tvk_random_fill(2, capi.F32, 1, 16, 1.5, 0.0, 0, 0, None, None) == capi.ERR_INVALID      # p > 1
+    assert lib.tvk_random_fill(1, capi.F32, None, 0, 0.0, 1.0, 0, 0, None, None) == capi.OK
+    assert lib.tvk_dropout(capi.F16, 1, 1, 1, 16, 1.5, 0, 0, None, None) == capi.ERR_INVALID and b"keep probability" in lib.tvk_last_error()
+    assert lib.tvk_logical(9, 1, 1, 1, 16, None) == capi.ERR_INVALID
+    assert lib.tvk_logical(capi.L_AND, 1, 1, None, 16, None) == capi.ERR_INVALID                        # and needs two operands
+    assert lib.tvk_logical(capi.L_NOT, None, None, None, 0, None) == capi.OK
+
+
 CHILD = textwrap.dedent(
     """
     import ctypes as C, sys

@@ -94,6 +94,12 @@ class Conv2dDesc(C.Structure):
 CONV_X_CHANNELS_LAST, CONV_Y_CHANNELS_LAST, CONV_W_CHANNELS_LAST = 1, 2, 4
 
 
+class Pool2dDesc(C.Structure):
+    _fields_ = [("dtype", C.c_int32)] + [(n, C.c_int64) for n in (
+        "planes", "h", "w", "ho", "wo", "kh", "kw", "stride_h", "stride_w", "pad_h", "pad_w", "dilation_h", "dilation_w")] + [
+        ("count_include_pad", C.c_int32), ("divisor_override", C.c_int64)]
+
+
 class Iter(C.Structure):
     _fields_ = [("ndim", C.c_int32), ("noperands", C.c_int32), ("sizes", C.c_int64 * MAX_DIMS),
                 ("strides", (C.c_int64 * MAX_DIMS) * 4)]
