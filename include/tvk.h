@@ -339,6 +339,7 @@ typedef enum tvk_unary_op {
     TVK_U_LOG2, TVK_U_LOG10, TVK_U_LOG1P, TVK_U_EXPM1, TVK_U_EXP2,
     TVK_U_TAN, TVK_U_SINH, TVK_U_COSH, TVK_U_ASIN, TVK_U_ACOS, TVK_U_ATAN, TVK_U_ERF, TVK_U_ERFC,
     TVK_U_HARDSIGMOID, TVK_U_HARDSWISH, TVK_U_MISH, TVK_U_LOGSIGMOID,
+    TVK_U_ASINH, TVK_U_ACOSH, TVK_U_ATANH, TVK_U_ERFINV, TVK_U_LGAMMA, TVK_U_FRAC, TVK_U_SINC,
     TVK_U_COUNT_
 } tvk_unary_op;
 
@@ -368,6 +369,9 @@ typedef enum tvk_binary_op {
     TVK_B_ELU_BACKWARD,          /* alpha as in the forward, b = the input                   */
     TVK_B_HARDSWISH_BACKWARD, TVK_B_HARDSIGMOID_BACKWARD, TVK_B_MISH_BACKWARD, TVK_B_LOGSIGMOID_BACKWARD,
     TVK_B_SOFTPLUS_BACKWARD,     /* beta = alpha, threshold 20                               */
+    TVK_B_HYPOT, TVK_B_COPYSIGN, TVK_B_LOGADDEXP, TVK_B_LOGADDEXP2,
+    TVK_B_FMAX, TVK_B_FMIN,      /* maximum / minimum that ignore a NaN operand              */
+    TVK_B_HEAVISIDE,             /* a < 0 ? 0 : a > 0 ? 1 : b                                */
     TVK_B_COUNT_
 } tvk_binary_op;
 

@@ -40,6 +40,10 @@ UNARY = {
     "erf": (torch.erf, 2.0), "erfc": (torch.erfc, 1.5), "hardsigmoid": (F.hardsigmoid, 4.0), "hardswish": (F.hardswish, 4.0), "mish": (F.mish, 4.0),
     "logsigmoid": (F.logsigmoid, 4.0), "isnan": (torch.isnan, 1.0), "isinf": (torch.isinf, 1.0), "isfinite": (torch.isfinite, 1.0),
     "isposinf": (torch.isposinf, 1.0), "isneginf": (torch.isneginf, 1.0),
+    "asinh": (torch.asinh, 4.0), "acosh": (lambda t: torch.acosh(t.abs() + 1.0), 4.0), "atanh": (lambda t: torch.atanh(t.clamp(-0.95, 0.95)), 0.6),
+    "erfinv": (lambda t: torch.erfinv(t.clamp(-0.98, 0.98)), 0.6), "lgamma": (lambda t: torch.lgamma(t.abs() + 0.5), 3.0), "frac": (torch.frac, 4.0), "sinc": (torch.sinc, 2.0),
+    "nan_to_num": (lambda t: torch.nan_to_num(t, nan=0.5), 1.0), "nan_to_num_args": (lambda t: torch.nan_to_num(t, nan=0.0, posinf=9.0, neginf=-9.0), 1.0),
+    "softshrink": (lambda t: F.softshrink(t, 0.4), 2.0), "count_nonzero": (lambda t: torch.count_nonzero(t.round(), dim=1), 1.0),
     "clamp": (lambda t: t.clamp(-1.0, 0.5), 2.0), "clamp_min": (lambda t: t.clamp_min(0.25), 2.0), "clamp_max": (lambda t: t.clamp(max=0.25), 2.0),
     "relu6": (F.relu6, 5.0), "hardtanh": (lambda t: F.hardtanh(t, -0.5, 1.5), 2.0), "leaky_relu": (lambda t: F.leaky_relu(t, 0.1), 2.0),
     "elu": (lambda t: F.elu(t, 1.3), 2.0), "softplus": (lambda t: F.softplus(t, 2.0), 6.0), "selu": (F.selu, 2.0), "celu": (lambda t: F.celu(t, 0.7), 2.0),
@@ -53,7 +57,7 @@ def test_unary_surface(vk, name, dtype):
     fn, spread = UNARY[name]
     g = torch.Generator().manual_seed(3)
     x = (torch.randn(37, 53, generator=g) * spread).to(dtype)
-    if name.startswith("is") or name.startswith("clamp"):
+    if name.startswith("is") or name.startswith("clamp") or name.startswith("nan_to_num"):
         x[3, 5], x[4, 6], x[5, 7] = float("nan"), float("inf"), float("-inf")
     tol = 2e-5 if dtype == torch.float32 else 1e-2
     _close(fn(x.to(vk)), fn(x), tol)
@@ -85,6 +89,8 @@ def test_elu_in_place_gradient_from_the_result(vk):
 
 BINARY = {
     "fmod": torch.fmod, "remainder": torch.remainder, "atan2": torch.atan2, "floor_divide": torch.floor_divide,
+    "hypot": torch.hypot, "copysign": torch.copysign, "logaddexp": torch.logaddexp, "logaddexp2": torch.logaddexp2, "fmax": torch.fmax, "fmin": torch.fmin,
+    "heaviside": lambda a, b: torch.heaviside(a.round(), b),
     "fmod_scalar": lambda a, b: a.fmod(1.5), "remainder_scalar": lambda a, b: a % -1.5, "floor_divide_scalar": lambda a, b: a // 0.75,
 }
 
@@ -723,3 +729,14 @@ def test_new_operators_on_empty_tensors(vk):
         assert got.shape == want.shape and got.dtype == want.dtype
     assert float(e.to(vk).sum().cpu()) == 0.0 and int((e.to(vk) > 0).sum().cpu()) == 0 and not bool((e.to(vk) > 0).any().cpu())
     assert torch.ones(3, 4).to(vk)[none.to(vk)].shape == (0, 4)
+
+
+def test_index_fill_and_nan_aware_extrema(vk):
+    x = torch.randn(5, 7)
+    idx = torch.tensor([6, 0, 0])
+    _close(x.to(vk).index_fill(1, idx.to(vk), -3.0), x.index_fill(1, idx, -3.0), 0)
+    a = torch.tensor([1.0, float("nan"), 3.0, float("nan")]); b = torch.tensor([2.0, 5.0, float("nan"), float("nan")])
+    _close(torch.fmax(a.to(vk), b.to(vk)), torch.fmax(a, b), 0)
+    _close(torch.fmin(a.to(vk), b.to(vk)), torch.fmin(a, b), 0)
+    _close(torch.logaddexp(torch.tensor([float("-inf"), 1.0]).to(vk), torch.tensor([float("-inf"), float("inf")]).to(vk)),
+           torch.logaddexp(torch.tensor([float("-inf"), 1.0]), torch.tensor([float("-inf"), float("inf")])), 0)

@@ -391,9 +391,56 @@ at::Tensor upsample_bilinear2d_backward(const at::Tensor& grad, at::IntArrayRef 
     return blend_axis_backward(blend_axis_backward(grad, 3, w, input_size[3]), 2, h, input_size[2]);
 }
 
+// nan_to_num: NaN -> nan (0), +inf -> posinf (the dtype's largest value), -inf -> neginf (its lowest)
+at::Tensor vk_nan_to_num(const at::Tensor& self, c10::optional<double> nan, c10::optional<double> posinf, c10::optional<double> neginf) {
+    TORCH_CHECK(is_hot_float(self.scalar_type()), "torchvulkan [NOT IMPLEMENTED]: nan_to_num for ", self.scalar_type());
+    const double top = self.scalar_type() == at::kHalf ? 65504.0 : (self.scalar_type() == at::kBFloat16 ? 3.3895313892515355e38 : 3.4028234663852886e38);
+    auto constant = [&](double v) { at::Tensor t = at::empty({}, self.options()); t.fill_(v); return t; };
+    at::Tensor r = at::where(at::isnan(self), constant(nan.value_or(0.0)), self);
+    r = at::where(at::eq(self, std::numeric_limits<double>::infinity()), constant(posinf.value_or(top)), r);
+    return at::where(at::eq(self, -std::numeric_limits<double>::infinity()), constant(neginf.value_or(-top)), r);
+}
+at::Tensor& nan_to_num_out(const at::Tensor& self, c10::optional<double> nan, c10::optional<double> posinf, c10::optional<double> neginf, at::Tensor& out) {
+    return into(out, vk_nan_to_num(self, nan, posinf, neginf));
+}
+at::Tensor& nan_to_num_(at::Tensor& self, c10::optional<double> nan, c10::optional<double> posinf, c10::optional<double> neginf) {
+    self.copy_(vk_nan_to_num(self, nan, posinf, neginf));
+    return self;
+}
+at::Tensor count_nonzero(const at::Tensor& self, at::IntArrayRef dims) {
+    at::Tensor nz = self.scalar_type() == at::kBool ? self : at::ne(self, 0);
+    return dims.empty() ? nz.sum() : nz.sum(dims);
+}
+// softshrink(x) = x > l ? x - l : x < -l ? x + l : 0
+at::Tensor softshrink(const at::Tensor& self, const at::Scalar& lambd) {
+    at::Tensor zero = at::zeros({}, self.options());
+    return at::where(at::gt(self, lambd), self - lambd, at::where(at::lt(self, -lambd.toDouble()), self + lambd, zero));
+}
+at::Tensor softshrink_backward(const at::Tensor& grad, const at::Tensor& self, const at::Scalar& lambd) {
+    return at::where(at::gt(at::abs(self), lambd), grad, at::zeros({}, grad.options()));
+}
+// index_fill: the slices named by index along dim take one value
+at::Tensor& index_fill_scalar_(at::Tensor& self, int64_t dim, const at::Tensor& index, const at::Scalar& value) {
+    dim = at::maybe_wrap_dim(dim, std::max<int64_t>(self.dim(), 1));
+    TORCH_CHECK(self.dim() > 0 && index.dim() <= 1, "index_fill_(): expected a tensor with dimensions and a vector of indices");
+    if (index.numel() == 0) return self;
+    at::Tensor hits = at::zeros({self.size(dim)}, self.options().dtype(at::kFloat)).index_add(0, index.reshape({-1}), at::ones({index.numel()}, self.options().dtype(at::kFloat)));
+    std::vector<int64_t> view(self.dim(), 1);
+    view[dim] = self.size(dim);
+    self.masked_fill_(at::gt(hits, 0).view(view), value);
+    return self;
+}
+
 }  // namespace
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+    m.impl("nan_to_num", &vk_nan_to_num);
+    m.impl("nan_to_num.out", &nan_to_num_out);
+    m.impl("nan_to_num_", &nan_to_num_);
+    m.impl("count_nonzero.dim_IntList", &count_nonzero);
+    m.impl("softshrink", &softshrink);
+    m.impl("softshrink_backward", &softshrink_backward);
+    m.impl("index_fill_.int_Scalar", &index_fill_scalar_);
     m.impl("binary_cross_entropy", &bce);
     m.impl("binary_cross_entropy_backward", &bce_backward);
     m.impl("_adaptive_avg_pool2d", &adaptive_avg_pool2d);

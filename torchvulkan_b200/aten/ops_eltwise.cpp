@@ -616,6 +616,22 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     REG_UNARY(m, "hardsigmoid", TVK_U_HARDSIGMOID);
     REG_UNARY(m, "hardswish", TVK_U_HARDSWISH);
     REG_UNARY(m, "mish", TVK_U_MISH);
+    REG_UNARY(m, "asinh", TVK_U_ASINH);
+    REG_UNARY(m, "acosh", TVK_U_ACOSH);
+    REG_UNARY(m, "atanh", TVK_U_ATANH);
+    REG_UNARY(m, "erfinv", TVK_U_ERFINV);
+    REG_UNARY(m, "lgamma", TVK_U_LGAMMA);
+    REG_UNARY(m, "frac", TVK_U_FRAC);
+    REG_UNARY(m, "sinc", TVK_U_SINC);
+    REG_BINARY(m, "hypot", TVK_B_HYPOT, false);
+    REG_BINARY(m, "logaddexp", TVK_B_LOGADDEXP, false);
+    REG_BINARY(m, "logaddexp2", TVK_B_LOGADDEXP2, false);
+    REG_BINARY(m, "fmax", TVK_B_FMAX, false);
+    REG_BINARY(m, "fmin", TVK_B_FMIN, false);
+    REG_BINARY(m, "heaviside", TVK_B_HEAVISIDE, false);
+    m.impl("copysign.Tensor", &bin_fn<TVK_B_COPYSIGN, false>);
+    m.impl("copysign_.Tensor", &bin_fn_<TVK_B_COPYSIGN, false>);
+    m.impl("copysign.out", &bin_out<TVK_B_COPYSIGN, false>);
     m.impl("fmod.Tensor", &bin_fn<TVK_B_FMOD, true>);
     m.impl("fmod_.Tensor", &bin_fn_<TVK_B_FMOD, true>);
     m.impl("fmod.Tensor_out", &bin_out<TVK_B_FMOD, true>);

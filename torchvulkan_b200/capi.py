@@ -17,11 +17,11 @@ F32, F16, BF16, I64, I32, U8, F64 = range(7)
 ACT_NONE, ACT_RELU, ACT_GELU = range(3)
 (U_NEG, U_EXP, U_LOG, U_SQRT, U_RSQRT, U_SIGMOID, U_RELU, U_GELU, U_TANH, U_ABS, U_SILU, U_RECIPROCAL, U_SQUARE,
  U_SIN, U_COS, U_GELU_TANH, U_FLOOR, U_CEIL, U_ROUND, U_TRUNC, U_SIGN, U_LOG2, U_LOG10, U_LOG1P, U_EXPM1, U_EXP2, U_TAN, U_SINH, U_COSH, U_ASIN, U_ACOS,
- U_ATAN, U_ERF, U_ERFC, U_HARDSIGMOID, U_HARDSWISH, U_MISH, U_LOGSIGMOID) = range(38)
+ U_ATAN, U_ERF, U_ERFC, U_HARDSIGMOID, U_HARDSWISH, U_MISH, U_LOGSIGMOID, U_ASINH, U_ACOSH, U_ATANH, U_ERFINV, U_LGAMMA, U_FRAC, U_SINC) = range(45)
 (B_ADD, B_SUB, B_MUL, B_DIV, B_MAXIMUM, B_MINIMUM, B_POW, B_GELU_BACKWARD, B_THRESHOLD_BACKWARD, B_SILU_BACKWARD,
  B_SIGMOID_BACKWARD, B_TANH_BACKWARD, B_GELU_TANH_BACKWARD, B_ADD_RELU, B_FMOD, B_REMAINDER, B_ATAN2, B_FLOOR_DIVIDE, B_CLAMP, B_LEAKY_RELU, B_ELU,
  B_SOFTPLUS, B_LEAKY_RELU_BACKWARD, B_ELU_BACKWARD, B_HARDSWISH_BACKWARD, B_HARDSIGMOID_BACKWARD, B_MISH_BACKWARD, B_LOGSIGMOID_BACKWARD,
- B_SOFTPLUS_BACKWARD) = range(29)
+ B_SOFTPLUS_BACKWARD, B_HYPOT, B_COPYSIGN, B_LOGADDEXP, B_LOGADDEXP2, B_FMAX, B_FMIN, B_HEAVISIDE) = range(36)
 (L_AND, L_OR, L_XOR, L_NOT) = range(4)
 C_EQ, C_NE, C_LT, C_LE, C_GT, C_GE = range(6)
 T_ADDCMUL, T_ADDCDIV, T_LERP, T_WHERE = range(4)

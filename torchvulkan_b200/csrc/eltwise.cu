@@ -51,6 +51,13 @@ template <int OP> __device__ __forceinline__ float unary_apply(float x) {
     else if constexpr (OP == TVK_U_HARDSWISH) return x * fminf(fmaxf(x + 3.0f, 0.0f), 6.0f) / 6.0f;
     else if constexpr (OP == TVK_U_MISH) return x * tanhf(x > 20.0f ? x : log1pf(expf(x)));
     else if constexpr (OP == TVK_U_LOGSIGMOID) return fminf(x, 0.0f) - log1pf(expf(-fabsf(x)));
+    else if constexpr (OP == TVK_U_ASINH) return asinhf(x);
+    else if constexpr (OP == TVK_U_ACOSH) return acoshf(x);
+    else if constexpr (OP == TVK_U_ATANH) return atanhf(x);
+    else if constexpr (OP == TVK_U_ERFINV) return erfinvf(x);
+    else if constexpr (OP == TVK_U_LGAMMA) return lgammaf(x);
+    else if constexpr (OP == TVK_U_FRAC) return x - truncf(x);
+    else if constexpr (OP == TVK_U_SINC) return x == 0.0f ? 1.0f : sinpif(x) / (3.14159265358979323846f * x);
     else return x;
 }
 
@@ -108,7 +115,20 @@ template <int OP> __device__ __forceinline__ float binary_apply(float a, float b
     else if constexpr (OP == TVK_B_SOFTPLUS_BACKWARD) {
         const float z = expf(b * alpha);
         return (b * alpha > 20.0f) ? a : a * z / (z + 1.0f);
-    } else return a;
+    } else if constexpr (OP == TVK_B_HYPOT) return hypotf(a, b);
+    else if constexpr (OP == TVK_B_COPYSIGN) return copysignf(a, b);
+    else if constexpr (OP == TVK_B_LOGADDEXP) {
+        if (isinf(a) && a == b) return a;                            // inf - inf would be NaN
+        const float mx = fmaxf(a, b), mn = fminf(a, b);
+        return (a != a || b != b) ? a + b : mx + log1pf(expf(mn - mx));
+    } else if constexpr (OP == TVK_B_LOGADDEXP2) {
+        if (isinf(a) && a == b) return a;
+        const float mx = fmaxf(a, b), mn = fminf(a, b);
+        return (a != a || b != b) ? a + b : mx + log1pf(exp2f(mn - mx)) * 1.4426950408889634f;
+    } else if constexpr (OP == TVK_B_FMAX) return fmaxf(a, b);
+    else if constexpr (OP == TVK_B_FMIN) return fminf(a, b);
+    else if constexpr (OP == TVK_B_HEAVISIDE) return (a != a) ? a : (a < 0.0f ? 0.0f : (a > 0.0f ? 1.0f : b));
+    else return a;
 }
 
 template <typename T> struct CmpVal { using type = float; static __device__ __forceinline__ float get(T v) { return to_f32(v); } };
@@ -653,6 +673,7 @@ template <typename F> static int dispatch_unary_op(int op, F&& f) {
         C(TVK_U_FLOOR) C(TVK_U_CEIL) C(TVK_U_ROUND) C(TVK_U_TRUNC) C(TVK_U_SIGN) C(TVK_U_LOG2) C(TVK_U_LOG10) C(TVK_U_LOG1P) C(TVK_U_EXPM1) C(TVK_U_EXP2)
         C(TVK_U_TAN) C(TVK_U_SINH) C(TVK_U_COSH) C(TVK_U_ASIN) C(TVK_U_ACOS) C(TVK_U_ATAN) C(TVK_U_ERF) C(TVK_U_ERFC)
         C(TVK_U_HARDSIGMOID) C(TVK_U_HARDSWISH) C(TVK_U_MISH) C(TVK_U_LOGSIGMOID)
+        C(TVK_U_ASINH) C(TVK_U_ACOSH) C(TVK_U_ATANH) C(TVK_U_ERFINV) C(TVK_U_LGAMMA) C(TVK_U_FRAC) C(TVK_U_SINC)
 #undef C
         default: return set_error(TVK_ERR_INVALID, "unknown unary op %d", op);
     }
@@ -666,6 +687,7 @@ template <typename F> static int dispatch_binary_op(int op, F&& f) {
         C(TVK_B_FMOD) C(TVK_B_REMAINDER) C(TVK_B_ATAN2) C(TVK_B_FLOOR_DIVIDE) C(TVK_B_CLAMP) C(TVK_B_LEAKY_RELU) C(TVK_B_ELU) C(TVK_B_SOFTPLUS)
         C(TVK_B_LEAKY_RELU_BACKWARD) C(TVK_B_ELU_BACKWARD) C(TVK_B_HARDSWISH_BACKWARD) C(TVK_B_HARDSIGMOID_BACKWARD) C(TVK_B_MISH_BACKWARD)
         C(TVK_B_LOGSIGMOID_BACKWARD) C(TVK_B_SOFTPLUS_BACKWARD)
+        C(TVK_B_HYPOT) C(TVK_B_COPYSIGN) C(TVK_B_LOGADDEXP) C(TVK_B_LOGADDEXP2) C(TVK_B_FMAX) C(TVK_B_FMIN) C(TVK_B_HEAVISIDE)
 #undef C
         default: return set_error(TVK_ERR_INVALID, "unknown binary op %d", op);
     }
