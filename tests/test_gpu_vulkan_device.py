@@ -1026,3 +1026,30 @@ def test_recurrent_transformer_and_padding_modules_match_cpu(vk):
     for red in ("mean", "sum", "none"):
         _module_matches_cpu(vk, lambda: torch.nn.Conv2d(8, 8, 1), [img],
                             loss=lambda o, red=red: F.cross_entropy(o, tgt.to(o.device), reduction=red, ignore_index=-100).sum())
+
+
+def test_unfold_fold_embedding_renorm_and_triangle_indices(vk):
+    g = torch.Generator().manual_seed(6)
+    img = torch.randn(2, 3, 9, 8, generator=g)
+    for kw in (dict(kernel_size=3), dict(kernel_size=(3, 2), stride=2, padding=1), dict(kernel_size=2, dilation=2, padding=(1, 0), stride=(1, 2))):
+        xd, xc = img.to(vk).requires_grad_(), img.clone().requires_grad_()
+        cd, cc = F.unfold(xd, **kw), F.unfold(xc, **kw)
+        assert rel_fro(cd.detach().cpu().double().numpy(), cc.detach().double().numpy()) == 0.0
+        gy = torch.randn(cc.shape, generator=g)
+        cd.backward(gy.to(vk)); cc.backward(gy)
+        assert rel_fro(xd.grad.cpu().double().numpy(), xc.grad.double().numpy()) <= 1e-6
+        fd, fc = F.fold(gy.to(vk), (9, 8), **kw), F.fold(gy, (9, 8), **kw)
+        assert rel_fro(fd.cpu().double().numpy(), fc.double().numpy()) <= 1e-6
+    torch.manual_seed(0)
+    emb_c = torch.nn.Embedding(12, 6, max_norm=1.0)
+    emb_d = torch.nn.Embedding(12, 6, max_norm=1.0)
+    emb_d.load_state_dict(emb_c.state_dict())
+    emb_d = emb_d.to(vk)
+    ids = torch.tensor([[1, 5, 5], [9, 0, 1]])
+    out_d, out_c = emb_d(ids.to(vk)), emb_c(ids)
+    assert rel_fro(out_d.detach().cpu().double().numpy(), out_c.detach().double().numpy()) <= 1e-6
+    assert rel_fro(emb_d.weight.detach().cpu().double().numpy(), emb_c.weight.detach().double().numpy()) <= 1e-6   # only the rows that were looked up shrank
+    m = torch.randn(5, 5, generator=g)
+    assert abs(float(m.to(vk).trace().cpu()) - float(m.trace())) < 1e-5
+    assert torch.equal(torch.tril_indices(4, 5, -1, device=vk).cpu(), torch.tril_indices(4, 5, -1))
+    assert torch.equal(torch.triu_indices(4, 5, 1, device=vk).cpu(), torch.triu_indices(4, 5, 1))

@@ -142,6 +142,84 @@ std::tuple<at::Tensor, at::Tensor> weight_norm_interface_backward(const at::Tens
     return {grad_v, grad_g};
 }
 
+// ---- F.unfold / F.fold: patches as columns. Each spatial axis is a gather with the index vector (tap, output position) ->
+// padded input position; the adjoint adds the columns back. [N, C, H, W] <-> [N, C * kh * kw, Ho * Wo] ------------------
+struct PatchAxis {
+    int64_t out, padded;
+    at::Tensor index;           // [k * out] positions in the padded axis
+};
+PatchAxis patch_axis(int64_t in, int64_t k, int64_t dil, int64_t pad, int64_t stride, const at::Device& dev) {
+    PatchAxis a;
+    a.padded = in + 2 * pad;
+    a.out = (a.padded - dil * (k - 1) - 1) / stride + 1;
+    TORCH_CHECK(a.out > 0, "im2col / col2im: the sliding blocks do not fit the padded input");
+    std::vector<int64_t> idx((size_t)(k * a.out));
+    for (int64_t t = 0; t < k; ++t)
+        for (int64_t o = 0; o < a.out; ++o) idx[(size_t)(t * a.out + o)] = o * stride + t * dil;
+    a.index = at::tensor(idx, at::TensorOptions().dtype(at::kLong)).to(dev);
+    return a;
+}
+std::array<int64_t, 2> pair2(at::IntArrayRef v, const char* what) {
+    TORCH_CHECK(v.size() == 1 || v.size() == 2, "im2col / col2im: ", what, " must have one or two values");
+    return {v[0], v.size() == 1 ? v[0] : v[1]};
+}
+at::Tensor im2col(const at::Tensor& self, at::IntArrayRef kernel, at::IntArrayRef dilation, at::IntArrayRef padding, at::IntArrayRef stride) {
+    TORCH_CHECK(self.dim() == 3 || self.dim() == 4, "im2col: expected a 3-D or 4-D input");
+    at::Tensor x = self.dim() == 3 ? self.unsqueeze(0) : self;
+    const auto k = pair2(kernel, "kernel_size"), d = pair2(dilation, "dilation"), p = pair2(padding, "padding"), st = pair2(stride, "stride");
+    const int64_t N = x.size(0), C = x.size(1);
+    const PatchAxis h = patch_axis(x.size(2), k[0], d[0], p[0], st[0], x.device()), w = patch_axis(x.size(3), k[1], d[1], p[1], st[1], x.device());
+    at::Tensor xp = (p[0] || p[1]) ? at::constant_pad_nd(x, {p[1], p[1], p[0], p[0]}, 0) : x;
+    at::Tensor g = at::index_select(at::index_select(xp, 2, h.index), 3, w.index);              // [N, C, kh*Ho, kw*Wo]
+    g = g.reshape({N, C, k[0], h.out, k[1], w.out}).permute({0, 1, 2, 4, 3, 5});                // [N, C, kh, kw, Ho, Wo]
+    at::Tensor cols = contiguous_vulkan(g).reshape({N, C * k[0] * k[1], h.out * w.out});
+    return self.dim() == 3 ? cols.squeeze(0) : cols;
+}
+at::Tensor col2im(const at::Tensor& self, c10::SymIntArrayRef output_size, at::IntArrayRef kernel, at::IntArrayRef dilation, at::IntArrayRef padding,
+                  at::IntArrayRef stride) {
+    TORCH_CHECK((self.dim() == 2 || self.dim() == 3) && output_size.size() == 2, "col2im: expected a 2-D or 3-D input and two output sizes");
+    at::Tensor cols = self.dim() == 2 ? self.unsqueeze(0) : self;
+    const auto k = pair2(kernel, "kernel_size"), d = pair2(dilation, "dilation"), p = pair2(padding, "padding"), st = pair2(stride, "stride");
+    const int64_t H = output_size[0].guard_int(__FILE__, __LINE__), W = output_size[1].guard_int(__FILE__, __LINE__);
+    const int64_t N = cols.size(0), C = cols.size(1) / (k[0] * k[1]);
+    const PatchAxis h = patch_axis(H, k[0], d[0], p[0], st[0], cols.device()), w = patch_axis(W, k[1], d[1], p[1], st[1], cols.device());
+    TORCH_CHECK(cols.size(1) == C * k[0] * k[1] && cols.size(2) == h.out * w.out, "col2im: the input does not fit output_size and the sliding blocks");
+    at::Tensor g = contiguous_vulkan(cols.reshape({N, C, k[0], k[1], h.out, w.out}).permute({0, 1, 2, 4, 3, 5})).reshape({N, C, k[0] * h.out, k[1] * w.out});
+    at::Tensor gw = at::zeros({N, C, k[0] * h.out, w.padded}, cols.options()).index_add(3, w.index, g);
+    at::Tensor gh = at::zeros({N, C, h.padded, w.padded}, cols.options()).index_add(2, h.index, gw);
+    at::Tensor out = contiguous_vulkan(gh.narrow(2, p[0], H).narrow(3, p[1], W));
+    return self.dim() == 2 ? out.squeeze(0) : out;
+}
+
+// embedding rows named by `indices` whose p-norm exceeds max_norm are scaled down to it (nn.Embedding(max_norm=...))
+at::Tensor& embedding_renorm_(at::Tensor& self, const at::Tensor& indices, double max_norm, double norm_type) {
+    TORCH_CHECK(self.dim() == 2, "embedding_renorm_: the weight must be 2-D");
+    if (indices.numel() == 0) return self;
+    at::Tensor hits = at::zeros({self.size(0)}, self.options().dtype(at::kFloat)).index_add(0, indices.reshape({-1}), at::ones({indices.numel()}, self.options().dtype(at::kFloat)));
+    at::Tensor norms = at::linalg_vector_norm(self, norm_type, at::IntArrayRef({1}), false, at::kFloat);
+    at::Tensor over = at::logical_and(at::gt(hits, 0), at::gt(norms, max_norm));
+    at::Tensor scale = at::where(over, max_norm / (norms + 1e-7), at::ones({}, norms.options()));
+    self.mul_(scale.to(self.scalar_type()).unsqueeze(1));
+    return self;
+}
+at::Tensor trace(const at::Tensor& self) {
+    TORCH_CHECK(self.dim() == 2, "trace: expected a matrix");
+    return self.diagonal().sum();
+}
+at::Tensor tri_indices(int64_t row, int64_t col, int64_t offset, bool lower, c10::optional<at::ScalarType> dtype, const c10::optional<at::Device>& device) {
+    at::TensorOptions host = at::TensorOptions().dtype(dtype.value_or(at::kLong)).device(at::kCPU);
+    at::Tensor t = lower ? at::tril_indices(row, col, offset, host) : at::triu_indices(row, col, offset, host);
+    return device.has_value() ? t.to(*device) : t;
+}
+at::Tensor tril_indices(int64_t row, int64_t col, int64_t offset, c10::optional<at::ScalarType> dtype, c10::optional<at::Layout>, c10::optional<at::Device> device,
+                        c10::optional<bool>) {
+    return tri_indices(row, col, offset, true, dtype, device);
+}
+at::Tensor triu_indices(int64_t row, int64_t col, int64_t offset, c10::optional<at::ScalarType> dtype, c10::optional<at::Layout>, c10::optional<at::Device> device,
+                        c10::optional<bool>) {
+    return tri_indices(row, col, offset, false, dtype, device);
+}
+
 at::Tensor vdot(const at::Tensor& a, const at::Tensor& b) { return at::dot(a, b); }                 // real tensors: no conjugate
 at::Tensor& where_self_out(const at::Tensor& cond, const at::Tensor& a, const at::Tensor& b, at::Tensor& out) {
     at::Tensor r = at::where(cond, a, b);
@@ -169,6 +247,12 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("replication_pad2d_backward", &replication_pad_backward);
     m.impl("_weight_norm_interface", &weight_norm_interface);
     m.impl("_weight_norm_interface_backward", &weight_norm_interface_backward);
+    m.impl("im2col", &im2col);
+    m.impl("col2im", &col2im);
+    m.impl("embedding_renorm_", &embedding_renorm_);
+    m.impl("trace", &trace);
+    m.impl("tril_indices", &tril_indices);
+    m.impl("triu_indices", &triu_indices);
     m.impl("vdot", &vdot);
     m.impl("where.self_out", &where_self_out);
 }
