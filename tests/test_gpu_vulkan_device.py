@@ -1053,3 +1053,22 @@ def test_unfold_fold_embedding_renorm_and_triangle_indices(vk):
     assert abs(float(m.to(vk).trace().cpu()) - float(m.trace())) < 1e-5
     assert torch.equal(torch.tril_indices(4, 5, -1, device=vk).cpu(), torch.tril_indices(4, 5, -1))
     assert torch.equal(torch.triu_indices(4, 5, 1, device=vk).cpu(), torch.triu_indices(4, 5, 1))
+
+
+@pytest.mark.parametrize("mode,padding_mode,align", [("bilinear", "zeros", False), ("bilinear", "zeros", True), ("bilinear", "border", False), ("nearest", "zeros", False)])
+def test_grid_sample(vk, mode, padding_mode, align):
+    """F.grid_sample (2-D) on the device against ATen CPU: output, the gradient of the input and, for bilinear sampling, of
+    the grid; sampling positions reach outside the image."""
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(2, 3, 7, 6, generator=g)
+    grid = torch.rand(2, 5, 4, 2, generator=g) * 2.6 - 1.3
+    xd, xc = x.to(vk).requires_grad_(), x.clone().requires_grad_()
+    gd, gc = grid.to(vk).requires_grad_(), grid.clone().requires_grad_()
+    yd = F.grid_sample(xd, gd, mode=mode, padding_mode=padding_mode, align_corners=align)
+    yc = F.grid_sample(xc, gc, mode=mode, padding_mode=padding_mode, align_corners=align)
+    assert rel_fro(yd.detach().cpu().double().numpy(), yc.detach().double().numpy()) <= 1e-5
+    gy = torch.randn(yc.shape, generator=g)
+    yd.backward(gy.to(vk)); yc.backward(gy)
+    assert rel_fro(xd.grad.cpu().double().numpy(), xc.grad.double().numpy()) <= 1e-5
+    if mode == "bilinear":
+        assert rel_fro(gd.grad.cpu().double().numpy(), gc.grad.double().numpy()) <= 1e-4

@@ -220,6 +220,106 @@ at::Tensor triu_indices(int64_t row, int64_t col, int64_t offset, c10::optional<
     return tri_indices(row, col, offset, false, dtype, device);
 }
 
+// ---- F.grid_sample, 2-D, bilinear or nearest, zeros or border padding ------------------------------------------------------
+// Sampling positions are turned into flat pixel offsets and corner weights with elementwise launches; the corner values are
+// gathered from input viewed as [N, C, H*W] and the gradient with respect to the input is the scatter-add of the same
+// corners. Coordinates follow ATen's grid sampler: x in [-1, 1] maps to pixel centres (align_corners) or pixel edges.
+struct GridAxis {
+    at::Tensor pos;        // unnormalised (and, for border padding, clamped) coordinate, fp32 [N, P]
+    at::Tensor inside;     // border padding: 1 where the coordinate was not clamped (its derivative), else undefined
+    double scale;          // d pos / d grid
+};
+GridAxis grid_axis(const at::Tensor& g, int64_t size, bool align_corners, int64_t padding_mode) {
+    GridAxis a;
+    if (align_corners) { a.scale = 0.5 * (double)(size - 1); a.pos = (g + 1.0) * a.scale; }
+    else { a.scale = 0.5 * (double)size; a.pos = (g + 1.0) * a.scale - 0.5; }
+    if (padding_mode == 1) {
+        a.inside = at::logical_and(at::ge(a.pos, 0.0), at::le(a.pos, (double)(size - 1))).to(at::kFloat);
+        a.pos = at::clamp(a.pos, 0.0, (double)(size - 1));
+    }
+    return a;
+}
+struct Corner {
+    at::Tensor index, weight;      // [N, 1, P] Long flat offsets (clamped into the image) and fp32 weights (0 outside the image)
+};
+Corner make_corner(const at::Tensor& xi, const at::Tensor& yi, const at::Tensor& w, int64_t H, int64_t W) {
+    at::Tensor valid = at::logical_and(at::logical_and(at::ge(xi, 0.0), at::le(xi, (double)(W - 1))), at::logical_and(at::ge(yi, 0.0), at::le(yi, (double)(H - 1)))).to(at::kFloat);
+    at::Tensor xc = at::clamp(xi, 0.0, (double)(W - 1)), yc = at::clamp(yi, 0.0, (double)(H - 1));
+    Corner c;
+    c.index = (yc * (double)W + xc).to(at::kLong).unsqueeze(1);
+    c.weight = (w * valid).unsqueeze(1);
+    return c;
+}
+void check_grid_sampler(const at::Tensor& input, const at::Tensor& grid, int64_t interpolation_mode, int64_t padding_mode) {
+    TORCH_CHECK(input.dim() == 4 && grid.dim() == 4 && grid.size(3) == 2 && grid.size(0) == input.size(0), "grid_sampler_2d: expected input [N, C, H, W] and grid [N, Ho, Wo, 2]");
+    if (interpolation_mode > 1) TVK_NOT_IMPLEMENTED("grid_sample with bicubic interpolation");
+    if (padding_mode > 1) TVK_NOT_IMPLEMENTED("grid_sample with reflection padding");
+    if (!is_hot_float(input.scalar_type())) TVK_NOT_IMPLEMENTED("grid_sample for dtype ", input.scalar_type());
+}
+std::vector<Corner> grid_corners(const GridAxis& gx, const GridAxis& gy, int64_t H, int64_t W, bool nearest) {
+    if (nearest) {
+        at::Tensor one = at::ones({}, gx.pos.options());
+        return {make_corner(at::round(gx.pos), at::round(gy.pos), one.expand_as(gx.pos), H, W)};
+    }
+    at::Tensor x0 = at::floor(gx.pos), y0 = at::floor(gy.pos);
+    at::Tensor wx1 = gx.pos - x0, wy1 = gy.pos - y0, wx0 = 1.0 - wx1, wy0 = 1.0 - wy1;
+    return {make_corner(x0, y0, wx0 * wy0, H, W), make_corner(x0 + 1.0, y0, wx1 * wy0, H, W), make_corner(x0, y0 + 1.0, wx0 * wy1, H, W),
+            make_corner(x0 + 1.0, y0 + 1.0, wx1 * wy1, H, W)};
+}
+at::Tensor grid_sampler_2d(const at::Tensor& input, const at::Tensor& grid, int64_t interpolation_mode, int64_t padding_mode, bool align_corners) {
+    check_grid_sampler(input, grid, interpolation_mode, padding_mode);
+    const int64_t N = input.size(0), C = input.size(1), H = input.size(2), W = input.size(3), Ho = grid.size(1), Wo = grid.size(2), P = Ho * Wo;
+    at::Tensor g = grid.to(at::kFloat).reshape({N, P, 2});
+    const GridAxis gx = grid_axis(g.select(2, 0), W, align_corners, padding_mode), gy = grid_axis(g.select(2, 1), H, align_corners, padding_mode);
+    at::Tensor flat = contiguous_vulkan(input).reshape({N, C, H * W}).to(at::kFloat);
+    at::Tensor out;
+    for (const Corner& c : grid_corners(gx, gy, H, W, interpolation_mode == 1)) {
+        at::Tensor v = at::gather(flat, 2, c.index.expand({N, C, P})) * c.weight;
+        out = out.defined() ? out + v : v;
+    }
+    return out.reshape({N, C, Ho, Wo}).to(input.scalar_type());
+}
+std::tuple<at::Tensor, at::Tensor> grid_sampler_2d_backward(const at::Tensor& grad_output, const at::Tensor& input, const at::Tensor& grid, int64_t interpolation_mode,
+                                                             int64_t padding_mode, bool align_corners, std::array<bool, 2> output_mask) {
+    check_grid_sampler(input, grid, interpolation_mode, padding_mode);
+    const int64_t N = input.size(0), C = input.size(1), H = input.size(2), W = input.size(3), Ho = grid.size(1), Wo = grid.size(2), P = Ho * Wo;
+    at::Tensor g = grid.to(at::kFloat).reshape({N, P, 2});
+    const GridAxis gx = grid_axis(g.select(2, 0), W, align_corners, padding_mode), gy = grid_axis(g.select(2, 1), H, align_corners, padding_mode);
+    const bool nearest = interpolation_mode == 1;
+    const std::vector<Corner> corners = grid_corners(gx, gy, H, W, nearest);
+    at::Tensor go = grad_output.to(at::kFloat).reshape({N, C, P});
+    at::Tensor grad_input, grad_grid;
+    if (output_mask[0]) {
+        at::Tensor acc = at::zeros({N, C, H * W}, go.options());
+        for (const Corner& c : corners) acc = acc.scatter_add(2, c.index.expand({N, C, P}), go * c.weight);
+        grad_input = acc.reshape({N, C, H, W}).to(input.scalar_type());
+    }
+    if (output_mask[1]) {
+        if (nearest) {
+            grad_grid = at::zeros(grid.sizes(), grid.options());
+        } else {
+            // values of the four corners (0 outside the image), then d out / d x = sum_c go * ((v10 - v00) wy0 + (v11 - v01) wy1), likewise y
+            at::Tensor flat = contiguous_vulkan(input).reshape({N, C, H * W}).to(at::kFloat);
+            at::Tensor x0 = at::floor(gx.pos), y0 = at::floor(gy.pos);
+            at::Tensor wx1 = (gx.pos - x0).unsqueeze(1), wy1 = (gy.pos - y0).unsqueeze(1), wx0 = 1.0 - wx1, wy0 = 1.0 - wy1;
+            std::vector<at::Tensor> v;
+            for (const Corner& c : corners) {
+                // the corner's validity is its weight being a product of the fractional weights: recover the 0 / 1 mask from index clamping instead
+                v.push_back(at::gather(flat, 2, c.index.expand({N, C, P})));
+            }
+            // re-mask the values with each corner's validity (weight / unmasked weight is not safe at zero weights)
+            at::Tensor one = at::ones({}, gx.pos.options());
+            const at::Tensor xs[4] = {x0, x0 + 1.0, x0, x0 + 1.0}, ys[4] = {y0, y0, y0 + 1.0, y0 + 1.0};
+            for (int i = 0; i < 4; ++i) v[i] = v[i] * make_corner(xs[i], ys[i], one.expand_as(gx.pos), H, W).weight;
+            at::Tensor dx = (go * ((v[1] - v[0]) * wy0 + (v[3] - v[2]) * wy1)).sum(at::IntArrayRef({1})) * gx.scale;      // [N, P]
+            at::Tensor dy = (go * ((v[2] - v[0]) * wx0 + (v[3] - v[1]) * wx1)).sum(at::IntArrayRef({1})) * gy.scale;
+            if (padding_mode == 1) { dx = dx * gx.inside; dy = dy * gy.inside; }
+            grad_grid = at::stack({dx, dy}, 2).reshape(grid.sizes()).to(grid.scalar_type());
+        }
+    }
+    return {grad_input, grad_grid};
+}
+
 at::Tensor vdot(const at::Tensor& a, const at::Tensor& b) { return at::dot(a, b); }                 // real tensors: no conjugate
 at::Tensor& where_self_out(const at::Tensor& cond, const at::Tensor& a, const at::Tensor& b, at::Tensor& out) {
     at::Tensor r = at::where(cond, a, b);
@@ -247,6 +347,8 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("replication_pad2d_backward", &replication_pad_backward);
     m.impl("_weight_norm_interface", &weight_norm_interface);
     m.impl("_weight_norm_interface_backward", &weight_norm_interface_backward);
+    m.impl("grid_sampler_2d", &grid_sampler_2d);
+    m.impl("grid_sampler_2d_backward", &grid_sampler_2d_backward);
     m.impl("im2col", &im2col);
     m.impl("col2im", &col2im);
     m.impl("embedding_renorm_", &embedding_renorm_);
