@@ -1072,3 +1072,25 @@ def test_grid_sample(vk, mode, padding_mode, align):
     assert rel_fro(xd.grad.cpu().double().numpy(), xc.grad.double().numpy()) <= 1e-5
     if mode == "bilinear":
         assert rel_fro(gd.grad.cpu().double().numpy(), gc.grad.double().numpy()) <= 1e-4
+
+
+def test_cdist_bucketize_searchsorted(vk):
+    g = torch.Generator().manual_seed(9)
+    a, b = torch.randn(2, 5, 7, generator=g), torch.randn(2, 6, 7, generator=g)
+    ad, ac = a.to(vk).requires_grad_(), a.clone().requires_grad_()
+    bd, bc = b.to(vk).requires_grad_(), b.clone().requires_grad_()
+    dd, dc = torch.cdist(ad, bd), torch.cdist(ac, bc)
+    assert rel_fro(dd.detach().cpu().double().numpy(), dc.detach().double().numpy()) <= 1e-5
+    gy = torch.randn(dc.shape, generator=g)
+    dd.backward(gy.to(vk)); dc.backward(gy)
+    assert rel_fro(ad.grad.cpu().double().numpy(), ac.grad.double().numpy()) <= 1e-4 and rel_fro(bd.grad.cpu().double().numpy(), bc.grad.double().numpy()) <= 1e-4
+    for p in (1.0, float("inf"), 3.0):
+        assert rel_fro(torch.cdist(a.to(vk), b.to(vk), p=p).cpu().double().numpy(), torch.cdist(a, b, p=p).double().numpy()) <= 1e-5
+    codes = torch.randn(32, 7, generator=g)                                  # the nearest-code search of a vector quantiser
+    assert torch.equal(torch.cdist(a[0].to(vk), codes.to(vk)).argmin(1).cpu(), torch.cdist(a[0], codes).argmin(1))
+    bnd = torch.tensor([0.1, 0.5, 0.5, 2.0]); v = torch.tensor([[0.0, 0.1, 0.3], [0.5, 2.0, 3.0]])
+    seq = torch.sort(torch.randn(3, 8, generator=g), dim=1).values; q = torch.randn(3, 4, generator=g)
+    for right in (False, True):
+        assert torch.equal(torch.bucketize(v.to(vk), bnd.to(vk), right=right).cpu(), torch.bucketize(v, bnd, right=right))
+        assert torch.equal(torch.searchsorted(seq.to(vk), q.to(vk), right=right).cpu(), torch.searchsorted(seq, q, right=right))
+    assert torch.bucketize(v.to(vk), bnd.to(vk), out_int32=True).dtype == torch.int32

@@ -7,6 +7,8 @@
 // are private to the forward / backward pair of this backend.
 #include "common.h"
 
+#include <cmath>
+
 namespace tvk_aten {
 namespace {
 
@@ -320,6 +322,46 @@ std::tuple<at::Tensor, at::Tensor> grid_sampler_2d_backward(const at::Tensor& gr
     return {grad_input, grad_grid};
 }
 
+// ---- pairwise distances (torch.cdist, the nearest-codebook search of vector quantisers) ------------------------------------------
+// p = 2 through the matmul expansion |a|^2 + |b|^2 - 2 a.b (the large term is one tensor-core product); other p by broadcasting.
+at::Tensor cdist_forward(const at::Tensor& x1, const at::Tensor& x2, double p, c10::optional<int64_t>) {
+    TORCH_CHECK(x1.dim() >= 2 && x2.dim() >= 2 && x1.size(-1) == x2.size(-1), "cdist: expected two batches of row vectors of the same length");
+    if (p == 2.0) {
+        at::Tensor a2 = (x1 * x1).sum(at::IntArrayRef({-1}), true), b2 = (x2 * x2).sum(at::IntArrayRef({-1}), false).unsqueeze(-2);
+        return at::sqrt(at::clamp_min(a2 + b2 - at::matmul(x1, x2.transpose(-1, -2)) * 2.0, 0.0));
+    }
+    at::Tensor diff = at::abs(x1.unsqueeze(-2) - x2.unsqueeze(-3));
+    if (p == 1.0) return diff.sum(at::IntArrayRef({-1}));
+    if (std::isinf(p)) return at::amax(diff, {-1}, false);
+    if (p == 0.0) return at::ne(diff, 0).to(x1.scalar_type()).sum(at::IntArrayRef({-1}));
+    return at::pow(at::pow(diff, p).sum(at::IntArrayRef({-1})), 1.0 / p);
+}
+at::Tensor cdist_backward(const at::Tensor& grad, const at::Tensor& x1, const at::Tensor& x2, double p, const at::Tensor& cdist) {
+    if (p != 2.0) TVK_NOT_IMPLEMENTED("the gradient of cdist for p other than 2");
+    // d/dx1_i = sum_j grad_ij (x1_i - x2_j) / d_ij (0 where the distance is 0): x1 * rowsum(G) - G @ x2 with G = grad / d
+    at::Tensor G = at::where(at::gt(cdist, 0), grad / cdist, at::zeros({}, grad.options()));
+    return x1 * G.sum(at::IntArrayRef({-1}), true) - at::matmul(G, x2);
+}
+
+// bucketize / searchsorted: the insertion position is the number of boundaries below (right: not above) the value - a broadcast
+// comparison and an exact integer count. For boundary vectors of a few thousand entries.
+at::Tensor count_below(const at::Tensor& seq, const at::Tensor& values, bool right, bool out_int32) {
+    at::Tensor b = seq.unsqueeze(-2), v = values.unsqueeze(-1);
+    at::Tensor pos = (right ? at::le(b, v) : at::lt(b, v)).sum(at::IntArrayRef({-1}));
+    return out_int32 ? pos.to(at::kInt) : pos;
+}
+at::Tensor bucketize(const at::Tensor& self, const at::Tensor& boundaries, bool out_int32, bool right) {
+    TORCH_CHECK(boundaries.dim() == 1, "boundaries tensor must be 1 dimension, but got dim(", boundaries.dim(), ")");
+    return count_below(boundaries, self, right, out_int32);
+}
+at::Tensor searchsorted(const at::Tensor& sorted_sequence, const at::Tensor& self, bool out_int32, bool right, c10::optional<c10::string_view> side,
+                        const c10::optional<at::Tensor>& sorter) {
+    if (sorter.has_value() && sorter->defined()) TVK_NOT_IMPLEMENTED("searchsorted with a sorter");
+    const bool r = right || (side.has_value() && *side == "right");
+    TORCH_CHECK(sorted_sequence.dim() == 1 || sorted_sequence.dim() == self.dim(), "searchsorted: the sorted sequence must be 1-D or have the dimensions of the values");
+    return count_below(sorted_sequence, self, r, out_int32);
+}
+
 at::Tensor vdot(const at::Tensor& a, const at::Tensor& b) { return at::dot(a, b); }                 // real tensors: no conjugate
 at::Tensor& where_self_out(const at::Tensor& cond, const at::Tensor& a, const at::Tensor& b, at::Tensor& out) {
     at::Tensor r = at::where(cond, a, b);
@@ -349,6 +391,10 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("_weight_norm_interface_backward", &weight_norm_interface_backward);
     m.impl("grid_sampler_2d", &grid_sampler_2d);
     m.impl("grid_sampler_2d_backward", &grid_sampler_2d_backward);
+    m.impl("_cdist_forward", &cdist_forward);
+    m.impl("_cdist_backward", &cdist_backward);
+    m.impl("bucketize.Tensor", &bucketize);
+    m.impl("searchsorted.Tensor", &searchsorted);
     m.impl("im2col", &im2col);
     m.impl("col2im", &col2im);
     m.impl("embedding_renorm_", &embedding_renorm_);
