@@ -740,3 +740,20 @@ def test_index_fill_and_nan_aware_extrema(vk):
     _close(torch.fmin(a.to(vk), b.to(vk)), torch.fmin(a, b), 0)
     _close(torch.logaddexp(torch.tensor([float("-inf"), 1.0]).to(vk), torch.tensor([float("-inf"), float("inf")]).to(vk)),
            torch.logaddexp(torch.tensor([float("-inf"), 1.0]), torch.tensor([float("-inf"), float("inf")])), 0)
+
+
+def test_upsampling_in_one_and_three_dimensions(vk):
+    g = torch.Generator().manual_seed(24)
+    x1, x3 = torch.randn(2, 3, 9, generator=g), torch.randn(2, 3, 4, 5, 6, generator=g)
+
+    def both(x, **kw):
+        xd, xc = x.to(vk).requires_grad_(), x.double().requires_grad_()
+        yd, yc = F.interpolate(xd, **kw), F.interpolate(xc, **kw)
+        _close(yd.double(), yc, 1e-5)
+        gy = torch.randn(yc.shape, generator=g)
+        yd.backward(gy.to(vk)); yc.backward(gy.double())
+        _close(xd.grad.double(), xc.grad, 1e-5)
+
+    both(x1, scale_factor=2); both(x1, size=14, mode="nearest-exact"); both(x1, scale_factor=1.5, mode="linear"); both(x1, size=17, mode="linear", align_corners=True)
+    both(x3, scale_factor=2); both(x3, size=(7, 9, 8), mode="nearest-exact"); both(x3, scale_factor=(2, 1.5, 2), mode="trilinear"); both(x3, size=(6, 7, 11), mode="trilinear", align_corners=True)
+    both(torch.randn(1, 2, 5, 7, generator=g), size=(8, 9), mode="nearest-exact")

@@ -431,9 +431,85 @@ at::Tensor& index_fill_scalar_(at::Tensor& self, int64_t dim, const at::Tensor& 
     return self;
 }
 
+// ---- the 1-D and 3-D forms, and "nearest-exact": the same per-axis selections over one or three spatial axes ------------------------
+// exact: ATen's nearest-exact rounds at pixel centres, floor((o + 0.5) * scale)
+AxisMap nearest_axis_any(int64_t in, int64_t out, const c10::optional<double>& scale, bool exact, const at::Device& dev) {
+    if (!exact) return nearest_axis(in, out, scale, dev);
+    const float s = (float)((scale.has_value() && *scale > 0) ? 1.0 / *scale : (double)in / (double)out);
+    std::vector<int64_t> idx(out);
+    for (int64_t o = 0; o < out; ++o) idx[o] = std::min<int64_t>((int64_t)std::floor(((float)o + 0.5f) * s), in - 1);
+    AxisMap m;
+    m.i0 = at::tensor(idx, at::TensorOptions().dtype(at::kLong)).to(dev);
+    return m;
+}
+at::Tensor nearest_nd(const at::Tensor& self, at::IntArrayRef size, std::initializer_list<c10::optional<double>> scales, bool exact) {
+    const int64_t nsp = (int64_t)size.size();
+    TORCH_CHECK(self.dim() == nsp + 2, "upsample_nearest: expected a ", nsp + 2, "-D input");
+    at::Tensor r = self;
+    int64_t a = 0;
+    for (const auto& sc : scales) { r = at::index_select(r, 2 + a, nearest_axis_any(self.size(2 + a), size[a], sc, exact, self.device()).i0); ++a; }
+    return r;
+}
+at::Tensor nearest_nd_backward(const at::Tensor& grad, at::IntArrayRef size, at::IntArrayRef input_size, std::initializer_list<c10::optional<double>> scales, bool exact) {
+    at::Tensor g = grad;
+    int64_t a = 0;
+    for (const auto& sc : scales) {
+        std::vector<int64_t> shape(g.sizes().begin(), g.sizes().end());
+        shape[2 + a] = input_size[2 + a];
+        g = at::zeros(shape, g.options()).index_add(2 + a, nearest_axis_any(input_size[2 + a], size[a], sc, exact, grad.device()).i0, g);
+        ++a;
+    }
+    return g;
+}
+at::Tensor linear_nd(const at::Tensor& self, at::IntArrayRef size, bool align_corners, std::initializer_list<c10::optional<double>> scales) {
+    const int64_t nsp = (int64_t)size.size();
+    TORCH_CHECK(self.dim() == nsp + 2, "upsample_linear: expected a ", nsp + 2, "-D input");
+    at::Tensor r = self;
+    int64_t a = 0;
+    for (const auto& sc : scales) { r = blend_axis(r, 2 + a, bilinear_axis(self.size(2 + a), size[a], align_corners, sc, self.device())); ++a; }
+    return r;
+}
+at::Tensor linear_nd_backward(const at::Tensor& grad, at::IntArrayRef size, at::IntArrayRef input_size, bool align_corners, std::initializer_list<c10::optional<double>> scales) {
+    at::Tensor g = grad;
+    int64_t a = 0;
+    for (const auto& sc : scales) { g = blend_axis_backward(g, 2 + a, bilinear_axis(input_size[2 + a], size[a], align_corners, sc, grad.device()), input_size[2 + a]); ++a; }
+    return g;
+}
+using OptD = c10::optional<double>;
+at::Tensor up_nearest1d(const at::Tensor& x, at::IntArrayRef size, OptD s) { return nearest_nd(x, size, {s}, false); }
+at::Tensor up_nearest1d_bw(const at::Tensor& g, at::IntArrayRef size, at::IntArrayRef in, OptD s) { return nearest_nd_backward(g, size, in, {s}, false); }
+at::Tensor up_nearest3d(const at::Tensor& x, at::IntArrayRef size, OptD sd, OptD sh, OptD sw) { return nearest_nd(x, size, {sd, sh, sw}, false); }
+at::Tensor up_nearest3d_bw(const at::Tensor& g, at::IntArrayRef size, at::IntArrayRef in, OptD sd, OptD sh, OptD sw) { return nearest_nd_backward(g, size, in, {sd, sh, sw}, false); }
+at::Tensor up_exact1d(const at::Tensor& x, at::IntArrayRef size, OptD s) { return nearest_nd(x, size, {s}, true); }
+at::Tensor up_exact1d_bw(const at::Tensor& g, at::IntArrayRef size, at::IntArrayRef in, OptD s) { return nearest_nd_backward(g, size, in, {s}, true); }
+at::Tensor up_exact2d(const at::Tensor& x, at::IntArrayRef size, OptD sh, OptD sw) { return nearest_nd(x, size, {sh, sw}, true); }
+at::Tensor up_exact2d_bw(const at::Tensor& g, at::IntArrayRef size, at::IntArrayRef in, OptD sh, OptD sw) { return nearest_nd_backward(g, size, in, {sh, sw}, true); }
+at::Tensor up_exact3d(const at::Tensor& x, at::IntArrayRef size, OptD sd, OptD sh, OptD sw) { return nearest_nd(x, size, {sd, sh, sw}, true); }
+at::Tensor up_exact3d_bw(const at::Tensor& g, at::IntArrayRef size, at::IntArrayRef in, OptD sd, OptD sh, OptD sw) { return nearest_nd_backward(g, size, in, {sd, sh, sw}, true); }
+at::Tensor up_linear1d(const at::Tensor& x, at::IntArrayRef size, bool ac, OptD s) { return linear_nd(x, size, ac, {s}); }
+at::Tensor up_linear1d_bw(const at::Tensor& g, at::IntArrayRef size, at::IntArrayRef in, bool ac, OptD s) { return linear_nd_backward(g, size, in, ac, {s}); }
+at::Tensor up_trilinear3d(const at::Tensor& x, at::IntArrayRef size, bool ac, OptD sd, OptD sh, OptD sw) { return linear_nd(x, size, ac, {sd, sh, sw}); }
+at::Tensor up_trilinear3d_bw(const at::Tensor& g, at::IntArrayRef size, at::IntArrayRef in, bool ac, OptD sd, OptD sh, OptD sw) {
+    return linear_nd_backward(g, size, in, ac, {sd, sh, sw});
+}
+
 }  // namespace
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+    m.impl("upsample_nearest1d", &up_nearest1d);
+    m.impl("upsample_nearest1d_backward", &up_nearest1d_bw);
+    m.impl("upsample_nearest3d", &up_nearest3d);
+    m.impl("upsample_nearest3d_backward", &up_nearest3d_bw);
+    m.impl("_upsample_nearest_exact1d", &up_exact1d);
+    m.impl("_upsample_nearest_exact1d_backward", &up_exact1d_bw);
+    m.impl("_upsample_nearest_exact2d", &up_exact2d);
+    m.impl("_upsample_nearest_exact2d_backward", &up_exact2d_bw);
+    m.impl("_upsample_nearest_exact3d", &up_exact3d);
+    m.impl("_upsample_nearest_exact3d_backward", &up_exact3d_bw);
+    m.impl("upsample_linear1d", &up_linear1d);
+    m.impl("upsample_linear1d_backward", &up_linear1d_bw);
+    m.impl("upsample_trilinear3d", &up_trilinear3d);
+    m.impl("upsample_trilinear3d_backward", &up_trilinear3d_bw);
     m.impl("nan_to_num", &vk_nan_to_num);
     m.impl("nan_to_num.out", &nan_to_num_out);
     m.impl("nan_to_num_", &nan_to_num_);
