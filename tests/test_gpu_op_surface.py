@@ -621,8 +621,12 @@ def test_upsampling_adaptive_pools_bce_and_norms(vk, dtype):
     both(lambda t: F.adaptive_avg_pool2d(t, (3, 2)))
     both(lambda t: F.adaptive_max_pool2d(t, (2, 4)))
     both(lambda t: F.pixel_shuffle(t.repeat(1, 4, 1, 1)[:, :4], 2))
-    with pytest.raises(RuntimeError, match="NOT IMPLEMENTED"):
-        F.adaptive_avg_pool2d(x.to(vk), (4, 3))
+    both(lambda t: F.adaptive_avg_pool2d(t, (4, 3)))                 # windows of unequal size
+    both(lambda t: F.adaptive_avg_pool2d(t, (5, 7)))
+    both(lambda t: F.adaptive_max_pool2d(t, (4, 3)))
+    both(lambda t: F.adaptive_max_pool2d(t[0], (5, 5)))
+    idx_d = F.adaptive_max_pool2d(x.to(vk), (4, 5), return_indices=True)[1].cpu()
+    assert torch.equal(idx_d, F.adaptive_max_pool2d(x.float(), (4, 5), return_indices=True)[1])
     p, t = torch.rand(7, 5, generator=g).clamp(0.02, 0.98), (torch.rand(7, 5, generator=g) > 0.5).float()
     pd, pc = p.to(vk).requires_grad_(), p.clone().requires_grad_()
     ld, lc = F.binary_cross_entropy(pd, t.to(vk)), F.binary_cross_entropy(pc, t)
@@ -757,3 +761,56 @@ def test_upsampling_in_one_and_three_dimensions(vk):
     both(x1, scale_factor=2); both(x1, size=14, mode="nearest-exact"); both(x1, scale_factor=1.5, mode="linear"); both(x1, size=17, mode="linear", align_corners=True)
     both(x3, scale_factor=2); both(x3, size=(7, 9, 8), mode="nearest-exact"); both(x3, scale_factor=(2, 1.5, 2), mode="trilinear"); both(x3, size=(6, 7, 11), mode="trilinear", align_corners=True)
     both(torch.randn(1, 2, 5, 7, generator=g), size=(8, 9), mode="nearest-exact")
+
+
+def test_running_extremes_unique_and_bincount(vk):
+    g = torch.Generator().manual_seed(41)
+    x = torch.randint(0, 5, (4, 37, 3), generator=g).float()          # many ties: the later position must win
+    for dim in (0, 1, -1):
+        for fn in (torch.cummax, torch.cummin):
+            d, c = fn(x.to(vk), dim), fn(x, dim)
+            assert torch.equal(d.values.cpu(), c.values) and torch.equal(d.indices.cpu(), c.indices), (dim, fn)
+    y = torch.randn(3, 50, generator=g)
+    y[0, 7] = float("nan"); y[1, 20] = float("nan"); y[1, 30] = float("nan"); y[2, 3] = float("inf")
+    for fn in (torch.cummax, torch.cummin):
+        d, c = fn(y.to(vk), 1), fn(y, 1)
+        assert torch.equal(d.indices.cpu(), c.indices)
+        assert torch.allclose(d.values.cpu(), c.values, equal_nan=True)
+    li = torch.randint(-1000, 1000, (5, 9), generator=g)
+    d, c = torch.cummin(li.to(vk), 1), torch.cummin(li, 1)
+    assert torch.equal(d.values.cpu(), c.values) and torch.equal(d.indices.cpu(), c.indices)
+    h = torch.randn(6, 20, generator=g).half()
+    d, c = torch.cummax(h.to(vk), 1), torch.cummax(h, 1)
+    assert torch.equal(d.values.cpu(), c.values) and torch.equal(d.indices.cpu(), c.indices)
+    xd, xc = y[2:].to(vk).requires_grad_(), y[2:].clone().requires_grad_()
+    torch.cummax(xd, 1).values.sum().backward(); torch.cummax(xc, 1).values.sum().backward()
+    _close(xd.grad, xc.grad, 1e-6)
+
+    for t in (torch.randint(-5, 9, (7, 11), generator=g), torch.randn(50, generator=g).round(), torch.tensor([3.0]),
+              torch.tensor([2, 2, 2]), torch.zeros(0)):
+        d = torch.unique(t.to(vk), return_inverse=True, return_counts=True)
+        c = torch.unique(t, return_inverse=True, return_counts=True)
+        for a, b in zip(d, c):
+            assert a.dtype == b.dtype and torch.equal(a.cpu(), b), t
+    assert torch.equal(torch.unique(li.to(vk)).cpu(), torch.unique(li))
+
+    b = torch.randint(0, 13, (500,), generator=g)
+    w = torch.rand(500, generator=g)
+    assert torch.equal(torch.bincount(b.to(vk)).cpu(), torch.bincount(b))
+    assert torch.equal(torch.bincount(b.to(vk), minlength=20).cpu(), torch.bincount(b, minlength=20))
+    _close(torch.bincount(b.to(vk), weights=w.to(vk)), torch.bincount(b, weights=w), 1e-5)
+    with pytest.raises(RuntimeError, match="non-negative"):
+        torch.bincount(torch.tensor([1, -1]).to(vk))
+
+
+def test_cross_product(vk):
+    g = torch.Generator().manual_seed(43)
+    a, b = torch.randn(5, 3, 4, generator=g), torch.randn(1, 3, 1, generator=g)
+    ad, ac = a.to(vk).requires_grad_(), a.clone().requires_grad_()
+    yd, yc = torch.linalg.cross(ad, b.to(vk), dim=1), torch.linalg.cross(ac, b, dim=1)
+    _close(yd, yc, 1e-6)
+    gy = torch.randn(yc.shape, generator=g)
+    yd.backward(gy.to(vk)); yc.backward(gy)
+    _close(ad.grad, ac.grad, 1e-6)
+    u, v = torch.randn(7, 3, generator=g), torch.randn(7, 3, generator=g)
+    _close(torch.cross(u.to(vk), v.to(vk), dim=-1), torch.cross(u, v, dim=-1), 1e-6)

@@ -9,6 +9,7 @@
 // fp32 inside those kernels.
 #include "common.h"
 
+#include <algorithm>
 #include <cmath>
 #include <limits>
 
@@ -267,22 +268,189 @@ std::array<int64_t, 2> even_windows(const at::Tensor& self, at::IntArrayRef outp
         TVK_NOT_IMPLEMENTED(name, " to an output size that does not divide the input (", H, " x ", W, " -> ", output_size[0], " x ", output_size[1], ")");
     return {H / output_size[0], W / output_size[1]};
 }
+bool divides_evenly(const at::Tensor& self, at::IntArrayRef output_size) {
+    return output_size.size() == 2 && output_size[0] > 0 && output_size[1] > 0 && self.size(-2) % output_size[0] == 0 && self.size(-1) % output_size[1] == 0;
+}
+// [out, in] matrix whose row o averages inputs floor(o in / out) .. ceil((o + 1) in / out) - 1: the adaptive pooling window
+at::Tensor adaptive_avg_matrix(int64_t in, int64_t out, const at::Tensor& like) {
+    std::vector<float> a(static_cast<size_t>(out * in), 0.f);
+    for (int64_t o = 0; o < out; ++o) {
+        const int64_t s = (o * in) / out, e = ((o + 1) * in + out - 1) / out;
+        for (int64_t i = s; i < e; ++i) a[static_cast<size_t>(o * in + i)] = 1.f / static_cast<float>(e - s);
+    }
+    return at::tensor(a, at::TensorOptions().dtype(at::kFloat)).view({out, in}).to(like.device()).to(like.scalar_type());
+}
+// uneven windows: the pooling is separable, one averaging matrix per axis, so it is two matrix products
+at::Tensor adaptive_avg_by_matrices(const at::Tensor& x, int64_t H, int64_t W, int64_t Ho, int64_t Wo, bool transpose) {
+    at::Tensor ah = adaptive_avg_matrix(H, Ho, x), aw = adaptive_avg_matrix(W, Wo, x);
+    at::Tensor x3 = x.contiguous().reshape({-1, x.size(-2), x.size(-1)});
+    at::Tensor y = transpose ? at::matmul(at::matmul(ah.t().contiguous(), x3), aw) : at::matmul(at::matmul(ah, x3), aw.t().contiguous());
+    std::vector<int64_t> shape(x.sizes().begin(), x.sizes().end());
+    shape[shape.size() - 2] = y.size(-2);
+    shape[shape.size() - 1] = y.size(-1);
+    return y.reshape(shape);
+}
 at::Tensor adaptive_avg_pool2d(const at::Tensor& self, at::IntArrayRef output_size) {
-    const auto k = even_windows(self, output_size, "adaptive_avg_pool2d");
-    return at::avg_pool2d(self, {k[0], k[1]}, {k[0], k[1]});
+    if (divides_evenly(self, output_size)) {
+        const auto k = even_windows(self, output_size, "adaptive_avg_pool2d");
+        return at::avg_pool2d(self, {k[0], k[1]}, {k[0], k[1]});
+    }
+    TORCH_CHECK(output_size.size() == 2 && (self.dim() == 3 || self.dim() == 4) && output_size[0] > 0 && output_size[1] > 0,
+                "adaptive_avg_pool2d: expected a 3-D or 4-D input and two positive output sizes");
+    return adaptive_avg_by_matrices(self, self.size(-2), self.size(-1), output_size[0], output_size[1], false);
 }
 at::Tensor adaptive_avg_pool2d_backward(const at::Tensor& grad, const at::Tensor& self) {
-    const auto k = even_windows(self, {grad.size(-2), grad.size(-1)}, "adaptive_avg_pool2d_backward");
-    return at::avg_pool2d_backward(grad, self, {k[0], k[1]}, {k[0], k[1]}, {0, 0}, false, true, c10::nullopt);
+    if (divides_evenly(self, {grad.size(-2), grad.size(-1)})) {
+        const auto k = even_windows(self, {grad.size(-2), grad.size(-1)}, "adaptive_avg_pool2d_backward");
+        return at::avg_pool2d_backward(grad, self, {k[0], k[1]}, {k[0], k[1]}, {0, 0}, false, true, c10::nullopt);
+    }
+    return adaptive_avg_by_matrices(grad, self.size(-2), self.size(-1), grad.size(-2), grad.size(-1), true);
+}
+// Uneven windows: a host-built table [Ho * Wo, L] of the flat input positions of every window, in row-major window order and
+// padded by repeating the window's last row / column (a repeat cannot win the first-maximum rule), turns the pooling into one
+// gather and one maximum along the last axis.
+at::Tensor adaptive_window_table(int64_t H, int64_t W, int64_t Ho, int64_t Wo, const at::Device& dev) {
+    auto start = [](int64_t o, int64_t in, int64_t out) { return (o * in) / out; };
+    auto stop = [](int64_t o, int64_t in, int64_t out) { return ((o + 1) * in + out - 1) / out; };
+    int64_t Lh = 1, Lw = 1;
+    for (int64_t o = 0; o < Ho; ++o) Lh = std::max(Lh, stop(o, H, Ho) - start(o, H, Ho));
+    for (int64_t o = 0; o < Wo; ++o) Lw = std::max(Lw, stop(o, W, Wo) - start(o, W, Wo));
+    std::vector<int64_t> t;
+    t.reserve(static_cast<size_t>(Ho * Wo * Lh * Lw));
+    for (int64_t oh = 0; oh < Ho; ++oh)
+        for (int64_t ow = 0; ow < Wo; ++ow)
+            for (int64_t a = 0; a < Lh; ++a) {
+                const int64_t h = std::min(start(oh, H, Ho) + a, stop(oh, H, Ho) - 1);
+                for (int64_t b = 0; b < Lw; ++b) t.push_back(h * W + std::min(start(ow, W, Wo) + b, stop(ow, W, Wo) - 1));
+            }
+    return at::tensor(t, at::TensorOptions().dtype(at::kLong)).view({Ho * Wo, Lh * Lw}).to(dev);
 }
 std::tuple<at::Tensor, at::Tensor> adaptive_max_pool2d(const at::Tensor& self, at::IntArrayRef output_size) {
-    const auto k = even_windows(self, output_size, "adaptive_max_pool2d");
-    return at::max_pool2d_with_indices(self, {k[0], k[1]}, {k[0], k[1]});
+    if (divides_evenly(self, output_size)) {
+        const auto k = even_windows(self, output_size, "adaptive_max_pool2d");
+        return at::max_pool2d_with_indices(self, {k[0], k[1]}, {k[0], k[1]});
+    }
+    TORCH_CHECK(output_size.size() == 2 && (self.dim() == 3 || self.dim() == 4) && output_size[0] > 0 && output_size[1] > 0,
+                "adaptive_max_pool2d: expected a 3-D or 4-D input and two positive output sizes");
+    const int64_t H = self.size(-2), W = self.size(-1), Ho = output_size[0], Wo = output_size[1];
+    at::Tensor table = adaptive_window_table(H, W, Ho, Wo, self.device());
+    at::Tensor flat = self.contiguous().reshape({-1, H * W});
+    const int64_t B = flat.size(0);
+    at::Tensor windows = at::index_select(flat, 1, table.reshape({-1})).reshape({B, Ho * Wo, table.size(1)});
+    auto [values, arg] = at::max(windows, -1, false);
+    at::Tensor index = at::gather(table.unsqueeze(0).expand({B, Ho * Wo, table.size(1)}).contiguous(), 2, arg.unsqueeze(-1)).squeeze(-1);
+    std::vector<int64_t> shape(self.sizes().begin(), self.sizes().end());
+    shape[shape.size() - 2] = Ho;
+    shape[shape.size() - 1] = Wo;
+    return {values.reshape(shape), index.reshape(shape)};
 }
 at::Tensor adaptive_max_pool2d_backward(const at::Tensor& grad, const at::Tensor& self, const at::Tensor& indices) {
-    const auto k = even_windows(self, {grad.size(-2), grad.size(-1)}, "adaptive_max_pool2d_backward");
-    return at::max_pool2d_with_indices_backward(grad, self, {k[0], k[1]}, {k[0], k[1]}, {0, 0}, {1, 1}, false, indices);
+    if (divides_evenly(self, {grad.size(-2), grad.size(-1)})) {
+        const auto k = even_windows(self, {grad.size(-2), grad.size(-1)}, "adaptive_max_pool2d_backward");
+        return at::max_pool2d_with_indices_backward(grad, self, {k[0], k[1]}, {k[0], k[1]}, {0, 0}, {1, 1}, false, indices);
+    }
+    const int64_t HW = self.size(-2) * self.size(-1), B = HW == 0 ? 0 : self.numel() / HW;
+    at::Tensor zero = at::zeros({B, HW}, grad.options());
+    return at::scatter_add(zero, 1, indices.contiguous().reshape({B, -1}), grad.contiguous().reshape({B, -1})).reshape(self.sizes());
 }
+
+// Running maximum / minimum with the position it came from, as a log-step scan along the last axis: at step s every
+// element is compared with the running result s places to its left. A strictly better left value wins, so ties keep the
+// later position, and a NaN on the left wins over any number; both are ATen's rules.
+void cum_extreme(const at::Tensor& self, at::Tensor& values, at::Tensor& indices, int64_t dim, bool is_max, const char* name) {
+    const at::ScalarType st = self.scalar_type();
+    const bool floating = is_hot_float(st);
+    if (!(floating || st == at::kLong || st == at::kInt)) TVK_NOT_IMPLEMENTED(name, " for dtype ", st);
+    if (self.numel() == 0) return;
+    if (self.dim() == 0) { values.copy_(self); indices.zero_(); return; }
+    dim = at::maybe_wrap_dim(dim, self.dim());
+    const int64_t n = self.size(dim);
+    at::Tensor moved = self.movedim(dim, -1).contiguous();
+    const auto moved_shape = moved.sizes().vec();
+    at::Tensor v = moved.reshape({-1, n});
+    at::Tensor idx = at::arange(n, at::TensorOptions().dtype(at::kLong).device(at::kCPU)).to(self.device()).expand({v.size(0), n}).contiguous();
+    at::Scalar worst;
+    if (floating) worst = is_max ? -std::numeric_limits<double>::infinity() : std::numeric_limits<double>::infinity();
+    else if (st == at::kLong) worst = is_max ? std::numeric_limits<int64_t>::min() : std::numeric_limits<int64_t>::max() - 1023;   // the fill goes through a double: 2^63 - 1024 is the largest value that survives
+    else worst = static_cast<int64_t>(is_max ? std::numeric_limits<int32_t>::min() : std::numeric_limits<int32_t>::max());
+    for (int64_t s = 1; s < n; s *= 2) {
+        at::Tensor lv = at::full_like(v, worst), li = at::zeros_like(idx);
+        lv.narrow(1, s, n - s).copy_(v.narrow(1, 0, n - s));
+        li.narrow(1, s, n - s).copy_(idx.narrow(1, 0, n - s));
+        at::Tensor take = is_max ? at::gt(lv, v) : at::lt(lv, v);
+        if (floating) take = at::logical_or(take, at::logical_and(at::isnan(lv), at::logical_not(at::isnan(v))));
+        v = at::where(take, lv, v);
+        idx = at::where(take, li, idx);
+    }
+    values.copy_(v.reshape(moved_shape).movedim(-1, dim));
+    indices.copy_(idx.reshape(moved_shape).movedim(-1, dim));
+}
+void cummax_helper(const at::Tensor& self, at::Tensor& values, at::Tensor& indices, int64_t dim) { cum_extreme(self, values, indices, dim, true, "cummax"); }
+void cummin_helper(const at::Tensor& self, at::Tensor& values, at::Tensor& indices, int64_t dim) { cum_extreme(self, values, indices, dim, false, "cummin"); }
+
+// torch.unique without a dimension: sort, mark the first element of every run, compact. The inverse is the run number
+// scattered back through the sort permutation; a count is the distance between consecutive run starts. Integers are sorted
+// as fp32, so they must be below 2^24 in magnitude, and run numbers are carried in fp32, which bounds the element count.
+std::tuple<at::Tensor, at::Tensor, at::Tensor> unique2(const at::Tensor& self, bool, bool return_inverse, bool return_counts) {
+    const at::ScalarType st = self.scalar_type();
+    const bool floating = is_hot_float(st);
+    if (!(floating || st == at::kLong || st == at::kInt)) TVK_NOT_IMPLEMENTED("unique for dtype ", st);
+    const at::TensorOptions long_opts = self.options().dtype(at::kLong);
+    const int64_t n = self.numel();
+    if (n == 0) return {at::empty({0}, self.options()), at::empty(return_inverse ? self.sizes() : at::IntArrayRef{0}, long_opts), at::empty({0}, long_opts)};
+    TORCH_CHECK(n <= (int64_t{1} << 24), "torchvulkan [NOT IMPLEMENTED]: unique of more than 2^24 elements");
+    at::Tensor flat = self.contiguous().reshape({-1});
+    at::Tensor work = floating ? flat : flat.to(at::kFloat);
+    if (!floating && at::amax(at::abs(work), {0}).item<float>() >= 16777216.f) TVK_NOT_IMPLEMENTED("unique of integers of magnitude 2^24 or more");
+    auto [vals, perm] = at::sort(work, 0, false);
+    at::Tensor first = at::ones({n}, self.options().dtype(at::kBool));
+    if (n > 1) first.narrow(0, 1, n - 1).copy_(at::ne(vals.narrow(0, 1, n - 1), vals.narrow(0, 0, n - 1)));
+    at::Tensor uniq = at::masked_select(vals, first).to(st);
+    at::Tensor inverse = at::empty({0}, long_opts), counts = at::empty({0}, long_opts);
+    if (return_inverse) {
+        at::Tensor run = at::cumsum(first.to(at::kFloat), 0) - 1.0;
+        inverse = at::scatter_add(at::zeros({n}, run.options()), 0, perm, run).to(at::kLong).reshape(self.sizes());
+    }
+    if (return_counts) {
+        at::Tensor pos = at::nonzero(first).reshape({-1});
+        const int64_t u = pos.numel();
+        at::Tensor next = at::full({u}, n, long_opts);
+        if (u > 1) next.narrow(0, 0, u - 1).copy_(pos.narrow(0, 1, u - 1));
+        counts = next - pos;
+    }
+    return {uniq, inverse, counts};
+}
+// bincount: ones (or the weights) added at their bin; the largest value sizes the result, which costs one read-back
+at::Tensor bincount(const at::Tensor& self, const c10::optional<at::Tensor>& weights, int64_t minlength) {
+    TORCH_CHECK(self.dim() == 1 && (self.scalar_type() == at::kLong || self.scalar_type() == at::kInt), "bincount only supports 1-d non-negative integral inputs.");
+    TORCH_CHECK(minlength >= 0, "minlength should be >= 0");
+    const bool weighted = weights.has_value() && weights->defined();
+    const at::TensorOptions long_opts = self.options().dtype(at::kLong);
+    if (self.numel() == 0) return at::zeros({minlength}, weighted ? weights->options() : long_opts);
+    TORCH_CHECK(self.numel() <= (int64_t{1} << 24), "torchvulkan [NOT IMPLEMENTED]: bincount of more than 2^24 elements");
+    at::Tensor as_float = self.to(at::kFloat);
+    const float lo = at::amin(as_float, {0}).item<float>(), hi = at::amax(as_float, {0}).item<float>();
+    TORCH_CHECK(lo >= 0.f, "bincount only supports 1-d non-negative integral inputs.");
+    if (hi >= 16777216.f) TVK_NOT_IMPLEMENTED("bincount of values of 2^24 or more");
+    const int64_t bins = std::max<int64_t>(static_cast<int64_t>(hi) + 1, minlength);
+    at::Tensor index = self.scalar_type() == at::kLong ? self : self.to(at::kLong);
+    if (weighted) {
+        TORCH_CHECK(weights->dim() == 1 && weights->size(0) == self.size(0), "weights should be 1-d and have the same length as input");
+        if (!is_hot_float(weights->scalar_type())) TVK_NOT_IMPLEMENTED("bincount with weights of dtype ", weights->scalar_type());
+        return at::scatter_add(at::zeros({bins}, weights->options()), 0, index, *weights);
+    }
+    return at::scatter_add(at::zeros({bins}, as_float.options()), 0, index, at::ones_like(as_float)).to(at::kLong);
+}
+
+// cross product along a dimension of length 3: c_i = a_{i+1} b_{i+2} - a_{i+2} b_{i+1}, the shifted operands being rolls
+at::Tensor vk_linalg_cross(const at::Tensor& self, const at::Tensor& other, int64_t dim) {
+    auto both = at::broadcast_tensors({self, other});
+    dim = at::maybe_wrap_dim(dim, both[0].dim());
+    TORCH_CHECK(both[0].size(dim) == 3, "linalg.cross: inputs dimension ", dim, " must have length 3. Got ", self.size(dim), " and ", other.size(dim));
+    at::Tensor a = both[0].contiguous(), b = both[1].contiguous();
+    return at::roll(a, {-1}, {dim}) * at::roll(b, {-2}, {dim}) - at::roll(a, {-2}, {dim}) * at::roll(b, {-1}, {dim});
+}
+at::Tensor& vk_linalg_cross_out(const at::Tensor& self, const at::Tensor& other, int64_t dim, at::Tensor& out) { return into(out, vk_linalg_cross(self, other, dim)); }
 
 // prelu with its weight already broadcast to the input (ATen reshapes it before calling the kernel)
 at::Tensor prelu_kernel(const at::Tensor& self, const at::Tensor& weight) { return at::where(at::gt(self, 0), self, weight * self); }
@@ -519,6 +687,12 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("index_fill_.int_Scalar", &index_fill_scalar_);
     m.impl("binary_cross_entropy", &bce);
     m.impl("binary_cross_entropy_backward", &bce_backward);
+    m.impl("linalg_cross", &vk_linalg_cross);
+    m.impl("linalg_cross.out", &vk_linalg_cross_out);
+    m.impl("_unique2", &unique2);
+    m.impl("bincount", &bincount);
+    m.impl("_cummax_helper", &cummax_helper);
+    m.impl("_cummin_helper", &cummin_helper);
     m.impl("_adaptive_avg_pool2d", &adaptive_avg_pool2d);
     m.impl("_adaptive_avg_pool2d_backward", &adaptive_avg_pool2d_backward);
     m.impl("adaptive_max_pool2d", &adaptive_max_pool2d);
