@@ -1094,3 +1094,86 @@ def test_cdist_bucketize_searchsorted(vk):
         assert torch.equal(torch.bucketize(v.to(vk), bnd.to(vk), right=right).cpu(), torch.bucketize(v, bnd, right=right))
         assert torch.equal(torch.searchsorted(seq.to(vk), q.to(vk), right=right).cpu(), torch.searchsorted(seq, q, right=right))
     assert torch.bucketize(v.to(vk), bnd.to(vk), out_int32=True).dtype == torch.int32
+
+
+def test_attention_modules_in_eval_mode_take_the_one_operator_path(vk, monkeypatch):
+    """In eval mode without gradients nn.MultiheadAttention and nn.TransformerEncoderLayer call one operator for the whole
+    block (torch._native_multi_head_attention / torch._transformer_encoder_layer_fwd) on this device too. Outputs and attention
+    weights against the same modules on ATen CPU, with each kind of mask; the padded batch of a TransformerEncoder stays padded."""
+    calls = {"mha": 0, "layer": 0}
+    real_mha, real_layer = torch._native_multi_head_attention, torch._transformer_encoder_layer_fwd
+
+    def spy_mha(*a, **k):
+        calls["mha"] += a[0].device.type == "vulkan"
+        return real_mha(*a, **k)
+
+    def spy_layer(*a, **k):
+        calls["layer"] += a[0].device.type == "vulkan"
+        return real_layer(*a, **k)
+
+    monkeypatch.setattr(torch, "_native_multi_head_attention", spy_mha)
+    monkeypatch.setattr(torch, "_transformer_encoder_layer_fwd", spy_layer)
+    g = torch.Generator().manual_seed(9)
+    B, T, D, H = 3, 10, 32, 4
+    x = torch.randn(B, T, D, generator=g)
+    pad = torch.zeros(B, T, dtype=torch.bool)
+    pad[0, 7:] = True
+    pad[2, 4:] = True
+    causal = torch.triu(torch.ones(T, T, dtype=torch.bool), 1)
+    valid = ~pad
+
+    def close(d, c, tol=2e-5, rows=None):
+        d, c = d.cpu().float(), c.float()
+        if rows is not None:
+            d, c = d[rows], c[rows]
+        assert float((d - c).abs().max()) <= tol * (1 + float(c.abs().max())), float((d - c).abs().max())
+
+    torch.manual_seed(0)
+    ref = torch.nn.MultiheadAttention(D, H, batch_first=True).eval()
+    dev = torch.nn.MultiheadAttention(D, H, batch_first=True)
+    dev.load_state_dict(ref.state_dict())
+    dev = dev.to(vk).eval()
+    xd = x.to(vk)
+    with torch.no_grad():
+        for kw in ({}, {"key_padding_mask": pad}, {"attn_mask": causal}, {"key_padding_mask": pad, "attn_mask": causal},
+                   {"average_attn_weights": False}, {"need_weights": False}, {"need_weights": False, "key_padding_mask": pad}):
+            kd = {k: (v.to(vk) if torch.is_tensor(v) else v) for k, v in kw.items()}
+            (oc, wc), (od, wd) = ref(x, x, x, **kw), dev(xd, xd, xd, **kd)
+            close(od, oc)
+            assert (wc is None) == (wd is None)
+            if wc is not None:
+                close(wd, wc)
+    assert calls["mha"] == 7
+
+    for act, norm_first in (("relu", False), ("gelu", True)):
+        torch.manual_seed(1)
+        make = lambda: torch.nn.TransformerEncoderLayer(D, H, 64, dropout=0.0, activation=act, batch_first=True, norm_first=norm_first)
+        ref, dev = make().eval(), make()
+        dev.load_state_dict(ref.state_dict())
+        dev = dev.to(vk).eval()
+        before = calls["layer"]
+        with torch.no_grad():
+            close(dev(xd), ref(x), 5e-5)
+            close(dev(xd, src_key_padding_mask=pad.to(vk)), ref(x, src_key_padding_mask=pad), 5e-5)
+            close(dev(xd, src_mask=causal.to(vk)), ref(x, src_mask=causal), 5e-5)
+        assert calls["layer"] == before + 3
+
+    torch.manual_seed(2)
+    make = lambda: torch.nn.TransformerEncoder(torch.nn.TransformerEncoderLayer(D, H, 64, dropout=0.0, batch_first=True), 2)
+    ref, dev = make().eval(), make()
+    dev.load_state_dict(ref.state_dict())
+    dev = dev.to(vk).eval()
+    with torch.no_grad():
+        yc, yd = ref(x, src_key_padding_mask=pad), dev(xd, src_key_padding_mask=pad.to(vk))
+    close(yd, yc, 1e-4, rows=valid)                       # ATen CPU packs the batch and returns zeros at the padding
+
+    torch.manual_seed(3)
+    half = torch.nn.MultiheadAttention(64, 4, batch_first=True).eval()
+    dhalf = torch.nn.MultiheadAttention(64, 4, batch_first=True)
+    dhalf.load_state_dict(half.state_dict())
+    dhalf = dhalf.half().to(vk).eval()
+    xh = torch.randn(2, 128, 64, generator=g)
+    with torch.no_grad():
+        oc = half(xh, xh, xh, need_weights=False)[0]
+        od = dhalf(xh.half().to(vk), xh.half().to(vk), xh.half().to(vk), need_weights=False)[0]
+    close(od, oc, 1e-2)

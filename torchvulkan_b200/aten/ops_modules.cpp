@@ -8,6 +8,7 @@
 #include "common.h"
 
 #include <cmath>
+#include <limits>
 
 namespace tvk_aten {
 namespace {
@@ -370,9 +371,78 @@ at::Tensor& where_self_out(const at::Tensor& cond, const at::Tensor& a, const at
     return out;
 }
 
+// ---- inference fast paths of nn.MultiheadAttention and nn.TransformerEncoderLayer ------------------------------------------
+// In eval mode without gradients those modules call one operator for the whole block on every device type they list, this
+// one included. A mask marks what is EXCLUDED (nonzero / True / -inf), shaped by mask_type: 0 = [T, T] over (query, key),
+// 1 = [B, T] key padding, 2 = [B, H, T, T]. A row with every key excluded comes out NaN, as ATen's own kernels leave it.
+at::Tensor excluded_positions(const c10::optional<at::Tensor>& mask, c10::optional<int64_t> mask_type, int64_t B, int64_t T) {
+    at::Tensor m = opt(mask);
+    if (!m.defined()) return m;
+    TORCH_CHECK(mask_type.has_value(), "a mask needs its mask_type");
+    if (m.scalar_type() != at::kBool) m = m.to(at::kBool);
+    switch (*mask_type) {
+        case 0: TORCH_CHECK(m.dim() == 2 && m.size(0) == T && m.size(1) == T, "mask_type 0 expects a [T, T] mask"); return m.view({1, 1, T, T});
+        case 1: TORCH_CHECK(m.dim() == 2 && m.size(0) == B && m.size(1) == T, "mask_type 1 expects a [B, T] mask"); return m.view({B, 1, 1, T});
+        case 2: TORCH_CHECK(m.dim() == 4 && m.size(0) == B && m.size(2) == T && m.size(3) == T, "mask_type 2 expects a [B, H, T, T] mask"); return m;
+        default: TORCH_CHECK(false, "unknown mask_type ", *mask_type);
+    }
+}
+std::tuple<at::Tensor, at::Tensor> native_multi_head_attention(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value, int64_t embed_dim,
+                                                               int64_t num_head, const at::Tensor& qkv_weight, const at::Tensor& qkv_bias,
+                                                               const at::Tensor& proj_weight, const at::Tensor& proj_bias, const c10::optional<at::Tensor>& mask,
+                                                               bool need_weights, bool average_attn_weights, c10::optional<int64_t> mask_type) {
+    TORCH_CHECK(!query.is_nested() && !key.is_nested() && !value.is_nested(), "torchvulkan [NOT IMPLEMENTED]: multi-head attention on nested tensors");
+    TORCH_CHECK(query.dim() == 3 && query.size(2) == embed_dim, "expected a [batch, sequence, ", embed_dim, "] query, got ", query.sizes());
+    TORCH_CHECK(query.is_same(key) && key.is_same(value), "torchvulkan [NOT IMPLEMENTED]: the fused multi-head attention block is self-attention only");
+    TORCH_CHECK(num_head > 0 && embed_dim % num_head == 0, "embed_dim ", embed_dim, " is not divisible by num_head ", num_head);
+    TORCH_CHECK(qkv_weight.dim() == 2 && qkv_weight.size(0) == 3 * embed_dim && qkv_weight.size(1) == embed_dim, "expected a [3 * embed_dim, embed_dim] qkv_weight");
+    const int64_t B = query.size(0), T = query.size(1), D = embed_dim, H = num_head, dh = D / H;
+    auto parts = at::linear(query, qkv_weight, qkv_bias).chunk(3, -1);
+    auto heads = [&](const at::Tensor& t) { return t.reshape({B, T, H, dh}).transpose(1, 2); };           // [B, H, T, dh]
+    at::Tensor q = heads(parts[0]), k = heads(parts[1]), v = heads(parts[2]);
+    at::Tensor excluded = excluded_positions(mask, mask_type, B, T);
+    at::Tensor mixed, weights;
+    if (!need_weights && !excluded.defined()) {
+        mixed = at::scaled_dot_product_attention(q, k, v);
+    } else {
+        at::Tensor scores = at::matmul(q * (1.0 / std::sqrt(static_cast<double>(dh))), k.transpose(-1, -2));
+        if (excluded.defined()) scores = scores.masked_fill(excluded, -std::numeric_limits<double>::infinity());
+        at::Tensor w = at::softmax(scores, -1);
+        mixed = at::matmul(w, v);
+        if (need_weights) weights = average_attn_weights ? at::mean(w, {1}) : w;
+    }
+    at::Tensor out = at::linear(mixed.transpose(1, 2).reshape({B, T, D}), proj_weight, proj_bias);
+    return {out, weights};
+}
+at::Tensor transformer_encoder_layer_fwd(const at::Tensor& src, int64_t embed_dim, int64_t num_heads, const at::Tensor& qkv_weight, const at::Tensor& qkv_bias,
+                                         const at::Tensor& proj_weight, const at::Tensor& proj_bias, bool use_gelu, bool norm_first, double eps,
+                                         const at::Tensor& norm_weight_1, const at::Tensor& norm_bias_1, const at::Tensor& norm_weight_2,
+                                         const at::Tensor& norm_bias_2, const at::Tensor& ffn_weight_1, const at::Tensor& ffn_bias_1,
+                                         const at::Tensor& ffn_weight_2, const at::Tensor& ffn_bias_2, const c10::optional<at::Tensor>& mask,
+                                         c10::optional<int64_t> mask_type) {
+    TORCH_CHECK(!src.is_nested(), "torchvulkan [NOT IMPLEMENTED]: the transformer encoder layer on nested tensors");
+    at::Tensor x = norm_first ? at::layer_norm(src, {embed_dim}, norm_weight_1, norm_bias_1, eps) : src;
+    x = std::get<0>(native_multi_head_attention(x, x, x, embed_dim, num_heads, qkv_weight, qkv_bias, proj_weight, proj_bias, mask, false, true, mask_type));
+    x = x + src;
+    if (!norm_first) x = at::layer_norm(x, {embed_dim}, norm_weight_1, norm_bias_1, eps);
+    at::Tensor residual = x;
+    if (norm_first) x = at::layer_norm(x, {embed_dim}, norm_weight_2, norm_bias_2, eps);
+    x = at::linear(x, ffn_weight_1, ffn_bias_1);
+    x = at::linear(use_gelu ? at::gelu(x) : at::relu(x), ffn_weight_2, ffn_bias_2);
+    x = x + residual;
+    if (!norm_first) x = at::layer_norm(x, {embed_dim}, norm_weight_2, norm_bias_2, eps);
+    return x;
+}
+// nn.TransformerEncoder asks this before packing a padded batch into a nested tensor. There are no nested tensors on this
+// device, so the answer is always "not left aligned": the batch stays padded and the layers receive the padding mask.
+bool nested_tensor_from_mask_left_aligned(const at::Tensor&, const at::Tensor&) { return false; }
+
 }  // namespace
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+    m.impl("_native_multi_head_attention", &native_multi_head_attention);
+    m.impl("_transformer_encoder_layer_fwd", &transformer_encoder_layer_fwd);
+    m.impl("_nested_tensor_from_mask_left_aligned", &nested_tensor_from_mask_left_aligned);
     m.impl("_thnn_fused_lstm_cell", &lstm_cell);
     m.impl("_thnn_fused_lstm_cell_backward_impl", &lstm_cell_backward);
     m.impl("_thnn_fused_gru_cell", &gru_cell);
