@@ -814,3 +814,85 @@ def test_cross_product(vk):
     _close(ad.grad, ac.grad, 1e-6)
     u, v = torch.randn(7, 3, generator=g), torch.randn(7, 3, generator=g)
     _close(torch.cross(u.to(vk), v.to(vk), dim=-1), torch.cross(u, v, dim=-1), 1e-6)
+
+
+def _pooling_of_volumes(dev):
+    g = torch.Generator().manual_seed(47)
+    x = torch.randint(0, 4, (2, 3, 9, 10, 11), generator=g).float()          # ties: the first maximum must win
+    for k, s, p, d, ceil in (((2, 2, 2), (2, 2, 2), (0, 0, 0), (1, 1, 1), False), ((3, 2, 3), (2, 1, 2), (1, 1, 1), (1, 1, 1), True),
+                             ((2, 3, 2), (1, 2, 2), (0, 1, 1), (2, 1, 2), False)):
+        vd, idd = F.max_pool3d(x.to(dev), k, s, p, d, ceil, return_indices=True)
+        vc, idc = F.max_pool3d(x, k, s, p, d, ceil, return_indices=True)
+        assert torch.equal(vd.cpu(), vc) and torch.equal(idd.cpu(), idc), (k, s, p, d, ceil)
+    y = torch.randn(2, 3, 9, 10, 11, generator=g)
+    cases = [lambda t: F.max_pool3d(t, 2), lambda t: F.max_pool3d(t, (3, 2, 3), (2, 1, 2), (1, 1, 1), ceil_mode=True),
+             lambda t: F.avg_pool3d(t, 2), lambda t: F.avg_pool3d(t, (3, 2, 3), (2, 1, 2), (1, 1, 1), True, True),
+             lambda t: F.avg_pool3d(t, (3, 2, 3), (2, 1, 2), (1, 1, 1), True, False),
+             lambda t: F.avg_pool3d(t, (2, 3, 2), (1, 2, 2), (0, 1, 1), False, False, 5),
+             lambda t: F.adaptive_avg_pool3d(t, 1), lambda t: F.adaptive_avg_pool3d(t, (3, 5, 11)), lambda t: F.adaptive_avg_pool3d(t[0], (4, 3, 2))]
+    for fn in cases:
+        yd, yc = y.clone().to(dev).requires_grad_(), y.clone().requires_grad_()
+        od, oc = fn(yd), fn(yc)
+        _close(od, oc, 1e-5)
+        gy = torch.randn(oc.shape, generator=g)
+        od.backward(gy.to(dev)); oc.backward(gy)
+        _close(yd.grad, yc.grad, 1e-5)
+
+
+def _assorted_small_operators(dev):
+    g = torch.Generator().manual_seed(53)
+    a = torch.randn(6, 9, generator=g)
+    _close(2.0 ** a.to(dev), 2.0 ** a, 1e-5)
+    _close(torch.pow(0.5, a.to(dev)), torch.pow(0.5, a), 1e-5)
+    nan = a.clone(); nan[1, 2] = float("nan"); nan[4, 0] = float("nan")
+    _close(torch.nansum(nan.to(dev)), torch.nansum(nan), 1e-5)
+    _close(torch.nansum(nan.to(dev), dim=1, keepdim=True), torch.nansum(nan, dim=1, keepdim=True), 1e-5)
+    pr = torch.rand(6, 9, generator=g).clamp(0.01, 0.99)
+    for eps in (None, 0.2):
+        pd, pc = pr.clone().to(dev).requires_grad_(), pr.clone().requires_grad_()
+        ld, lc = torch.logit(pd, eps), torch.logit(pc, eps)
+        _close(ld, lc, 1e-5)
+        ld.sum().backward(); lc.sum().backward()
+        _close(pd.grad, pc.grad, 1e-5)
+    for kw in ({}, {"dim": 1}, {"dim": 0, "keepdim": True}):
+        d, c = torch.aminmax(a.to(dev), **kw), torch.aminmax(a, **kw)
+        assert torch.equal(d.min.cpu(), c.min) and torch.equal(d.max.cpu(), c.max)
+    img = torch.randn(2, 12, 5, 4, generator=g)
+    assert torch.equal(F.channel_shuffle(img.to(dev), 3).cpu(), F.channel_shuffle(img, 3))
+    ints = torch.randint(0, 20, (7, 5), generator=g)
+    cand = torch.tensor([3, 7, 19, 40])
+    assert torch.equal(torch.isin(ints.to(dev), cand.to(dev)).cpu(), torch.isin(ints, cand))
+    assert torch.equal(torch.isin(ints.to(dev), cand.to(dev), invert=True).cpu(), torch.isin(ints, cand, invert=True))
+    assert torch.equal(torch.isin(ints.to(dev), 7).cpu(), torch.isin(ints, 7))
+    assert torch.equal(torch.isin(a.to(dev), a[2].to(dev)).cpu(), torch.isin(a, a[2]))
+    reps = torch.tensor([2, 0, 3, 1])
+    assert torch.equal(torch.repeat_interleave(reps.to(dev)).cpu(), torch.repeat_interleave(reps))
+    rows = torch.randn(4, 3, generator=g)
+    assert torch.equal(torch.repeat_interleave(rows.to(dev), reps.to(dev), dim=0).cpu(), torch.repeat_interleave(rows, reps, dim=0))
+    assert torch.equal(torch.repeat_interleave(rows.to(dev), 2, dim=1).cpu(), torch.repeat_interleave(rows, 2, dim=1))
+    pooled, where = F.max_pool2d(img, 2, return_indices=True, ceil_mode=True)
+    ud = F.max_unpool2d(pooled.to(dev), where.to(dev), 2, output_size=(5, 4))
+    assert torch.equal(ud.cpu(), F.max_unpool2d(pooled, where, 2, output_size=(5, 4)))
+    index = torch.stack([torch.randperm(9, generator=g)[:4] for _ in range(6)])           # unique along the scattered dimension
+    src = torch.randn(6, 7, generator=g)
+    assert torch.equal(a.to(dev).scatter(1, index.to(dev), src.to(dev)).cpu(), a.scatter(1, index, src))
+    col = torch.stack([torch.randperm(6, generator=g)[:3] for _ in range(9)], 1)
+    src_rows = torch.randn(3, 9, generator=g)
+    b = a.clone().to(dev)
+    b.scatter_(0, col.to(dev), src_rows.to(dev))
+    assert torch.equal(b.cpu(), a.clone().scatter_(0, col, src_rows))
+    mean, std = torch.full((20000,), 3.0), torch.full((20000,), 0.5)
+    for draw in (torch.normal(mean.to(dev), std.to(dev)), torch.normal(mean.to(dev), 0.5), torch.normal(3.0, std.to(dev))):
+        draw = draw.cpu()
+        assert draw.shape == (20000,) and abs(float(draw.mean()) - 3.0) < 0.02 and abs(float(draw.std()) - 0.5) < 0.02
+
+
+def test_pooling_of_volumes(vk):
+    _pooling_of_volumes(vk)
+    h = torch.randn(2, 3, 8, 10, 6, generator=torch.Generator().manual_seed(48)).half()
+    _close(F.max_pool3d(h.to(vk), 2).float(), F.max_pool3d(h.float(), 2), 1e-3)
+    _close(F.avg_pool3d(h.to(vk), 2).float(), F.avg_pool3d(h.float(), 2), 2e-3)
+
+
+def test_assorted_small_operators(vk):
+    _assorted_small_operators(vk)

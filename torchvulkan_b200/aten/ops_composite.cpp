@@ -452,6 +452,120 @@ at::Tensor vk_linalg_cross(const at::Tensor& self, const at::Tensor& other, int6
 }
 at::Tensor& vk_linalg_cross_out(const at::Tensor& self, const at::Tensor& other, int64_t dim, at::Tensor& out) { return into(out, vk_linalg_cross(self, other, dim)); }
 
+// adaptive average pooling of a volume: one averaging matrix per axis, depth first and then the two plane axes
+at::Tensor adaptive_avg_volume(const at::Tensor& x, at::IntArrayRef in, at::IntArrayRef out, bool transpose) {
+    TORCH_CHECK(x.dim() == 4 || x.dim() == 5, "adaptive_avg_pool3d: expected a 4-D or 5-D input, got ", x.sizes());
+    auto mat = [&](int i) {
+        at::Tensor a = adaptive_avg_matrix(in[i], out[i], x);
+        return transpose ? a.t().contiguous() : a;                        // forward [out, in]; backward [in, out]
+    };
+    const int64_t d0 = x.size(-3), h0 = x.size(-2), w0 = x.size(-1);
+    const int64_t d1 = transpose ? in[0] : out[0], h1 = transpose ? in[1] : out[1], w1 = transpose ? in[2] : out[2];
+    at::Tensor v = x.contiguous().reshape({-1, d0, h0 * w0});
+    const int64_t P = v.size(0);
+    v = at::matmul(mat(0), v).reshape({P * d1, h0, w0});
+    v = at::matmul(at::matmul(mat(1), v), mat(2).t().contiguous());
+    std::vector<int64_t> shape(x.sizes().begin(), x.sizes().end() - 3);
+    shape.insert(shape.end(), {d1, h1, w1});
+    return v.reshape(shape);
+}
+at::Tensor adaptive_avg_pool3d(const at::Tensor& self, at::IntArrayRef output_size) {
+    TORCH_CHECK(output_size.size() == 3 && output_size[0] > 0 && output_size[1] > 0 && output_size[2] > 0, "adaptive_avg_pool3d: output_size must be three positive sizes");
+    return adaptive_avg_volume(self, {self.size(-3), self.size(-2), self.size(-1)}, output_size, false);
+}
+at::Tensor adaptive_avg_pool3d_backward(const at::Tensor& grad, const at::Tensor& self) {
+    return adaptive_avg_volume(grad, {self.size(-3), self.size(-2), self.size(-1)}, {grad.size(-3), grad.size(-2), grad.size(-1)}, true);
+}
+
+// a scalar base raised to a tensor of exponents
+at::Tensor pow_scalar(const at::Scalar& base, const at::Tensor& exponent) {
+    if (!is_hot_float(exponent.scalar_type())) TVK_NOT_IMPLEMENTED("pow(scalar, tensor) for exponent dtype ", exponent.scalar_type());
+    return at::pow(at::full_like(exponent, base), exponent);
+}
+// torch.normal with tensor parameters: standard normal draws, scaled and shifted
+at::Tensor normal_draw(at::IntArrayRef shape, const at::Tensor& like, c10::optional<at::Generator> gen) {
+    if (!is_hot_float(like.scalar_type())) TVK_NOT_IMPLEMENTED("normal for dtype ", like.scalar_type());
+    return at::empty(shape, like.options()).normal_(0.0, 1.0, gen);
+}
+at::Tensor normal_tensor_float(const at::Tensor& mean, double std, c10::optional<at::Generator> gen) {
+    TORCH_CHECK(std >= 0.0, "normal expects std >= 0.0, but found std ", std);
+    return normal_draw(mean.sizes(), mean, gen) * std + mean;
+}
+at::Tensor normal_float_tensor(double mean, const at::Tensor& std, c10::optional<at::Generator> gen) { return normal_draw(std.sizes(), std, gen) * std + mean; }
+at::Tensor normal_tensor_tensor(const at::Tensor& mean, const at::Tensor& std, c10::optional<at::Generator> gen) {
+    return normal_draw(at::infer_size(mean.sizes(), std.sizes()), mean, gen) * std + mean;
+}
+
+// membership test by comparing every element with every candidate (candidates are expected to be few)
+at::Tensor isin_tensors(const at::Tensor& elements, const at::Tensor& test_elements, bool, bool invert) {
+    TORCH_CHECK(elements.numel() * std::max<int64_t>(test_elements.numel(), 1) <= (int64_t{1} << 30), "torchvulkan [NOT IMPLEMENTED]: isin over more than 2^30 comparisons");
+    at::Tensor tests = is_vulkan(test_elements) ? test_elements : test_elements.to(elements.device());
+    at::Tensor elems = is_vulkan(elements) ? elements : elements.to(tests.device());
+    at::Tensor found = tests.numel() == 0 ? at::zeros(elems.sizes(), elems.options().dtype(at::kBool))
+                                          : at::any(at::eq(elems.contiguous().unsqueeze(-1), tests.contiguous().reshape({-1})), -1, false);
+    return invert ? at::logical_not(found) : found;
+}
+at::Tensor isin_tensor_scalar(const at::Tensor& elements, const at::Scalar& test, bool, bool invert) { return invert ? at::ne(elements, test) : at::eq(elements, test); }
+at::Tensor isin_scalar_tensor(const at::Scalar& element, const at::Tensor& tests, bool assume_unique, bool invert) {
+    return isin_tensors(at::full({}, element, tests.options()), tests, assume_unique, invert);
+}
+
+at::Tensor nansum(const at::Tensor& self, at::OptionalIntArrayRef dim, bool keepdim, c10::optional<at::ScalarType> dtype) {
+    return at::sum(at::where(at::isnan(self), at::zeros({}, self.options()), self), dim, keepdim, dtype);
+}
+// logit(x) = log(x / (1 - x)), x clamped to [eps, 1 - eps] when eps is given
+at::Tensor logit(const at::Tensor& self, c10::optional<double> eps) {
+    at::Tensor x = eps.has_value() ? at::clamp(self, *eps, 1.0 - *eps) : self;
+    return at::log(x / (1.0 - x));
+}
+at::Tensor logit_backward(const at::Tensor& grad, const at::Tensor& self, c10::optional<double> eps) {
+    const double lo = eps.value_or(0.0), hi = 1.0 - lo;
+    at::Tensor outside = at::logical_or(at::lt(self, lo), at::gt(self, hi));
+    at::Tensor fill = at::full({}, eps.has_value() ? 0.0 : std::numeric_limits<double>::quiet_NaN(), grad.options());
+    return at::where(outside, fill, grad / (self * (1.0 - self)));
+}
+std::tuple<at::Tensor, at::Tensor> aminmax(const at::Tensor& self, c10::optional<int64_t> dim, bool keepdim) {
+    if (dim.has_value()) return {at::amin(self, {*dim}, keepdim), at::amax(self, {*dim}, keepdim)};
+    TORCH_CHECK(self.numel() > 0, "aminmax(): cannot compute aminmax over an empty dimension as the operation has no identity.");
+    at::Tensor flat = self.reshape({-1});
+    at::Tensor lo = at::amin(flat, {0}, false), hi = at::amax(flat, {0}, false);
+    if (!keepdim) return {lo, hi};
+    std::vector<int64_t> ones(self.dim(), 1);
+    return {lo.reshape(ones), hi.reshape(ones)};
+}
+// channel i of group j moves to position i * groups + j
+at::Tensor channel_shuffle(const at::Tensor& self, c10::SymInt groups_sym) {
+    const int64_t groups = groups_sym.guard_int(__FILE__, __LINE__);
+    TORCH_CHECK(self.dim() > 2, "channel_shuffle expects input with > 2 dims, but got input with sizes ", self.sizes());
+    const int64_t c = self.size(1);
+    TORCH_CHECK(groups > 0 && c % groups == 0, "Number of groups to divide channels in must be positive and divide the number of channels; got ", groups, " for ", c, " channels");
+    if (self.numel() == 0) return self.clone();
+    return self.contiguous().reshape({self.size(0), groups, c / groups, -1}).transpose(1, 2).contiguous().reshape(self.sizes());
+}
+// repeat_interleave of a vector of counts: output position p belongs to the first entry whose running total exceeds p
+at::Tensor repeat_interleave_counts(const at::Tensor& repeats, c10::optional<c10::SymInt> output_size) {
+    TORCH_CHECK(repeats.dim() == 1 && (repeats.scalar_type() == at::kLong || repeats.scalar_type() == at::kInt), "repeat_interleave only accept 1D vector of int or long as repeat");
+    if (repeats.numel() == 0) return at::empty({0}, repeats.options().dtype(at::kLong));
+    TORCH_CHECK(repeats.numel() <= (int64_t{1} << 24), "torchvulkan [NOT IMPLEMENTED]: repeat_interleave of more than 2^24 counts");
+    at::Tensor totals = at::cumsum(repeats.to(at::kFloat), 0);
+    const int64_t n = output_size.has_value() ? output_size->guard_int(__FILE__, __LINE__) : static_cast<int64_t>(totals.narrow(0, repeats.numel() - 1, 1).item<float>());
+    TORCH_CHECK(n < (int64_t{1} << 24), "torchvulkan [NOT IMPLEMENTED]: repeat_interleave to 2^24 elements or more");
+    at::Tensor positions = at::arange(n, at::TensorOptions().dtype(at::kFloat).device(at::kCPU)).to(repeats.device());
+    return at::searchsorted(totals, positions, false, true);
+}
+// max_unpool2d: every pooled value goes back to the flat position its index names, zeros elsewhere
+at::Tensor max_unpool2d(const at::Tensor& self, const at::Tensor& indices, at::IntArrayRef output_size) {
+    TORCH_CHECK(output_size.size() == 2, "There should be exactly two elements (height, width) in output_size");
+    TORCH_CHECK((self.dim() == 3 || self.dim() == 4) && self.sizes() == indices.sizes(), "max_unpool2d: expected a 3-D or 4-D input and indices of its shape");
+    TORCH_CHECK(indices.scalar_type() == at::kLong, "elements in indices should be type int64");
+    const int64_t planes = self.numel() ? self.numel() / (self.size(-2) * self.size(-1)) : 0;
+    std::vector<int64_t> shape(self.sizes().begin(), self.sizes().end() - 2);
+    shape.insert(shape.end(), {output_size[0], output_size[1]});
+    if (planes == 0) return at::zeros(shape, self.options());
+    at::Tensor zero = at::zeros({planes, output_size[0] * output_size[1]}, self.options());
+    return at::scatter_add(zero, 1, indices.contiguous().reshape({planes, -1}), self.contiguous().reshape({planes, -1})).reshape(shape);
+}
+
 // prelu with its weight already broadcast to the input (ATen reshapes it before calling the kernel)
 at::Tensor prelu_kernel(const at::Tensor& self, const at::Tensor& weight) { return at::where(at::gt(self, 0), self, weight * self); }
 std::tuple<at::Tensor, at::Tensor> prelu_kernel_backward(const at::Tensor& grad, const at::Tensor& self, const at::Tensor& weight) {
@@ -687,6 +801,22 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("index_fill_.int_Scalar", &index_fill_scalar_);
     m.impl("binary_cross_entropy", &bce);
     m.impl("binary_cross_entropy_backward", &bce_backward);
+    m.impl("_adaptive_avg_pool3d", &adaptive_avg_pool3d);
+    m.impl("_adaptive_avg_pool3d_backward", &adaptive_avg_pool3d_backward);
+    m.impl("pow.Scalar", &pow_scalar);
+    m.impl("normal.Tensor_float", &normal_tensor_float);
+    m.impl("normal.float_Tensor", &normal_float_tensor);
+    m.impl("normal.Tensor_Tensor", &normal_tensor_tensor);
+    m.impl("isin.Tensor_Tensor", &isin_tensors);
+    m.impl("isin.Tensor_Scalar", &isin_tensor_scalar);
+    m.impl("isin.Scalar_Tensor", &isin_scalar_tensor);
+    m.impl("nansum", &nansum);
+    m.impl("logit", &logit);
+    m.impl("logit_backward", &logit_backward);
+    m.impl("aminmax", &aminmax);
+    m.impl("channel_shuffle", &channel_shuffle);
+    m.impl("repeat_interleave.Tensor", &repeat_interleave_counts);
+    m.impl("max_unpool2d", &max_unpool2d);
     m.impl("linalg_cross", &vk_linalg_cross);
     m.impl("linalg_cross.out", &vk_linalg_cross_out);
     m.impl("_unique2", &unique2);

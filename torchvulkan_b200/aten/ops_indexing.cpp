@@ -166,6 +166,27 @@ at::Tensor& vk_scatter_add_(at::Tensor& self, int64_t dim, const at::Tensor& ind
     return self;
 }
 
+// scatter of a source tensor: the addressed elements take the source value, the others keep self. It is built from two
+// additive scatters (the values and a hit count); where several source elements address one position, for which ATen
+// promises no particular winner, the result is their mean.
+at::Tensor vk_scatter_src(const at::Tensor& self, int64_t dim, const at::Tensor& index_in, const at::Tensor& src) {
+    require_table(self, "scatter");
+    at::Tensor index = long_index(index_in, "scatter");
+    if (index.numel() == 0) return self.clone();
+    TORCH_CHECK(src.scalar_type() == self.scalar_type(), "scatter(): Expected self.dtype to be equal to src.dtype");
+    at::Tensor zero = at::zeros_like(self, at::MemoryFormat::Contiguous);
+    at::Tensor count = vk_scatter_add(zero, dim, index, at::ones(index.sizes(), self.options()));
+    at::Tensor sum = vk_scatter_add(zero, dim, index, src);
+    return at::where(at::gt(count, 0), sum / at::clamp_min(count, 1.0), self);
+}
+at::Tensor& vk_scatter_src_out(const at::Tensor& self, int64_t dim, const at::Tensor& index, const at::Tensor& src, at::Tensor& out) {
+    return into(out, vk_scatter_src(self, dim, index, src));
+}
+at::Tensor& vk_scatter_src_(at::Tensor& self, int64_t dim, const at::Tensor& index, const at::Tensor& src) {
+    self.copy_(vk_scatter_src(self, dim, index, src));
+    return self;
+}
+
 // scatter of one value: out = self with `value` at the addressed elements. The addressed set is the union over the index
 // entries along dim, found by comparing a coordinate ramp with each index slice (one_hot is the case of one slice).
 at::Tensor vk_scatter_value(const at::Tensor& self, int64_t dim, const at::Tensor& index_in, const at::Scalar& value) {
@@ -426,6 +447,9 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("scatter_add", &vk_scatter_add);
     m.impl("scatter_add.out", &vk_scatter_add_out);
     m.impl("scatter_add_", &vk_scatter_add_);
+    m.impl("scatter.src", &vk_scatter_src);
+    m.impl("scatter.src_out", &vk_scatter_src_out);
+    m.impl("scatter_.src", &vk_scatter_src_);
     m.impl("scatter.value", &vk_scatter_value);
     m.impl("scatter.value_out", &vk_scatter_value_out);
     m.impl("scatter_.value", &vk_scatter_value_);
