@@ -896,3 +896,73 @@ def test_pooling_of_volumes(vk):
 
 def test_assorted_small_operators(vk):
     _assorted_small_operators(vk)
+
+
+def _bicubic_and_embedding_bags(dev):
+    g = torch.Generator().manual_seed(59)
+    x = torch.randn(2, 3, 7, 9, generator=g)
+    for kw in ({"size": (14, 18)}, {"size": (11, 5), "align_corners": True}, {"size": (5, 13)}, {"size": (1, 1), "align_corners": True},
+               {"scale_factor": (1.5, 2.5), "recompute_scale_factor": False}, {"size": (20, 3)}):
+        xd, xc = x.clone().to(dev).requires_grad_(), x.clone().requires_grad_()
+        yd, yc = F.interpolate(xd, mode="bicubic", **kw), F.interpolate(xc, mode="bicubic", **kw)
+        _close(yd, yc, 2e-5)
+        gy = torch.randn(yc.shape, generator=g)
+        yd.backward(gy.to(dev)); yc.backward(gy)
+        _close(xd.grad, xc.grad, 2e-5)
+
+    V, D = 20, 6
+    idx = torch.randint(0, V, (17,), generator=g)
+    offs = torch.tensor([0, 3, 3, 9, 15])
+    psw = torch.rand(17, generator=g)
+    table = torch.randn(V, D, generator=g)
+    for mode, weights in (("sum", None), ("sum", psw), ("mean", None)):
+        for include_last in (False, True):
+            for pad in (None, 4):
+                o = torch.cat([offs, torch.tensor([17])]) if include_last else offs
+                wd, wc = table.clone().to(dev).requires_grad_(), table.clone().requires_grad_()
+                pd = None if weights is None else weights.clone().to(dev).requires_grad_()
+                pc = None if weights is None else weights.clone().requires_grad_()
+                yd = F.embedding_bag(idx.to(dev), wd, o.to(dev), mode=mode, per_sample_weights=pd, include_last_offset=include_last, padding_idx=pad)
+                yc = F.embedding_bag(idx, wc, o, mode=mode, per_sample_weights=pc, include_last_offset=include_last, padding_idx=pad)
+                _close(yd, yc, 1e-5)
+                gy = torch.randn(yc.shape, generator=g)
+                yd.backward(gy.to(dev)); yc.backward(gy)
+                _close(wd.grad, wc.grad, 1e-5)
+                if pc is not None:
+                    _close(pd.grad, pc.grad, 1e-5)
+    torch.manual_seed(3)
+    ref = torch.nn.EmbeddingBag(V, D)                                   # mean over the rows of a 2-D input
+    bag = torch.nn.EmbeddingBag(V, D)
+    bag.load_state_dict(ref.state_dict())
+    bag = bag.to(dev)
+    two_d = torch.randint(0, V, (4, 5), generator=g)
+    _close(bag(two_d.to(dev)), ref(two_d), 1e-5)
+    with torch.no_grad():
+        _close(bag(idx.to(dev), offs.to(dev)), ref(idx, offs), 1e-5)
+
+
+def test_bicubic_upsampling_and_embedding_bags(vk):
+    _bicubic_and_embedding_bags(vk)
+
+
+def _volume_padding_and_index_copy(dev):
+    g = torch.Generator().manual_seed(61)
+    v = torch.randn(2, 3, 5, 6, 7, generator=g)
+    for mode in ("reflect", "replicate"):
+        vd, vc = v.clone().to(dev).requires_grad_(), v.clone().requires_grad_()
+        yd, yc = F.pad(vd, (1, 2, 0, 3, 2, 1), mode=mode), F.pad(vc, (1, 2, 0, 3, 2, 1), mode=mode)
+        assert torch.equal(yd.detach().cpu(), yc.detach())
+        gy = torch.randn(yc.shape, generator=g)
+        yd.backward(gy.to(dev)); yc.backward(gy)
+        _close(vd.grad, vc.grad, 1e-5)
+    a = torch.randn(6, 9, generator=g)
+    rows, src = torch.tensor([4, 0, 2]), torch.randn(3, 9, generator=g)
+    assert torch.equal(a.clone().to(dev).index_copy(0, rows.to(dev), src.to(dev)).cpu(), a.index_copy(0, rows, src))
+    cols, src_c = torch.tensor([8, 1]), torch.randn(6, 2, generator=g)
+    b = a.clone().to(dev)
+    b.index_copy_(1, cols.to(dev), src_c.to(dev))
+    assert torch.equal(b.cpu(), a.clone().index_copy_(1, cols, src_c))
+
+
+def test_volume_padding_and_index_copy(vk):
+    _volume_padding_and_index_copy(vk)

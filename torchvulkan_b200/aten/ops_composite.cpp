@@ -673,6 +673,64 @@ at::Tensor upsample_bilinear2d_backward(const at::Tensor& grad, at::IntArrayRef 
     return blend_axis_backward(blend_axis_backward(grad, 3, w, input_size[3]), 2, h, input_size[2]);
 }
 
+// Bicubic upsampling is separable as well: four taps per axis around floor(source position), indices clamped to the
+// edge, weights from the cubic convolution kernel with A = -0.75 evaluated in fp32 on the host as ATen evaluates them.
+struct CubicAxis {
+    at::Tensor index[4], weight[4];
+};
+CubicAxis cubic_axis(int64_t in, int64_t out, bool align_corners, const c10::optional<double>& scale, const at::Device& dev) {
+    const float s = (float)area_scale(in, out, align_corners, scale), A = -0.75f;
+    auto near = [A](float x) { return ((A + 2.f) * x - (A + 3.f)) * x * x + 1.f; };                 // |x| <= 1
+    auto far = [A](float x) { return ((A * x - 5.f * A) * x + 8.f * A) * x - 4.f * A; };            // 1 < |x| < 2
+    std::vector<int64_t> idx[4];
+    std::vector<float> w[4];
+    for (int64_t o = 0; o < out; ++o) {
+        const float real = align_corners ? s * (float)o : s * ((float)o + 0.5f) - 0.5f;
+        const float fl = std::floor(real), t = real - fl;
+        const int64_t base = (int64_t)fl;
+        const float ws[4] = {far(t + 1.f), near(t), near(1.f - t), far(2.f - t)};
+        for (int k = 0; k < 4; ++k) {
+            idx[k].push_back(std::min<int64_t>(std::max<int64_t>(base - 1 + k, 0), in - 1));
+            w[k].push_back(ws[k]);
+        }
+    }
+    CubicAxis m;
+    for (int k = 0; k < 4; ++k) {
+        m.index[k] = at::tensor(idx[k], at::TensorOptions().dtype(at::kLong)).to(dev);
+        m.weight[k] = at::tensor(w[k], at::TensorOptions().dtype(at::kFloat)).to(dev);
+    }
+    return m;
+}
+at::Tensor cubic_blend(const at::Tensor& x, int64_t dim, const CubicAxis& m) {
+    std::vector<int64_t> view(x.dim(), 1);
+    view[dim] = m.weight[0].numel();
+    at::Tensor r;
+    for (int k = 0; k < 4; ++k) {
+        at::Tensor term = at::index_select(x, dim, m.index[k]) * m.weight[k].to(x.scalar_type()).view(view);
+        r = r.defined() ? r + term : term;
+    }
+    return r;
+}
+at::Tensor cubic_blend_backward(const at::Tensor& g, int64_t dim, const CubicAxis& m, int64_t in) {
+    std::vector<int64_t> view(g.dim(), 1), shape(g.sizes().begin(), g.sizes().end());
+    view[dim] = m.weight[0].numel();
+    shape[dim] = in;
+    at::Tensor r = at::zeros(shape, g.options());
+    for (int k = 0; k < 4; ++k) r = r.index_add(dim, m.index[k], g * m.weight[k].to(g.scalar_type()).view(view));
+    return r;
+}
+at::Tensor upsample_bicubic2d(const at::Tensor& self, at::IntArrayRef size, bool align_corners, c10::optional<double> sh, c10::optional<double> sw) {
+    TORCH_CHECK(self.dim() == 4 && size.size() == 2, "upsample_bicubic2d: expected a 4-D input and two output sizes");
+    TORCH_CHECK(self.size(2) > 0 && self.size(3) > 0 && size[0] > 0 && size[1] > 0, "upsample_bicubic2d: input and output sizes should be greater than 0");
+    return cubic_blend(cubic_blend(self, 2, cubic_axis(self.size(2), size[0], align_corners, sh, self.device())), 3,
+                       cubic_axis(self.size(3), size[1], align_corners, sw, self.device()));
+}
+at::Tensor upsample_bicubic2d_backward(const at::Tensor& grad, at::IntArrayRef size, at::IntArrayRef input_size, bool align_corners, c10::optional<double> sh,
+                                       c10::optional<double> sw) {
+    at::Tensor gw = cubic_blend_backward(grad, 3, cubic_axis(input_size[3], size[1], align_corners, sw, grad.device()), input_size[3]);
+    return cubic_blend_backward(gw, 2, cubic_axis(input_size[2], size[0], align_corners, sh, grad.device()), input_size[2]);
+}
+
 // nan_to_num: NaN -> nan (0), +inf -> posinf (the dtype's largest value), -inf -> neginf (its lowest)
 at::Tensor vk_nan_to_num(const at::Tensor& self, c10::optional<double> nan, c10::optional<double> posinf, c10::optional<double> neginf) {
     TORCH_CHECK(is_hot_float(self.scalar_type()), "torchvulkan [NOT IMPLEMENTED]: nan_to_num for ", self.scalar_type());
@@ -801,6 +859,8 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("index_fill_.int_Scalar", &index_fill_scalar_);
     m.impl("binary_cross_entropy", &bce);
     m.impl("binary_cross_entropy_backward", &bce_backward);
+    m.impl("upsample_bicubic2d", &upsample_bicubic2d);
+    m.impl("upsample_bicubic2d_backward", &upsample_bicubic2d_backward);
     m.impl("_adaptive_avg_pool3d", &adaptive_avg_pool3d);
     m.impl("_adaptive_avg_pool3d_backward", &adaptive_avg_pool3d_backward);
     m.impl("pow.Scalar", &pow_scalar);

@@ -187,6 +187,30 @@ at::Tensor& vk_scatter_src_(at::Tensor& self, int64_t dim, const at::Tensor& ind
     return self;
 }
 
+// index_copy: the slices of self named by index are replaced by the slices of source. Like scatter with a source it is two
+// additive passes (values and a hit count); slices named more than once, for which ATen promises no winner, average.
+at::Tensor vk_index_copy(const at::Tensor& self, int64_t dim, const at::Tensor& index_in, const at::Tensor& source) {
+    require_table(self, "index_copy");
+    at::Tensor index = long_index(index_in, "index_copy");
+    TORCH_CHECK(index.dim() <= 1, "index_copy_(): Index should have dimension 1 or 0, actual = ", index.dim());
+    TORCH_CHECK(source.scalar_type() == self.scalar_type(), "index_copy_(): self and source expected to have the same dtype");
+    if (index.numel() == 0) return self.clone();
+    if (self.dim() == 0) return source.reshape({}).clone();
+    dim = at::maybe_wrap_dim(dim, self.dim());
+    at::Tensor idx = index.reshape({-1});
+    TORCH_CHECK(source.dim() == self.dim() && source.size(dim) == idx.numel(), "index_copy_(): Number of indices (", idx.numel(), ") should be equal to source.size(dim)");
+    at::Tensor zero = at::zeros_like(self, at::MemoryFormat::Contiguous);
+    at::Tensor sum = zero.index_add(dim, idx, source), count = zero.index_add(dim, idx, at::ones_like(source));
+    return at::where(at::gt(count, 0), sum / at::clamp_min(count, 1.0), self);
+}
+at::Tensor& vk_index_copy_out(const at::Tensor& self, int64_t dim, const at::Tensor& index, const at::Tensor& source, at::Tensor& out) {
+    return into(out, vk_index_copy(self, dim, index, source));
+}
+at::Tensor& vk_index_copy_(at::Tensor& self, int64_t dim, const at::Tensor& index, const at::Tensor& source) {
+    self.copy_(vk_index_copy(self, dim, index, source));
+    return self;
+}
+
 // scatter of one value: out = self with `value` at the addressed elements. The addressed set is the union over the index
 // entries along dim, found by comparing a coordinate ramp with each index slice (one_hot is the case of one slice).
 at::Tensor vk_scatter_value(const at::Tensor& self, int64_t dim, const at::Tensor& index_in, const at::Scalar& value) {
@@ -447,6 +471,9 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("scatter_add", &vk_scatter_add);
     m.impl("scatter_add.out", &vk_scatter_add_out);
     m.impl("scatter_add_", &vk_scatter_add_);
+    m.impl("index_copy", &vk_index_copy);
+    m.impl("index_copy.out", &vk_index_copy_out);
+    m.impl("index_copy_", &vk_index_copy_);
     m.impl("scatter.src", &vk_scatter_src);
     m.impl("scatter.src_out", &vk_scatter_src_out);
     m.impl("scatter_.src", &vk_scatter_src_);

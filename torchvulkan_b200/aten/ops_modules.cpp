@@ -371,6 +371,84 @@ at::Tensor& where_self_out(const at::Tensor& cond, const at::Tensor& a, const at
     return out;
 }
 
+// ---- nn.EmbeddingBag (sum and mean) ----------------------------------------------------------------------------------------
+// Bags are runs of `indices` starting at `offsets`. The bag of every position is the number of later bag starts at or before
+// it (a searchsorted over the starts); the output is an index_add of the gathered rows into their bags, the weight gradient
+// an index_add of the bags' gradients into the rows. Entries equal to padding_idx weigh nothing and are not counted in a
+// mean. Positions ride in fp32, which bounds the number of indices.
+struct Bags {
+    at::Tensor indices, bag, scale;            // Long [n], Long [n], and the per-entry factor (undefined = all ones)
+    int64_t count;
+};
+Bags bags_of(const at::Tensor& indices_in, const at::Tensor& offsets_in, bool include_last_offset, const c10::optional<at::Tensor>& per_sample_weights,
+             int64_t padding_idx, at::ScalarType dtype) {
+    TORCH_CHECK(indices_in.dim() == 1 && offsets_in.dim() == 1, "embedding_bag: indices and offsets must be 1-D here (a 2-D input is flattened by the caller)");
+    Bags b;
+    b.indices = indices_in.scalar_type() == at::kLong ? indices_in : indices_in.to(at::kLong);
+    const int64_t n = b.indices.numel();
+    TORCH_CHECK(n < (int64_t{1} << 24), "torchvulkan [NOT IMPLEMENTED]: embedding_bag over 2^24 indices or more");
+    b.count = offsets_in.numel() - (include_last_offset ? 1 : 0);
+    TORCH_CHECK(b.count >= 0, "embedding_bag: include_last_offset needs at least one offset");
+    const at::TensorOptions long_opts = b.indices.options();
+    if (b.count <= 1 || n == 0) {
+        b.bag = at::zeros({n}, long_opts);
+    } else {
+        at::Tensor later_starts = offsets_in.narrow(0, 1, b.count - 1).to(at::kFloat).contiguous();
+        at::Tensor positions = at::arange(n, at::TensorOptions().dtype(at::kFloat).device(at::kCPU)).to(b.indices.device());
+        b.bag = at::searchsorted(later_starts, positions, false, true);
+    }
+    if (padding_idx >= 0) b.scale = at::ne(b.indices, padding_idx).to(dtype);
+    if (per_sample_weights.has_value() && per_sample_weights->defined()) {
+        TORCH_CHECK(per_sample_weights->dim() == 1 && per_sample_weights->numel() == n, "embedding_bag: per_sample_weights must have one entry per index");
+        b.scale = b.scale.defined() ? b.scale * per_sample_weights->to(dtype) : per_sample_weights->to(dtype);
+    }
+    return b;
+}
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> embedding_bag(const at::Tensor& weight, const at::Tensor& indices, const at::Tensor& offsets, bool,
+                                                                         int64_t mode, bool sparse, const c10::optional<at::Tensor>& per_sample_weights,
+                                                                         bool include_last_offset, int64_t padding_idx) {
+    if (mode != 0 && mode != 1) TVK_NOT_IMPLEMENTED("embedding_bag in max mode");
+    if (sparse) TVK_NOT_IMPLEMENTED("embedding_bag with sparse gradients");
+    TORCH_CHECK(weight.dim() == 2, "embedding_bag: weight must be 2-D");
+    const at::ScalarType st = weight.scalar_type();
+    Bags b = bags_of(indices, offsets, include_last_offset, per_sample_weights, padding_idx, st);
+    const int64_t n = b.indices.numel(), D = weight.size(1);
+    at::Tensor out = at::zeros({b.count, D}, weight.options()), sizes = at::zeros({b.count}, weight.options().dtype(at::kFloat));
+    if (n > 0 && b.count > 0) {
+        at::Tensor rows = at::index_select(weight, 0, b.indices);
+        if (b.scale.defined()) rows = rows * b.scale.unsqueeze(1);
+        out = out.index_add(0, b.bag, rows);
+        at::Tensor counted = padding_idx >= 0 ? at::ne(b.indices, padding_idx).to(at::kFloat) : at::ones({n}, sizes.options());
+        sizes = sizes.index_add(0, b.bag, counted);
+        if (mode == 1) out = out / at::clamp_min(sizes, 1.0).to(st).unsqueeze(1);
+    }
+    return {out, b.bag, sizes.to(at::kLong), at::empty({0}, b.indices.options())};
+}
+at::Tensor embedding_bag_backward(const at::Tensor& grad, const at::Tensor& indices, const at::Tensor& offsets, const at::Tensor& offset2bag,
+                                  const at::Tensor& bag_size, const at::Tensor&, c10::SymInt num_weights, bool scale_grad_by_freq, int64_t mode, bool sparse,
+                                  const c10::optional<at::Tensor>& per_sample_weights, int64_t padding_idx) {
+    if (mode != 0 && mode != 1) TVK_NOT_IMPLEMENTED("embedding_bag backward in max mode");
+    if (sparse || scale_grad_by_freq) TVK_NOT_IMPLEMENTED("embedding_bag backward with sparse gradients or scale_grad_by_freq");
+    const at::ScalarType st = grad.scalar_type();
+    Bags b = bags_of(indices, offsets, offsets.numel() > grad.size(0), per_sample_weights, padding_idx, st);
+    at::Tensor table = at::zeros({num_weights.guard_int(__FILE__, __LINE__), grad.size(1)}, grad.options());
+    if (b.indices.numel() == 0 || grad.size(0) == 0) return table;
+    const at::Tensor& bag = offset2bag.numel() == b.indices.numel() ? offset2bag : b.bag;
+    at::Tensor g = at::index_select(grad, 0, bag);
+    if (mode == 1) g = g / at::index_select(at::clamp_min(bag_size.to(at::kFloat), 1.0).to(st), 0, bag).unsqueeze(1);
+    if (b.scale.defined()) g = g * b.scale.unsqueeze(1);
+    return table.index_add(0, b.indices, g);
+}
+at::Tensor embedding_bag_per_sample_weights_backward(const at::Tensor& grad, const at::Tensor& weight, const at::Tensor& indices, const at::Tensor& offsets,
+                                                     const at::Tensor& offset2bag, int64_t mode, int64_t padding_idx) {
+    TORCH_CHECK(mode == 0, "embedding_bag_backward: per_sample_weights only supported for mode='sum'");
+    Bags b = bags_of(indices, offsets, offsets.numel() > grad.size(0), c10::nullopt, padding_idx, grad.scalar_type());
+    if (b.indices.numel() == 0) return at::zeros({0}, grad.options());
+    const at::Tensor& bag = offset2bag.numel() == b.indices.numel() ? offset2bag : b.bag;
+    at::Tensor dots = at::sum(at::index_select(grad, 0, bag) * at::index_select(weight, 0, b.indices), {1});
+    return b.scale.defined() ? dots * b.scale : dots;
+}
+
 // ---- inference fast paths of nn.MultiheadAttention and nn.TransformerEncoderLayer ------------------------------------------
 // In eval mode without gradients those modules call one operator for the whole block on every device type they list, this
 // one included. A mask marks what is EXCLUDED (nonzero / True / -inf), shaped by mask_type: 0 = [T, T] over (query, key),
@@ -440,6 +518,10 @@ bool nested_tensor_from_mask_left_aligned(const at::Tensor&, const at::Tensor&) 
 }  // namespace
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+    m.impl("_embedding_bag", &embedding_bag);
+    m.impl("_embedding_bag_forward_only", &embedding_bag);
+    m.impl("_embedding_bag_backward", &embedding_bag_backward);
+    m.impl("_embedding_bag_per_sample_weights_backward", &embedding_bag_per_sample_weights_backward);
     m.impl("_native_multi_head_attention", &native_multi_head_attention);
     m.impl("_transformer_encoder_layer_fwd", &transformer_encoder_layer_fwd);
     m.impl("_nested_tensor_from_mask_left_aligned", &nested_tensor_from_mask_left_aligned);
@@ -453,6 +535,10 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("reflection_pad2d", &reflection_pad);
     m.impl("reflection_pad1d_backward", &reflection_pad_backward);
     m.impl("reflection_pad2d_backward", &reflection_pad_backward);
+    m.impl("reflection_pad3d", &reflection_pad);
+    m.impl("reflection_pad3d_backward", &reflection_pad_backward);
+    m.impl("replication_pad3d", &replication_pad);
+    m.impl("replication_pad3d_backward", &replication_pad_backward);
     m.impl("replication_pad1d", &replication_pad);
     m.impl("replication_pad2d", &replication_pad);
     m.impl("replication_pad1d_backward", &replication_pad_backward);
