@@ -580,6 +580,8 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
     m.impl("minimum", &bin_fn<TVK_B_MINIMUM, true>);
     m.impl("minimum.out", &bin_out<TVK_B_MINIMUM, true>);
     m.impl("pow.Tensor_Tensor", &bin_fn<TVK_B_POW, false>);
+    m.impl("pow_.Tensor", &bin_fn_<TVK_B_POW, false>);
+    m.impl("pow.Tensor_Tensor_out", &bin_out<TVK_B_POW, false>);
     m.impl("pow.Tensor_Scalar", &pow_tensor_scalar);
     m.impl("pow.Tensor_Scalar_out", &pow_tensor_scalar_out);
 

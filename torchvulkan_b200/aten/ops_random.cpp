@@ -113,6 +113,29 @@ at::Tensor& random_from_(at::Tensor& self, int64_t from, c10::optional<int64_t> 
     return random_range_(self, from, *to, "random_");
 }
 at::Tensor& random_to_(at::Tensor& self, int64_t to, c10::optional<at::Generator>) { return random_range_(self, 0, to, "random_"); }
+// bernoulli with a tensor of probabilities (torch.bernoulli(p)): one uniform draw per element compared with its probability
+at::Tensor& bernoulli_tensor_(at::Tensor& self, const at::Tensor& p, c10::optional<at::Generator>) {
+    if (self.numel() == 0) return self;
+    at::Tensor prob = is_hot_float(p.scalar_type()) ? p : p.to(at::kFloat);
+    at::Tensor u = at::empty(self.sizes(), prob.options().dtype(at::kFloat));
+    u.uniform_(0.0, 1.0);
+    at::Tensor drawn = at::lt(u, prob.to(at::kFloat));
+    TORCH_CHECK(drawn.sizes() == self.sizes(), "bernoulli_: the probabilities must broadcast to the shape of self");
+    self.copy_(self.scalar_type() == at::kBool ? drawn : drawn.to(self.scalar_type()));
+    return self;
+}
+// exponential_(lambda): -log(1 - u) / lambda with u uniform in [0, 1)
+at::Tensor& exponential_(at::Tensor& self, double lambd, c10::optional<at::Generator>) {
+    TORCH_CHECK(lambd > 0.0, "exponential_ expects lambda > 0.0, but found lambda=", lambd);
+    if (!is_hot_float(self.scalar_type())) TVK_NOT_IMPLEMENTED("exponential_ for dtype ", self.scalar_type(), " on the vulkan device");
+    if (self.numel() == 0) return self;
+    at::Tensor u = at::empty(self.sizes(), self.options().dtype(at::kFloat));
+    u.uniform_(0.0, 1.0);
+    // a draw of exactly zero is excluded (its logarithm is taken by gumbel_softmax and the like): floor at half an fp32 epsilon, as ATen does
+    at::Tensor v = at::clamp_min(at::neg(at::log1p(at::neg(u))), 5.9604644775390625e-8) * (1.0 / lambd);
+    self.copy_(v.to(self.scalar_type()));
+    return self;
+}
 // a random permutation: the order that sorts n uniform numbers
 at::Tensor& randperm_out(int64_t n, c10::optional<at::Generator>, at::Tensor& out) {
     TORCH_CHECK(n >= 0, "n must be non-negative, got", n);
@@ -127,6 +150,8 @@ at::Tensor& randperm_out(int64_t n, c10::optional<at::Generator>, at::Tensor& ou
 }  // namespace
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+    m.impl("bernoulli_.Tensor", &bernoulli_tensor_);
+    m.impl("exponential_", &exponential_);
     m.impl("random_.from", &random_from_);
     m.impl("random_.to", &random_to_);
     m.impl("randperm.generator_out", &randperm_out);
