@@ -5,8 +5,8 @@ driver allocations once it is running, cannot hand tvk_reduce a freshly allocate
 no-alloc variant keeps the per-CTA partials in a fixed array inside the library, so only inputs
 and outputs are passed. This test calls it through the C-ABI twice in a row (the second call
 finds the first call's partials still in the array) and compares with tvk_reduce on the same
-inputs; it also checks that an oversized shape is refused. The file sorts last on purpose so that
-a run stopping at the first failure has already gone through every other test."""
+inputs; it also checks that an oversized shape is refused. The file sorts behind the operator and
+device tests on purpose so that a run stopping at the first failure has already gone through them."""
 import ctypes as C
 
 import numpy as np
