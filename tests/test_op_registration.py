@@ -27,8 +27,8 @@ _native_multi_head_attention _transformer_encoder_layer_fwd _nested_tensor_from_
 native_layer_norm native_layer_norm_backward native_group_norm native_group_norm_backward native_batch_norm native_batch_norm_backward
 _softmax _softmax_backward_data _log_softmax _log_softmax_backward_data nll_loss_forward nll_loss_backward nll_loss2d_forward nll_loss2d_backward
 embedding embedding_dense_backward _embedding_bag _embedding_bag_forward_only _embedding_bag_backward _embedding_bag_per_sample_weights_backward
-native_dropout native_dropout_backward uniform_ normal_ bernoulli_.float multinomial normal.Tensor_Tensor normal.Tensor_float normal.float_Tensor
-add.Tensor sub.Tensor mul.Tensor div.Tensor pow.Tensor_Tensor pow.Tensor_Scalar pow.Scalar maximum minimum atan2 fmod.Tensor remainder.Tensor
+native_dropout native_dropout_backward uniform_ normal_ bernoulli_.float bernoulli_.Tensor exponential_ multinomial normal.Tensor_Tensor normal.Tensor_float normal.float_Tensor
+add.Tensor sub.Tensor mul.Tensor div.Tensor pow.Tensor_Tensor pow_.Tensor pow.Tensor_Scalar pow.Scalar maximum minimum atan2 fmod.Tensor remainder.Tensor
 relu gelu gelu_backward silu silu_backward sigmoid tanh exp log sqrt rsqrt abs neg erf erfinv sin cos floor ceil round trunc sign sgn
 eq.Tensor ne.Tensor lt.Tensor le.Tensor gt.Tensor ge.Tensor eq.Scalar logical_and logical_or logical_not logical_xor isnan where.self
 clamp clamp_min clamp_max lerp.Tensor lerp.Scalar addcmul addcdiv masked_fill_.Scalar masked_fill_.Tensor fill_.Scalar
